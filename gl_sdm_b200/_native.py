@@ -1,0 +1,351 @@
+"""ctypes binding of the C-ABI library (include/glsdm.h) and tensor-level wrappers.
+
+There is exactly one implementation behind these functions: the sm_100a kernels in
+``libglsdm_b200.so``. If the library has not been built, or a tensor is not a contiguous
+CUDA tensor, the call raises; nothing here computes on the CPU.
+
+The wrappers mirror the three native functions the reference's "urm" backend calls
+(gl_sdm/memory/backends/urm.py:49-82,109-122 and gl_sdm/memory/backends/commit.py:57-58).
+"""
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(_HERE, "libglsdm_b200.so")
+
+F32, BF16 = 0, 1
+DEV_ADDRESS_OUT_OF_RANGE = 1
+DEV_WAIT_EXPIRED = 2
+MAX_WIDTH = 32
+
+_lock = threading.Lock()
+_lib = None
+
+
+class Bank(ctypes.Structure):
+    """glsdm_bank of include/glsdm.h."""
+    _fields_ = [("values", ctypes.c_void_p), ("dtype", ctypes.c_int), ("banks", ctypes.c_int64),
+                ("heads", ctypes.c_int32), ("slots", ctypes.c_int64), ("dim", ctypes.c_int32),
+                ("slot_lo", ctypes.c_int64), ("slot_hi", ctypes.c_int64)]
+
+
+_p, _i, _i32, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+_BANK = ctypes.POINTER(Bank)
+SIGNATURES = {
+    "glsdm_abi_version": (ctypes.c_int, []),
+    "glsdm_status_string": (ctypes.c_char_p, [_i]),
+    "glsdm_last_cuda_error": (ctypes.c_char_p, []),
+    "glsdm_pk_select": (_i, [_p, _i64, _i32, _i32, _p, _i, _p, _p]),
+    "glsdm_snapshot_read": (_i, [_BANK, _p, _i, _p, _p, _i64, _i64, _i32, _p, _p, _p]),
+    "glsdm_pk_select_read": (_i, [_BANK, _p, _i64, _i64, _i32, _i32, _p, _p, _i, _p, _p, _p]),
+    "glsdm_pk_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _i64,
+                              _i64, _i32, _i32, _p, _p, _p, _p, _p]),
+    "glsdm_gather_rows": (_i, [_p, _i, _i64, _i32, _p, _i64, _p, _p, _p]),
+    "glsdm_token_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
+    "glsdm_commit_workspace_bytes": (_sz, [_i64, _i32]),
+    "glsdm_commit": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p]),
+    "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
+    "glsdm_score_topk": (_i, [_p, _p, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
+    "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),
+}
+
+
+def library():
+    """Load the shared library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIBRARY_PATH):
+                    raise RuntimeError(
+                        f"{LIBRARY_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; "
+                        "g.build()'` (nvcc, sm_100a). There is no CPU or PyTorch fallback for the GL-SDM memory operator.")
+                lib = ctypes.CDLL(LIBRARY_PATH)
+                for name, (restype, argtypes) in SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.restype, fn.argtypes = restype, argtypes
+                _lib = lib
+    return _lib
+
+
+def _check(status):
+    if status == 0:
+        return
+    lib = library()
+    text = lib.glsdm_status_string(status).decode()
+    if status == 4:
+        text += ": " + lib.glsdm_last_cuda_error().decode()
+        raise RuntimeError(f"glsdm: {text}")
+    raise ValueError(f"glsdm: {text}")
+
+
+def require_cuda(*tensors):
+    """Reference gl_sdm/memory/backends/primitives.py:7-11: no silent CPU path."""
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError("GL-SDM native kernels require contiguous CUDA tensors")
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise ValueError("GL-SDM banks are float32 or bfloat16")
+
+
+def bank_of(values, slot_lo=0, slot_hi=None, slots=None):
+    """Describe values [banks, heads, local_slots, dim]; a shard passes its global range."""
+    if values.ndim != 4:
+        raise ValueError("bank values must be [banks, heads, slots, dim]")
+    require_cuda(values)
+    banks, heads, local, dim = values.shape
+    slots = local if slots is None else slots
+    slot_hi = slot_lo + local if slot_hi is None else slot_hi
+    if slot_hi - slot_lo != local:
+        raise ValueError("shard range does not match the values tensor")
+    return Bank(values.data_ptr(), _dtype_code(values), banks, heads, slots, dim, slot_lo, slot_hi)
+
+
+def routes_out(width, half):
+    factor = min(width, half)
+    return min(width, factor * factor)
+
+
+_status_words = {}
+
+
+def status_word(device):
+    """A zeroed per-device uint32 the kernels OR error bits into."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        _status_words[key] = word
+    return word
+
+
+def raise_on_device_status(device):
+    """Synchronising check of the device status word (tests and debug paths)."""
+    word = status_word(device)
+    bits = int(word.item())
+    if bits:
+        word.zero_()
+        names = [n for b, n in ((DEV_ADDRESS_OUT_OF_RANGE, "address out of range"),
+                                (DEV_WAIT_EXPIRED, "bounded wait expired")) if bits & b]
+        raise RuntimeError("glsdm device status: " + ", ".join(names))
+
+
+def pk_select(scores, width, index_dtype=torch.int64):
+    """scores [..., 2*half] fp32 -> (index [..., k], weights [..., k])."""
+    require_cuda(scores)
+    if scores.dtype != torch.float32:
+        raise ValueError("factor scores must be float32")
+    half = scores.shape[-1] // 2
+    if half * 2 != scores.shape[-1] or half < 1:
+        raise ValueError("scores must hold two factors of equal width")
+    k = routes_out(width, half)
+    rows = scores.numel() // (2 * half)
+    index = torch.empty((*scores.shape[:-1], k), dtype=index_dtype, device=scores.device)
+    weights = torch.empty((*scores.shape[:-1], k), dtype=torch.float32, device=scores.device)
+    _check(library().glsdm_pk_select(_ptr(scores), rows, half, width, _ptr(index),
+                                     int(index_dtype == torch.int64), _ptr(weights), _stream(scores.device)))
+    return index, weights
+
+
+def snapshot_read(values, index, weights, rows_per_bank, requests=None, slot_lo=0, slots=None):
+    """Weighted sum of supplied routes; index/weights [..., k] with rows laid out [bank, token, head]."""
+    require_cuda(values, index, weights, requests)
+    if index.dtype not in (torch.int64, torch.int32) or weights.dtype != torch.float32:
+        raise ValueError("routes are int32/int64 indices with float32 weights")
+    if requests is not None and requests.dtype != torch.int64:
+        raise ValueError("requests must be int64")
+    bank = bank_of(values, slot_lo, None, slots)
+    width = index.shape[-1]
+    rows = index.numel() // width
+    out = torch.empty((*index.shape[:-1], values.shape[-1]), dtype=torch.float32, device=values.device)
+    _check(library().glsdm_snapshot_read(ctypes.byref(bank), _ptr(index), int(index.dtype == torch.int64),
+                                         _ptr(weights), _ptr(requests), rows, rows_per_bank, width,
+                                         _ptr(out), _ptr(status_word(values.device)), _stream(values.device)))
+    return out
+
+
+def pk_select_read(values, scores, width, rows_per_bank, want_routes=True, index_dtype=torch.int64,
+                   slot_lo=0, slots=None):
+    """Fused route + read. scores [..., 2*half] fp32 -> readings [..., dim] (+ routes)."""
+    require_cuda(values, scores)
+    if scores.dtype != torch.float32:
+        raise ValueError("factor scores must be float32")
+    half = scores.shape[-1] // 2
+    bank = bank_of(values, slot_lo, None, slots)
+    k = routes_out(width, half)
+    rows = scores.numel() // (2 * half)
+    lead = scores.shape[:-1]
+    out = torch.empty((*lead, values.shape[-1]), dtype=torch.float32, device=values.device)
+    index = weights = None
+    if want_routes:
+        index = torch.empty((*lead, k), dtype=index_dtype, device=values.device)
+        weights = torch.empty((*lead, k), dtype=torch.float32, device=values.device)
+    _check(library().glsdm_pk_select_read(ctypes.byref(bank), _ptr(scores), rows, rows_per_bank, half, width,
+                                          _ptr(out), _ptr(index), int(index_dtype == torch.int64),
+                                          _ptr(weights), _ptr(status_word(values.device)),
+                                          _stream(values.device)))
+    return out, index, weights
+
+
+def pk_propose(values, scores, target, beta, log_decay, mass, tokens, width, chunk_offset, chunk_size,
+               num_layers, layer_index, out=None):
+    """Fused write proposal for rows laid out [bank, token, head].
+
+    Returns (addresses [rows*k] int64, deltas [rows*k, dim] fp32, keys [rows*k] int64); ``out`` may
+    supply preallocated views of an epoch-wide buffer.
+    """
+    require_cuda(values, scores, target, beta, log_decay, mass)
+    half = scores.shape[-1] // 2
+    bank = bank_of(values)
+    k = routes_out(width, half)
+    rows = scores.numel() // (2 * half)
+    dim = values.shape[-1]
+    if target.dtype not in (torch.float32, torch.bfloat16) or target.numel() != rows * dim:
+        raise ValueError("target must be [rows, dim] float32 or bfloat16")
+    if beta.dtype != torch.float32 or log_decay.dtype != torch.float32 or beta.numel() != rows or log_decay.numel() != rows:
+        raise ValueError("beta and log_decay must be float32 with one value per row")
+    heads = values.shape[1]
+    if mass is not None and (mass.dtype != torch.float32 or mass.numel() != rows // heads):
+        raise ValueError("mass must be float32 with one value per token")
+    if out is None:
+        addresses = torch.empty(rows * k, dtype=torch.int64, device=values.device)
+        deltas = torch.empty((rows * k, dim), dtype=torch.float32, device=values.device)
+        keys = torch.empty(rows * k, dtype=torch.int64, device=values.device)
+    else:
+        addresses, deltas, keys = out
+        require_cuda(addresses, deltas, keys)
+        if addresses.numel() != rows * k or deltas.numel() != rows * k * dim or keys.numel() != rows * k:
+            raise ValueError("preallocated proposal buffers have the wrong size")
+    rows_per_bank = tokens * heads
+    _check(library().glsdm_pk_propose(ctypes.byref(bank), _ptr(scores), _ptr(target), _dtype_code(target),
+                                      _ptr(beta), _ptr(log_decay), _ptr(mass), rows, rows_per_bank, tokens,
+                                      half, width, chunk_offset, chunk_size, num_layers, layer_index,
+                                      _ptr(addresses), _ptr(deltas), _ptr(keys),
+                                      _ptr(status_word(values.device)), _stream(values.device)))
+    return addresses, deltas, keys
+
+
+def gather_rows(flat, addresses):
+    """flat [rows, dim], addresses [...] int64 -> [..., dim] in the bank dtype."""
+    require_cuda(flat, addresses)
+    if addresses.dtype != torch.int64:
+        raise ValueError("addresses must be int64")
+    rows, dim = flat.shape
+    out = torch.empty((*addresses.shape, dim), dtype=flat.dtype, device=flat.device)
+    _check(library().glsdm_gather_rows(_ptr(flat), _dtype_code(flat), rows, dim, _ptr(addresses),
+                                       addresses.numel(), _ptr(out), _ptr(status_word(flat.device)),
+                                       _stream(flat.device)))
+    return out
+
+
+def token_propose(values, requests, index, weights, target, beta, log_decay, mass):
+    """Token-clock proposal: routes [A, H, K] -> (addresses [A*H*K] int64, deltas [A*H*K, dim])."""
+    require_cuda(values, requests, index, weights, target, beta, log_decay, mass)
+    bank = bank_of(values)
+    width = index.shape[-1]
+    rows = index.numel() // width
+    dim = values.shape[-1]
+    if target.numel() != rows * dim or beta.numel() != rows or log_decay.numel() != rows:
+        raise ValueError("targets, beta and log_decay must have one entry per (request, head)")
+    if requests.numel() * values.shape[1] != rows or mass.numel() != requests.numel():
+        raise ValueError("requests and mass must have one entry per active request")
+    addresses = torch.empty(rows * width, dtype=torch.int64, device=values.device)
+    deltas = torch.empty((rows * width, dim), dtype=torch.float32, device=values.device)
+    _check(library().glsdm_token_propose(ctypes.byref(bank), _ptr(requests), _ptr(index),
+                                         int(index.dtype == torch.int64), _ptr(weights), _ptr(target),
+                                         _ptr(beta), _ptr(log_decay), _ptr(mass), rows, width,
+                                         _ptr(addresses), _ptr(deltas), _ptr(status_word(values.device)),
+                                         _stream(values.device)))
+    return addresses, deltas
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    key = torch.device(device).index
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_base=0):
+    """Apply buffered deltas to a flat bank [rows, dim]; ``out is values`` updates in place.
+
+    Returns the updated bank (a new tensor unless ``out`` is given).
+    """
+    require_cuda(values, addresses, deltas, keys, out)
+    dim = values.shape[-1]
+    flat = values.view(-1, dim)
+    if addresses.dtype != torch.int64 or (keys is not None and keys.dtype != torch.int64):
+        raise ValueError("addresses and sort keys must be int64")
+    if deltas.dtype != torch.float32:
+        raise ValueError("deltas must be float32")
+    entries = addresses.numel()
+    if deltas.numel() != entries * dim or (keys is not None and keys.numel() != entries):
+        raise ValueError("addresses, deltas and keys disagree on the number of entries")
+    if out is None:
+        out = torch.empty_like(values)
+    elif out.shape != values.shape or out.dtype != values.dtype:
+        raise ValueError("output bank must match the input bank")
+    lib = library()
+    nbytes = lib.glsdm_commit_workspace_bytes(entries, dim)
+    work = _workspace(values.device, nbytes)
+    _check(lib.glsdm_commit(_ptr(flat), _ptr(out), _dtype_code(values), row_base, flat.shape[0], dim,
+                            _ptr(addresses), _ptr(deltas), _ptr(keys), entries, key_bits, _ptr(work),
+                            work.numel(), _ptr(status_word(values.device)), _stream(values.device)))
+    return out
+
+
+def topk_merge(cand_score, cand_slot, index_dtype=torch.int64):
+    """cand_* [parts, rows..., k] -> (index [rows..., k] ascending, softmax weights)."""
+    require_cuda(cand_score, cand_slot)
+    if cand_score.dtype != torch.float32 or cand_slot.dtype != torch.int32:
+        raise ValueError("candidates are float32 scores with int32 slots")
+    parts, width = cand_score.shape[0], cand_score.shape[-1]
+    rows = cand_score.numel() // (parts * width)
+    index = torch.empty(cand_score.shape[1:], dtype=index_dtype, device=cand_score.device)
+    weights = torch.empty(cand_score.shape[1:], dtype=torch.float32, device=cand_score.device)
+    _check(library().glsdm_topk_merge(_ptr(cand_score), _ptr(cand_slot), parts, rows, width, _ptr(index),
+                                      int(index_dtype == torch.int64), _ptr(weights),
+                                      _stream(cand_score.device)))
+    return index, weights
+
+
+def score_topk(queries, keys, width, col_base=0):
+    """Dense-key routing of one shard: best `width` (score, slot) per query row, best first."""
+    require_cuda(queries, keys)
+    if queries.dtype != torch.bfloat16 or keys.dtype != torch.bfloat16:
+        raise ValueError("queries and keys must be bfloat16")
+    rows, dk = queries.shape
+    slots = keys.shape[0]
+    lib = library()
+    nbytes = lib.glsdm_score_topk_workspace_bytes(rows, slots, dk, width)
+    work = _workspace(queries.device, nbytes)
+    score = torch.empty((rows, width), dtype=torch.float32, device=queries.device)
+    slot = torch.empty((rows, width), dtype=torch.int32, device=queries.device)
+    _check(lib.glsdm_score_topk(_ptr(queries), _ptr(keys), rows, slots, dk, width, col_base, _ptr(score),
+                                _ptr(slot), _ptr(work), work.numel(), _ptr(status_word(queries.device)),
+                                _stream(queries.device)))
+    return score, slot

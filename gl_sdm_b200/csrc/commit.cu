@@ -1,0 +1,576 @@
+// Buffered commit: stable LSD radix sort of the entries by key, segmented fp32 reduction
+// per address in sorted order, one read-modify-write per touched bank row.
+// Replaces gl_sdm/memory/transactions.py:69-97 and gl_sdm/memory/backends/commit.py:12-58.
+//
+// Phases (all on the caller's stream, no host synchronisation, no float atomics):
+//   1. prepare     keys -> order-preserving u64, entry ids, per-digit histograms (8 x 256)
+//   2. plan        a digit on which every key agrees needs no pass; record source buffers
+//   3. per digit   count (per tile) -> scan -> stable scatter, ping-ponging two buffers
+//   4. gather      sorted address of every position
+//   5. reduce      one warp per 32 sorted positions; each segment head sums its segment
+//                  left to right and updates its bank row; segments longer than
+//                  kLongSegment are queued
+//   6. long        one block per queued segment: fixed 256-entry chunks summed left to
+//                  right by warps, chunk sums added left to right, row updated
+#include "common.cuh"
+
+namespace glsdm {
+namespace {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kDigits = 64 / kRadixBits;
+constexpr int kSortThreads = 256;
+constexpr int kItems = 8;                           // keys per thread in a tile
+constexpr int kTile = kSortThreads * kItems;        // 2048 keys per block
+constexpr int kLongSegment = 256;                   // entries summed strictly in sequence
+constexpr int kScanThreads = 1024;
+
+struct Plan {
+  uint32_t skip[kDigits];    // 1 = all keys share this digit
+  uint32_t source[kDigits];  // buffer (0/1) holding the input of this pass
+  uint32_t final_buffer;     // buffer holding the fully sorted order
+  uint32_t long_count;       // queued long segments
+  uint32_t chunk_cursor;     // partial-sum rows handed out so far
+  uint32_t pad;
+};
+
+struct Workspace {
+  uint64_t* keys[2];
+  uint32_t* ids[2];
+  int64_t* sorted_address;
+  uint32_t* histogram;   // [kDigits][kRadix]
+  uint32_t* tile_count;  // [kRadix][tiles], scanned in place
+  Plan* plan;
+  uint2* long_list;      // (start, length) of queued segments
+  float* partial;        // [partial_rows][dim]
+  int64_t partial_rows;
+  int64_t long_capacity;
+  int tiles;
+};
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t carve(Workspace* w, char* base, int64_t entries, int32_t dim) {
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    char* p = base ? base + at : nullptr;
+    at += align_up(bytes, 256);
+    return p;
+  };
+  const int tiles = static_cast<int>((entries + kTile - 1) / kTile);
+  const int64_t long_capacity = entries / kLongSegment + 1;
+  const int64_t partial_rows = 2 * (entries / kLongSegment) + 2;
+  Workspace local;
+  Workspace* o = w ? w : &local;
+  o->tiles = tiles;
+  o->long_capacity = long_capacity;
+  o->partial_rows = partial_rows;
+  o->keys[0] = reinterpret_cast<uint64_t*>(take(sizeof(uint64_t) * entries));
+  o->keys[1] = reinterpret_cast<uint64_t*>(take(sizeof(uint64_t) * entries));
+  o->ids[0] = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * entries));
+  o->ids[1] = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * entries));
+  o->sorted_address = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
+  o->histogram = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * kDigits * kRadix));
+  o->tile_count = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * kRadix * static_cast<size_t>(tiles)));
+  o->plan = reinterpret_cast<Plan*>(take(sizeof(Plan)));
+  o->long_list = reinterpret_cast<uint2*>(take(sizeof(uint2) * long_capacity));
+  o->partial = reinterpret_cast<float*>(take(sizeof(float) * partial_rows * dim));
+  return at;
+}
+
+__device__ __forceinline__ uint32_t digit_of(uint64_t key, int pass) {
+  return static_cast<uint32_t>(key >> (pass * kRadixBits)) & (kRadix - 1);
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes,
+               uint64_t* __restrict__ out_keys, uint32_t* __restrict__ out_ids,
+               uint32_t* __restrict__ histogram) {
+  __shared__ uint32_t local[kDigits][kRadix];
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += kSortThreads) (&local[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+  for (int r = 0; r < kItems; ++r) {
+    const int64_t i = base + r * kSortThreads + threadIdx.x;
+    if (i < entries) {
+      const uint64_t k = static_cast<uint64_t>(keys[i]) ^ 0x8000000000000000ull;
+      out_keys[i] = k;
+      out_ids[i] = static_cast<uint32_t>(i);
+      for (int p = 0; p < passes; ++p) atomicAdd(&local[p][digit_of(k, p)], 1u);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) {
+    const uint32_t c = (&local[0][0])[i];
+    if (c) atomicAdd(histogram + i, c);
+  }
+}
+
+__global__ void plan_kernel(const uint32_t* __restrict__ histogram, int64_t entries, int passes,
+                            Plan* plan) {
+  __shared__ uint32_t uniform[kDigits];
+  if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
+    if (histogram[i] == static_cast<uint32_t>(entries)) uniform[i / kRadix] = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t buffer = 0;
+    for (int p = 0; p < kDigits; ++p) {
+      const uint32_t skip = (p >= passes) ? 1u : uniform[p];
+      plan->skip[p] = skip;
+      plan->source[p] = buffer;
+      if (!skip) buffer ^= 1u;
+    }
+    plan->final_buffer = buffer;
+    plan->long_count = 0;
+    plan->chunk_cursor = 0;
+  }
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+count_kernel(Workspace w, int64_t entries, int pass) {
+  if (w.plan->skip[pass]) return;
+  __shared__ uint32_t local[kRadix];
+  local[threadIdx.x] = 0;
+  __syncthreads();
+  const uint64_t* __restrict__ keys = w.keys[w.plan->source[pass]];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+  for (int r = 0; r < kItems; ++r) {
+    const int64_t i = base + r * kSortThreads + threadIdx.x;
+    if (i < entries) atomicAdd(&local[digit_of(keys[i], pass)], 1u);
+  }
+  __syncthreads();
+  w.tile_count[static_cast<size_t>(threadIdx.x) * w.tiles + blockIdx.x] = local[threadIdx.x];
+}
+
+// Exclusive scan of tile_count ([digit][tile] flattened) by a single block.
+__global__ void __launch_bounds__(kScanThreads)
+scan_kernel(Workspace w, int pass) {
+  if (w.plan->skip[pass]) return;
+  __shared__ uint32_t sums[kScanThreads];
+  const int64_t n = static_cast<int64_t>(kRadix) * w.tiles;
+  const int64_t per = (n + kScanThreads - 1) / kScanThreads;
+  const int64_t lo = per * threadIdx.x;
+  const int64_t hi = (lo + per < n) ? lo + per : n;
+  uint32_t total = 0;
+  for (int64_t i = lo; i < hi; ++i) total += w.tile_count[i];
+  sums[threadIdx.x] = total;
+  __syncthreads();
+  for (int off = 1; off < kScanThreads; off <<= 1) {
+    const uint32_t add = (threadIdx.x >= off) ? sums[threadIdx.x - off] : 0u;
+    __syncthreads();
+    sums[threadIdx.x] += add;
+    __syncthreads();
+  }
+  uint32_t run = sums[threadIdx.x] - total;
+  for (int64_t i = lo; i < hi; ++i) {
+    const uint32_t c = w.tile_count[i];
+    w.tile_count[i] = run;
+    run += c;
+  }
+}
+
+// Stable scatter of one tile. A warp owns 256 consecutive keys and takes them 32 at a time,
+// so (warp, round, lane) order is input order; ranks inside a round come from match_any.
+__global__ void __launch_bounds__(kSortThreads)
+scatter_kernel(Workspace w, int64_t entries, int pass) {
+  if (w.plan->skip[pass]) return;
+  constexpr int kWarps = kSortThreads / 32;
+  __shared__ uint32_t warp_count[kWarps][kRadix];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kWarps * kRadix; i += kSortThreads) (&warp_count[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t src = w.plan->source[pass];
+  const uint64_t* __restrict__ keys = w.keys[src];
+  const uint32_t* __restrict__ ids = w.ids[src];
+  uint64_t* __restrict__ out_keys = w.keys[src ^ 1u];
+  uint32_t* __restrict__ out_ids = w.ids[src ^ 1u];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItems * 32);
+  uint64_t key[kItems];
+  uint32_t id[kItems];
+  uint32_t rank[kItems];
+#pragma unroll
+  for (int r = 0; r < kItems; ++r) {
+    const int64_t i = base + r * 32 + lane;
+    const bool live = i < entries;
+    key[r] = live ? keys[i] : 0;
+    id[r] = live ? ids[i] : 0;
+    const uint32_t d = live ? digit_of(key[r], pass) : kRadix;  // dead lanes match only each other
+    const unsigned peers = __match_any_sync(kFullMask, d);
+    const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+    uint32_t prior = 0;
+    if (live) prior = warp_count[warp][d];
+    __syncwarp();
+    if (live && before == 0) warp_count[warp][d] = prior + __popc(peers);
+    __syncwarp();
+    rank[r] = prior + before;
+  }
+  __syncthreads();
+  {
+    const int d = threadIdx.x;  // kSortThreads == kRadix
+    uint32_t run = w.tile_count[static_cast<size_t>(d) * w.tiles + blockIdx.x];
+    for (int q = 0; q < kWarps; ++q) {
+      const uint32_t c = warp_count[q][d];
+      warp_count[q][d] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < kItems; ++r) {
+    const int64_t i = base + r * 32 + lane;
+    if (i < entries) {
+      const uint32_t at = warp_count[warp][digit_of(key[r], pass)] + rank[r];
+      out_keys[at] = key[r];
+      out_ids[at] = id[r];
+    }
+  }
+}
+
+__global__ void gather_address_kernel(Workspace w, const int64_t* __restrict__ addresses,
+                                      int64_t entries) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= entries) return;
+  const uint32_t* __restrict__ ids = w.ids[w.plan->final_buffer];
+  w.sorted_address[i] = addresses[ids[i]];
+}
+
+// Per-lane slice of a dim-wide fp32 row: lanes own column blocks of 32*V floats.
+template <int V>
+struct Slice {
+  float v[V];
+};
+
+template <int V>
+__device__ __forceinline__ void zero(Slice<V>& s) {
+#pragma unroll
+  for (int i = 0; i < V; ++i) s.v[i] = 0.f;
+}
+
+// Column layout per lane for V in {1,2,4,8}: V<=4 -> V consecutive floats at lane*V;
+// V==8 -> two float4 at lane*4 and 128+lane*4 (keeps every warp load contiguous).
+template <int V>
+__device__ __forceinline__ void load_delta(Slice<V>& s, const float* __restrict__ row, int lane) {
+  if constexpr (V == 1) {
+    s.v[0] = __ldg(row + lane);
+  } else if constexpr (V == 2) {
+    const float2 t = __ldg(reinterpret_cast<const float2*>(row) + lane);
+    s.v[0] = t.x; s.v[1] = t.y;
+  } else if constexpr (V == 4) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(row) + lane);
+    s.v[0] = t.x; s.v[1] = t.y; s.v[2] = t.z; s.v[3] = t.w;
+  } else {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(row) + lane);
+    const float4 b = __ldg(reinterpret_cast<const float4*>(row) + 32 + lane);
+    s.v[0] = a.x; s.v[1] = a.y; s.v[2] = a.z; s.v[3] = a.w;
+    s.v[4] = b.x; s.v[5] = b.y; s.v[6] = b.z; s.v[7] = b.w;
+  }
+}
+
+template <int V>
+__device__ __forceinline__ int column_of(int lane, int i) {
+  if constexpr (V == 8) return (i < 4) ? lane * 4 + i : 128 + lane * 4 + (i - 4);
+  return lane * V + i;
+}
+
+template <int V>
+__device__ __forceinline__ void add(Slice<V>& acc, const Slice<V>& x) {
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc.v[i] = __fadd_rn(acc.v[i], x.v[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_value(const T* p);
+template <>
+__device__ __forceinline__ float load_value<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_value<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+template <typename T>
+__device__ __forceinline__ void store_value(T* p, float v);
+template <>
+__device__ __forceinline__ void store_value<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+// new_row = old_row + acc (one rounding to the bank dtype), for this lane's columns.
+template <typename T, int V>
+__device__ __forceinline__ void apply_row(const T* in_row, T* out_row,
+                                          const Slice<V>& acc, int lane) {
+  if constexpr (sizeof(T) == 4 && V == 4) {
+    const float4 o = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in_row) + lane * 4);
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + lane * 4) =
+        make_float4(__fadd_rn(o.x, acc.v[0]), __fadd_rn(o.y, acc.v[1]), __fadd_rn(o.z, acc.v[2]),
+                    __fadd_rn(o.w, acc.v[3]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = column_of<V>(lane, i);
+      store_value<T>(out_row + c, __fadd_rn(load_value<T>(in_row + c), acc.v[i]));
+    }
+  }
+}
+
+// Sum entries [start, start+count) of the sorted order, strictly left to right.
+template <int V>
+__device__ __forceinline__ void sum_run(Slice<V>& acc, const uint32_t* __restrict__ ids,
+                                        const float* __restrict__ deltas, int dim, int64_t start,
+                                        int64_t count, int lane) {
+  for (int64_t done = 0; done < count; done += 32) {
+    const int n = (count - done < 32) ? static_cast<int>(count - done) : 32;
+    const uint32_t mine = (lane < n) ? ids[start + done + lane] : 0u;
+    int t = 0;
+    for (; t + 4 <= n; t += 4) {
+      Slice<V> x[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t e = __shfl_sync(kFullMask, mine, t + j);
+        load_delta<V>(x[j], deltas + static_cast<int64_t>(e) * dim, lane);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) add<V>(acc, x[j]);
+    }
+    for (; t < n; ++t) {
+      Slice<V> x;
+      const uint32_t e = __shfl_sync(kFullMask, mine, t);
+      load_delta<V>(x, deltas + static_cast<int64_t>(e) * dim, lane);
+      add<V>(acc, x);
+    }
+  }
+}
+
+// Generic-width variant: any dim, lanes stride the columns, 8 column blocks per sweep.
+__device__ __forceinline__ void sum_run_generic(float (&acc)[8], const uint32_t* __restrict__ ids,
+                                                const float* __restrict__ deltas, int dim, int c0,
+                                                int64_t start, int64_t count, int lane) {
+  for (int64_t t = 0; t < count; ++t) {
+    const float* row = deltas + static_cast<int64_t>(ids[start + t]) * dim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j * 32 + lane;
+      if (c < dim) acc[j] = __fadd_rn(acc[j], __ldg(row + c));
+    }
+  }
+}
+
+struct ReduceArgs {
+  const void* values_in;
+  void* values_out;
+  const float* deltas;
+  int64_t entries;
+  int64_t row_base;
+  int64_t bank_rows;
+  int dim;
+  uint32_t* device_status;
+};
+
+// Length of the segment starting at sorted position `start` (address `a`).
+__device__ __forceinline__ int64_t segment_length(const int64_t* __restrict__ sorted, int64_t start,
+                                                  int64_t entries, int64_t a, int lane) {
+  int64_t len = 1;
+  for (;;) {
+    const int64_t at = start + len + lane;
+    const bool same = at < entries && sorted[at] == a;
+    const unsigned m = __ballot_sync(kFullMask, same);
+    if (m == kFullMask) { len += 32; continue; }
+    len += __ffs(~m) - 1;
+    return len;
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+reduce_kernel(Workspace w, ReduceArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp) * 32;
+  if (first >= a.entries) return;
+  const int64_t* __restrict__ sorted = w.sorted_address;
+  const uint32_t* __restrict__ ids = w.ids[w.plan->final_buffer];
+  const int64_t at = first + lane;
+  const int64_t mine = at < a.entries ? sorted[at] : -1;
+  const int64_t prev = (at > 0 && at < a.entries) ? sorted[at - 1] : -2;
+  unsigned heads = __ballot_sync(kFullMask, at < a.entries && (at == 0 || mine != prev));
+  while (heads) {
+    const int h = __ffs(heads) - 1;
+    heads &= heads - 1;
+    const int64_t start = first + h;
+    const int64_t address = __shfl_sync(kFullMask, mine, h);
+    const int64_t local = address - a.row_base;
+    if (local < 0 || local >= a.bank_rows) {
+      if (lane == 0 && a.device_status) atomicOr(a.device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+      continue;
+    }
+    const int64_t len = segment_length(sorted, start, a.entries, address, lane);
+    if (len > kLongSegment) {
+      if (lane == 0) {
+        const uint32_t slot = atomicAdd(&w.plan->long_count, 1u);
+        w.long_list[slot] = make_uint2(static_cast<uint32_t>(start), static_cast<uint32_t>(len));
+      }
+      continue;
+    }
+    const T* in_row = static_cast<const T*>(a.values_in) + local * a.dim;
+    T* out_row = static_cast<T*>(a.values_out) + local * a.dim;
+    if constexpr (V > 0) {
+      Slice<V> acc;
+      zero<V>(acc);
+      sum_run<V>(acc, ids, a.deltas, a.dim, start, len, lane);
+      apply_row<T, V>(in_row, out_row, acc, lane);
+    } else {
+      for (int c0 = 0; c0 < a.dim; c0 += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        sum_run_generic(acc, ids, a.deltas, a.dim, c0, start, len, lane);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (c < a.dim) store_value<T>(out_row + c, __fadd_rn(load_value<T>(in_row + c), acc[j]));
+        }
+      }
+    }
+  }
+}
+
+// One block per queued long segment. Chunk c covers entries [c*256, c*256+256) of the
+// segment; warp (c % warps) sums it in order and stores the partial; warp 0 then adds the
+// partials in chunk order. The grouping depends only on the segment's length.
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+long_segment_kernel(Workspace w, ReduceArgs a) {
+  __shared__ uint32_t partial_base;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t* __restrict__ ids = w.ids[w.plan->final_buffer];
+  const uint32_t count = w.plan->long_count;
+  for (uint32_t s = blockIdx.x; s < count; s += gridDim.x) {
+    const uint2 seg = w.long_list[s];
+    const int64_t start = seg.x, len = seg.y;
+    const int chunks = static_cast<int>((len + kLongSegment - 1) / kLongSegment);
+    __syncthreads();
+    if (threadIdx.x == 0) partial_base = atomicAdd(&w.plan->chunk_cursor, static_cast<uint32_t>(chunks));
+    __syncthreads();
+    float* __restrict__ partial = w.partial + static_cast<int64_t>(partial_base) * a.dim;
+    const int64_t local = w.sorted_address[start] - a.row_base;
+    const T* in_row = static_cast<const T*>(a.values_in) + local * a.dim;
+    T* out_row = static_cast<T*>(a.values_out) + local * a.dim;
+    for (int c = warp; c < chunks; c += kWarpsPerBlock) {
+      const int64_t cs = start + static_cast<int64_t>(c) * kLongSegment;
+      const int64_t cn = (len - static_cast<int64_t>(c) * kLongSegment < kLongSegment)
+                             ? len - static_cast<int64_t>(c) * kLongSegment : kLongSegment;
+      float* prow = partial + static_cast<int64_t>(c) * a.dim;
+      if constexpr (V > 0) {
+        Slice<V> acc;
+        zero<V>(acc);
+        sum_run<V>(acc, ids, a.deltas, a.dim, cs, cn, lane);
+#pragma unroll
+        for (int i = 0; i < V; ++i) prow[column_of<V>(lane, i)] = acc.v[i];
+      } else {
+        for (int c0 = 0; c0 < a.dim; c0 += 256) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          sum_run_generic(acc, ids, a.deltas, a.dim, c0, cs, cn, lane);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int col = c0 + j * 32 + lane;
+            if (col < a.dim) prow[col] = acc[j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // Columns are spread over the whole block for the in-order sum of the chunk partials.
+    for (int col = threadIdx.x; col < a.dim; col += blockDim.x) {
+      float total = 0.f;
+      for (int c = 0; c < chunks; ++c) total = __fadd_rn(total, partial[static_cast<int64_t>(c) * a.dim + col]);
+      store_value<T>(out_row + col, __fadd_rn(load_value<T>(in_row + col), total));
+    }
+  }
+}
+
+template <typename T>
+int launch_reduce(const Workspace& w, const ReduceArgs& a, glsdm_stream_t stream) {
+  const int grid = blocks_for((a.entries + 31) / 32, kWarpsPerBlock);
+  const int long_grid = static_cast<int>(w.long_capacity < 1184 ? w.long_capacity : 1184);
+  const bool aligned = (reinterpret_cast<uintptr_t>(a.deltas) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.values_in) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.values_out) & 15u) == 0;
+#define GLSDM_REDUCE(V)                                                                     \
+  do {                                                                                      \
+    reduce_kernel<T, V><<<grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);                    \
+    GLSDM_CUDA_OK(cudaGetLastError(), "commit reduce launch");                              \
+    long_segment_kernel<T, V><<<long_grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);         \
+    GLSDM_CUDA_OK(cudaGetLastError(), "commit long-segment launch");                        \
+  } while (0)
+  if (aligned && a.dim == 32) GLSDM_REDUCE(1);
+  else if (aligned && a.dim == 64) GLSDM_REDUCE(2);
+  else if (aligned && a.dim == 128) GLSDM_REDUCE(4);
+  else if (aligned && a.dim == 256) GLSDM_REDUCE(8);
+  else GLSDM_REDUCE(0);
+#undef GLSDM_REDUCE
+  return GLSDM_OK;
+}
+
+}  // namespace
+}  // namespace glsdm
+
+using namespace glsdm;
+
+extern "C" size_t glsdm_commit_workspace_bytes(int64_t entries, int32_t dim) {
+  if (entries < 0 || dim < 1) return 0;
+  return carve(nullptr, nullptr, entries < 1 ? 1 : entries, dim);
+}
+
+extern "C" int glsdm_commit(const void* values_in, void* values_out, int dtype, int64_t row_base,
+                            int64_t bank_rows, int32_t dim, const int64_t* addresses,
+                            const float* deltas, const int64_t* keys, int64_t entries,
+                            int32_t key_bits, void* workspace, size_t workspace_bytes,
+                            uint32_t* device_status, glsdm_stream_t stream) {
+  if (values_in == nullptr || bank_rows < 1 || dim < 1 || entries < 0) return GLSDM_ERR_ARGUMENT;
+  if (dtype != GLSDM_F32 && dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
+  if (entries > 0xfffffff0ll) return GLSDM_ERR_LIMIT;
+  if (key_bits < 0 || key_bits > 64) return GLSDM_ERR_ARGUMENT;
+  const size_t elem = dtype == GLSDM_F32 ? 4 : 2;
+  if (values_out == nullptr) values_out = const_cast<void*>(values_in);
+  if (values_out != values_in) {
+    GLSDM_CUDA_OK(cudaMemcpyAsync(values_out, values_in, elem * bank_rows * dim,
+                                  cudaMemcpyDeviceToDevice, stream), "commit bank copy");
+  }
+  if (entries == 0) return GLSDM_OK;
+  if (addresses == nullptr || deltas == nullptr || workspace == nullptr) return GLSDM_ERR_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GLSDM_ERR_ARGUMENT;
+  Workspace w;
+  const size_t need = carve(&w, static_cast<char*>(workspace), entries, dim);
+  if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
+  if (keys == nullptr) keys = addresses;
+  // Keys are compared as signed 64-bit integers: the top digit always carries the sign.
+  const int passes = (key_bits == 0 || key_bits == 64) ? kDigits : (key_bits + kRadixBits - 1) / kRadixBits;
+
+  GLSDM_CUDA_OK(cudaMemsetAsync(w.histogram, 0, sizeof(uint32_t) * kDigits * kRadix, stream),
+                "commit histogram clear");
+  prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, passes, w.keys[0], w.ids[0],
+                                                       w.histogram);
+  GLSDM_CUDA_OK(cudaGetLastError(), "commit prepare launch");
+  plan_kernel<<<1, 256, 0, stream>>>(w.histogram, entries, passes, w.plan);
+  GLSDM_CUDA_OK(cudaGetLastError(), "commit plan launch");
+  for (int p = 0; p < passes; ++p) {
+    count_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
+    scan_kernel<<<1, kScanThreads, 0, stream>>>(w, p);
+    scatter_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
+    GLSDM_CUDA_OK(cudaGetLastError(), "commit sort launch");
+  }
+  gather_address_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, addresses, entries);
+  GLSDM_CUDA_OK(cudaGetLastError(), "commit gather launch");
+
+  ReduceArgs a;
+  a.values_in = values_in;
+  a.values_out = values_out;
+  a.deltas = deltas;
+  a.entries = entries;
+  a.row_base = row_base;
+  a.bank_rows = bank_rows;
+  a.dim = dim;
+  a.device_status = device_status;
+  if (dtype == GLSDM_F32) return launch_reduce<float>(w, a, stream);
+  return launch_reduce<__nv_bfloat16>(w, a, stream);
+}

@@ -1,0 +1,58 @@
+// Merge of per-shard route candidates into the global routes of a slot-sharded bank.
+// Every rank runs this on the same all-gathered candidate lists, so every rank derives the
+// same routes. Tie rule and softmax: gl_sdm/memory/routing.py:21-26.
+#include "common.cuh"
+
+namespace glsdm {
+namespace {
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+topk_merge_kernel(const float* __restrict__ cand_score, const int32_t* __restrict__ cand_slot,
+                  int parts, int64_t rows, int width, void* out_index, int i64,
+                  float* __restrict__ out_weights) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  WarpSelect sel;
+  sel.init(stage[warp], width, lane);
+  for (int p = 0; p < parts; ++p) {
+    const int64_t at = (static_cast<int64_t>(p) * rows + row) * width + lane;
+    uint64_t key = 0;
+    if (lane < width) {
+      const int32_t slot = cand_slot[at];
+      // A shard with fewer than `width` slots pads its list with slot -1.
+      if (slot >= 0) key = pack_key(orderable_bits(cand_score[at]), static_cast<uint32_t>(slot));
+    }
+    sel.offer(key);
+  }
+  sel.finish();
+  uint32_t slot;
+  float weight, score;
+  canonical_routes(sel.list, width, lane, slot, weight, score);
+  if (lane < width) {
+    const int64_t at = row * width + lane;
+    if (i64) static_cast<int64_t*>(out_index)[at] = slot;
+    else static_cast<int32_t*>(out_index)[at] = static_cast<int32_t>(slot);
+    out_weights[at] = weight;
+  }
+}
+
+}  // namespace
+}  // namespace glsdm
+
+using namespace glsdm;
+
+extern "C" int glsdm_topk_merge(const float* cand_score, const int32_t* cand_slot, int32_t parts,
+                                int64_t rows, int32_t width, void* out_index, int index_i64,
+                                float* out_weights, glsdm_stream_t stream) {
+  if (cand_score == nullptr || cand_slot == nullptr || out_index == nullptr || out_weights == nullptr)
+    return GLSDM_ERR_ARGUMENT;
+  if (parts < 1 || rows < 0 || width < 1) return GLSDM_ERR_ARGUMENT;
+  if (width > 32) return GLSDM_ERR_UNSUPPORTED;
+  if (rows == 0) return GLSDM_OK;
+  topk_merge_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+      cand_score, cand_slot, parts, rows, width, out_index, index_i64, out_weights);
+  GLSDM_CUDA_OK(cudaGetLastError(), "topk_merge launch");
+  return GLSDM_OK;
+}

@@ -1,0 +1,457 @@
+// Routing and snapshot-read kernels (one warp per (request, token, head) row) and their
+// C entry points: glsdm_pk_select, glsdm_snapshot_read, glsdm_pk_select_read,
+// glsdm_pk_propose.
+#include "route.cuh"
+
+namespace glsdm {
+namespace {
+
+__device__ __forceinline__ void store_routes(void* out_index, bool i64, float* out_weights,
+                                             int64_t row, int kout, int lane, uint32_t slot,
+                                             float weight) {
+  if (lane >= kout) return;
+  const int64_t at = row * kout + lane;
+  if (out_index != nullptr) {
+    if (i64) {
+      static_cast<int64_t*>(out_index)[at] = static_cast<int64_t>(slot);
+    } else {
+      static_cast<int32_t*>(out_index)[at] = static_cast<int32_t>(slot);
+    }
+  }
+  if (out_weights != nullptr) out_weights[at] = weight;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+pk_select_kernel(const float* __restrict__ scores, int64_t rows, int half, int kf, int kout,
+                 void* out_index, int i64, float* out_weights) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  uint32_t slot;
+  float weight;
+  pk_route_row(scores + row * 2 * half, half, kf, kout, stage[warp], lane, slot, weight);
+  store_routes(out_index, i64 != 0, out_weights, row, kout, lane, slot, weight);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+pk_select_read_kernel(BankView bank, const float* __restrict__ scores, int64_t rows,
+                      int64_t rows_per_bank, int half, int kf, int kout, bool vec,
+                      float* __restrict__ out_read, void* out_index, int i64,
+                      float* out_weights) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  uint32_t slot;
+  float weight;
+  pk_route_row(scores + row * 2 * half, half, kf, kout, stage[warp], lane, slot, weight);
+  store_routes(out_index, i64 != 0, out_weights, row, kout, lane, slot, weight);
+  const int64_t part = partition_of(bank, row, rows_per_bank, nullptr);
+  const T* base = static_cast<const T*>(bank.values) + part * bank.part_stride_rows * bank.dim;
+  read_row<T>(base, bank, slot, weight, kout, lane, vec, out_read + row * bank.dim);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+snapshot_read_kernel(BankView bank, const void* __restrict__ index, int i64,
+                     const float* __restrict__ weights, const int64_t* __restrict__ requests,
+                     int64_t rows, int64_t rows_per_bank, int width, bool vec,
+                     float* __restrict__ out_read, uint32_t* device_status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  uint32_t slot = 0;
+  float weight = 0.f;
+  if (lane < width) {
+    const int64_t at = row * width + lane;
+    const int64_t s = i64 ? static_cast<const int64_t*>(index)[at]
+                          : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
+    weight = weights[at];
+    if (s < 0 || s >= bank.slots) {
+      if (device_status != nullptr) atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+      weight = 0.f;
+    } else {
+      slot = static_cast<uint32_t>(s);
+    }
+  }
+  int64_t part = partition_of(bank, row, rows_per_bank, requests);
+  if (part < 0 || part >= bank.banks * bank.heads) {
+    if (lane == 0 && device_status != nullptr) atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+    part = row % bank.heads;
+    weight = 0.f;
+  }
+  const T* base = static_cast<const T*>(bank.values) + part * bank.part_stride_rows * bank.dim;
+  read_row<T>(base, bank, slot, weight, width, lane, vec, out_read + row * bank.dim);
+}
+
+// Fused write proposal for one row: route, prediction read, then one delta row per route
+//   delta_k = mass * ((decay - 1) * row_k + w_k * beta * (target - decay * prediction))
+// (reference gl_sdm/runtime/dense.py:11-14) plus the flat address and canonical sort key
+// (reference gl_sdm/layers/global_layer.py:45,52-53). The selected rows are read twice; the
+// second read of the same 16-byte units by the same lanes is served from L1/L2.
+template <typename T, typename TT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+pk_propose_kernel(BankView bank, const float* __restrict__ scores, const TT* __restrict__ target,
+                  const float* __restrict__ beta, const float* __restrict__ log_decay,
+                  const float* __restrict__ mass, int64_t rows, int64_t rows_per_bank,
+                  int64_t tokens, int half, int kf, int kout, bool vec, int64_t chunk_offset,
+                  int64_t key_stride, int num_layers, int layer_index,
+                  int64_t* __restrict__ out_addresses, float* __restrict__ out_deltas,
+                  int64_t* __restrict__ out_keys) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  constexpr int E = Unit<T>::kElems;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  uint32_t slot;
+  float weight;
+  pk_route_row(scores + row * 2 * half, half, kf, kout, stage[warp], lane, slot, weight);
+
+  const int dim = bank.dim;
+  const int64_t part = partition_of(bank, row, rows_per_bank, nullptr);
+  const T* base = static_cast<const T*>(bank.values) + part * bank.part_stride_rows * dim;
+  const int64_t token = row / bank.heads;
+  const float decay = expf(log_decay[row]);
+  const float gate = beta[row];
+  const float m = mass != nullptr ? mass[token] : 1.0f;
+  const float decay_m1 = __fadd_rn(decay, -1.0f);
+  float* __restrict__ drows = out_deltas + row * kout * dim;
+  const TT* __restrict__ trow = target + row * dim;
+
+  if (lane < kout) {
+    const int64_t address = part * bank.slots + slot;
+    const int64_t position = chunk_offset + token % tokens;
+    out_addresses[row * kout + lane] = address;
+    out_keys[row * kout + lane] = address * key_stride + position * num_layers + layer_index;
+  }
+
+  if (vec) {
+    const int units = dim / E;
+    const int passes = units <= 32 ? 1 : units / 32;
+    const int here = units < 32 ? units : 32;
+    const int groups = 32 / here;
+    const int g = lane / here;
+    const uint4* __restrict__ rows4 = reinterpret_cast<const uint4*>(base);
+    for (int ub = 0; ub < passes; ++ub) {
+      float pred[E];
+      gather_units<T>(base, bank, slot, weight, kout, lane, units, ub, pred);
+      const int u = ub * 32 + (lane % here);
+      float err[E];
+#pragma unroll
+      for (int i = 0; i < E; ++i) {
+        const float t = Unit<TT>::scalar(trow + u * E + i);
+        err[i] = __fmul_rn(gate, __fadd_rn(t, -__fmul_rn(decay, pred[i])));
+      }
+      for (int k0 = 0; k0 < kout; k0 += groups) {
+        const int k = k0 + g;
+        const uint32_t a = __shfl_sync(kFullMask, slot, k & 31);
+        const float w = __shfl_sync(kFullMask, weight, k & 31);
+        if (k < kout) {
+          float v[E];
+          const int64_t local = static_cast<int64_t>(a) - bank.slot_lo;
+          const bool owned = local >= 0 && local < bank.part_stride_rows;
+          uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+          if (owned) raw = __ldg(rows4 + local * units + u);
+          Unit<T>::decode(raw, v);
+          float d[E];
+#pragma unroll
+          for (int i = 0; i < E; ++i)
+            d[i] = __fmul_rn(m, __fadd_rn(__fmul_rn(decay_m1, v[i]), __fmul_rn(w, err[i])));
+          float4* dst = reinterpret_cast<float4*>(drows + static_cast<int64_t>(k) * dim + u * E);
+          dst[0] = make_float4(d[0], d[1], d[2], d[3]);
+          if constexpr (E == 8) dst[1] = make_float4(d[4], d[5], d[6], d[7]);
+        }
+      }
+    }
+  } else {
+    for (int d0 = 0; d0 < dim; d0 += 32) {
+      const int d = d0 + lane;
+      float pred = 0.f;
+      for (int k = 0; k < kout; ++k) {
+        const uint32_t a = __shfl_sync(kFullMask, slot, k);
+        const float w = __shfl_sync(kFullMask, weight, k);
+        const int64_t local = static_cast<int64_t>(a) - bank.slot_lo;
+        if (d < dim && local >= 0 && local < bank.part_stride_rows)
+          pred = fmaf(w, Unit<T>::scalar(base + local * dim + d), pred);
+      }
+      const float t = d < dim ? Unit<TT>::scalar(trow + d) : 0.f;
+      const float err = __fmul_rn(gate, __fadd_rn(t, -__fmul_rn(decay, pred)));
+      for (int k = 0; k < kout; ++k) {
+        const uint32_t a = __shfl_sync(kFullMask, slot, k);
+        const float w = __shfl_sync(kFullMask, weight, k);
+        const int64_t local = static_cast<int64_t>(a) - bank.slot_lo;
+        if (d < dim) {
+          const float v = (local >= 0 && local < bank.part_stride_rows)
+                              ? Unit<T>::scalar(base + local * dim + d) : 0.f;
+          drows[static_cast<int64_t>(k) * dim + d] =
+              __fmul_rn(m, __fadd_rn(__fmul_rn(decay_m1, v), __fmul_rn(w, err)));
+        }
+      }
+    }
+  }
+}
+
+// Row copy out[n] = flat[address[n]] (reference gl_sdm/memory/routing.py:37-42 and
+// gl_sdm/memory/backends/primitives.py:14-20). `unit` bytes move per thread.
+template <typename U>
+__global__ void gather_rows_kernel(const U* __restrict__ flat, const int64_t* __restrict__ address,
+                                   int64_t count, int64_t bank_rows, int units,
+                                   U* __restrict__ out, uint32_t* device_status) {
+  const int64_t total = count * units;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i / units;
+    const int u = static_cast<int>(i - n * units);
+    const int64_t a = address[n];
+    if (a < 0 || a >= bank_rows) {
+      if (device_status != nullptr) atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+      continue;
+    }
+    out[i] = flat[a * units + u];
+  }
+}
+
+// Token-clock write proposal (reference gl_sdm/memory/transactions.py:38-59), one warp per
+// (active request, head): rows decay first, the retrieval is the weighted sum of the
+// decayed rows, and each route receives (decayed - row) + w * beta * (target - retrieved),
+// scaled by the request's mass. Operation order follows the reference expression.
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+token_propose_kernel(const T* __restrict__ values, int64_t banks, int heads, int64_t slots, int dim,
+                     const int64_t* __restrict__ requests, const void* __restrict__ index, int i64,
+                     const float* __restrict__ weights, const float* __restrict__ target,
+                     const float* __restrict__ beta, const float* __restrict__ log_decay,
+                     const float* __restrict__ mass, int64_t rows, int width,
+                     int64_t* __restrict__ out_addresses, float* __restrict__ out_deltas,
+                     uint32_t* device_status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  const int64_t active = row / heads;
+  const int head = static_cast<int>(row % heads);
+  const int64_t request = requests[active];
+  const bool request_ok = request >= 0 && request < banks;
+  const int64_t part = (request_ok ? request : 0) * heads + head;
+  const float decay = expf(log_decay[row]);
+  const float gate = beta[row];
+  const float m = mass[active];
+  for (int k = lane; k < width; k += 32) {
+    const int64_t at = row * width + k;
+    const int64_t s = i64 ? static_cast<const int64_t*>(index)[at]
+                          : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
+    out_addresses[at] = part * slots + s;
+    if ((s < 0 || s >= slots || !request_ok) && device_status != nullptr)
+      atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+  }
+  for (int d = lane; d < dim; d += 32) {
+    float retrieved = 0.f;
+    for (int k = 0; k < width; ++k) {
+      const int64_t at = row * width + k;
+      const int64_t s = i64 ? static_cast<const int64_t*>(index)[at]
+                            : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
+      const bool ok = request_ok && s >= 0 && s < slots;
+      const float v = ok ? Unit<T>::scalar(values + (part * slots + s) * dim + d) : 0.f;
+      retrieved = __fadd_rn(retrieved, __fmul_rn(__fmul_rn(v, decay), weights[at]));
+    }
+    const float err = __fmul_rn(gate, __fadd_rn(target[row * dim + d], -retrieved));
+    for (int k = 0; k < width; ++k) {
+      const int64_t at = row * width + k;
+      const int64_t s = i64 ? static_cast<const int64_t*>(index)[at]
+                            : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
+      const bool ok = request_ok && s >= 0 && s < slots;
+      const float v = ok ? Unit<T>::scalar(values + (part * slots + s) * dim + d) : 0.f;
+      const float moved = __fadd_rn(__fmul_rn(v, decay), -v);
+      out_deltas[at * dim + d] = __fmul_rn(__fadd_rn(moved, __fmul_rn(weights[at], err)), m);
+    }
+  }
+}
+
+int route_shape(int32_t half, int32_t width, int* kf, int* kout) {
+  if (half < 1 || width < 1) return GLSDM_ERR_ARGUMENT;
+  if (half > 65536) return GLSDM_ERR_UNSUPPORTED;
+  const int f = width < half ? width : half;
+  if (f > 32) return GLSDM_ERR_UNSUPPORTED;
+  const int64_t cand = static_cast<int64_t>(f) * f;
+  const int o = width < cand ? width : static_cast<int>(cand);
+  if (o > 32) return GLSDM_ERR_UNSUPPORTED;
+  *kf = f;
+  *kout = o;
+  return GLSDM_OK;
+}
+
+}  // namespace
+}  // namespace glsdm
+
+using namespace glsdm;
+
+extern "C" int glsdm_pk_select(const float* scores, int64_t rows, int32_t half, int32_t width,
+                               void* out_index, int index_i64, float* out_weights,
+                               glsdm_stream_t stream) {
+  int kf, kout;
+  if (int s = route_shape(half, width, &kf, &kout)) return s;
+  if (rows < 0 || scores == nullptr) return GLSDM_ERR_ARGUMENT;
+  if ((half & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u)) return GLSDM_ERR_ARGUMENT;
+  if (rows == 0) return GLSDM_OK;
+  pk_select_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+      scores, rows, half, kf, kout, out_index, index_i64, out_weights);
+  GLSDM_CUDA_OK(cudaGetLastError(), "pk_select launch");
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, int index_i64,
+                                   const float* weights, const int64_t* requests, int64_t rows,
+                                   int64_t rows_per_bank, int32_t width, float* out_read,
+                                   uint32_t* device_status, glsdm_stream_t stream) {
+  if (int s = check_bank(bank)) return s;
+  if (index == nullptr || weights == nullptr || out_read == nullptr || rows < 0) return GLSDM_ERR_ARGUMENT;
+  if (width < 1 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (width > 32) return GLSDM_ERR_UNSUPPORTED;
+  if (rows == 0) return GLSDM_OK;
+  const BankView v = make_view(*bank);
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+  if (bank->dtype == GLSDM_F32) {
+    const bool vec = vector_rows<float>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
+    snapshot_read_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status);
+  } else {
+    const bool vec = vector_rows<__nv_bfloat16>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
+    snapshot_read_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status);
+  }
+  GLSDM_CUDA_OK(cudaGetLastError(), "snapshot_read launch");
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_pk_select_read(const glsdm_bank* bank, const float* scores, int64_t rows,
+                                    int64_t rows_per_bank, int32_t half, int32_t width,
+                                    float* out_read, void* out_index, int index_i64,
+                                    float* out_weights, uint32_t* device_status,
+                                    glsdm_stream_t stream) {
+  (void)device_status;
+  if (int s = check_bank(bank)) return s;
+  int kf, kout;
+  if (int s = route_shape(half, width, &kf, &kout)) return s;
+  if (scores == nullptr || out_read == nullptr || rows < 0 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
+  if ((half & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u)) return GLSDM_ERR_ARGUMENT;
+  if (rows == 0) return GLSDM_OK;
+  const BankView v = make_view(*bank);
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+  if (bank->dtype == GLSDM_F32) {
+    const bool vec = vector_rows<float>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
+    pk_select_read_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, scores, rows, rows_per_bank, half, kf, kout, vec, out_read, out_index, index_i64, out_weights);
+  } else {
+    const bool vec = vector_rows<__nv_bfloat16>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
+    pk_select_read_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, scores, rows, rows_per_bank, half, kf, kout, vec, out_read, out_index, index_i64, out_weights);
+  }
+  GLSDM_CUDA_OK(cudaGetLastError(), "pk_select_read launch");
+  return GLSDM_OK;
+}
+
+template <typename T, typename TT>
+static void launch_propose(const BankView& v, const float* scores, const void* target,
+                           const float* beta, const float* log_decay, const float* mass,
+                           int64_t rows, int64_t rows_per_bank, int64_t tokens, int half, int kf,
+                           int kout, int64_t chunk_offset, int64_t chunk_size, int num_layers,
+                           int layer_index, int64_t* out_addresses, float* out_deltas,
+                           int64_t* out_keys, glsdm_stream_t stream) {
+  const bool vec = vector_rows<T>(v.dim, v.values) &&
+                   (reinterpret_cast<uintptr_t>(out_deltas) & 15u) == 0;
+  pk_propose_kernel<T, TT><<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+      v, scores, static_cast<const TT*>(target), beta, log_decay, mass, rows, rows_per_bank, tokens,
+      half, kf, kout, vec, chunk_offset, chunk_size * num_layers, num_layers, layer_index,
+      out_addresses, out_deltas, out_keys);
+}
+
+extern "C" int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, const void* target,
+                                int target_dtype, const float* beta, const float* log_decay,
+                                const float* mass, int64_t rows, int64_t rows_per_bank,
+                                int64_t tokens, int32_t half, int32_t width, int64_t chunk_offset,
+                                int64_t chunk_size, int32_t num_layers, int32_t layer_index,
+                                int64_t* out_addresses, float* out_deltas, int64_t* out_keys,
+                                uint32_t* device_status, glsdm_stream_t stream) {
+  (void)device_status;
+  if (int s = check_bank(bank)) return s;
+  int kf, kout;
+  if (int s = route_shape(half, width, &kf, &kout)) return s;
+  if (scores == nullptr || target == nullptr || beta == nullptr || log_decay == nullptr ||
+      out_addresses == nullptr || out_deltas == nullptr || out_keys == nullptr)
+    return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || rows_per_bank < 1 || tokens < 1 || chunk_size < 1 || num_layers < 1 ||
+      layer_index < 0 || layer_index >= num_layers || chunk_offset < 0)
+    return GLSDM_ERR_ARGUMENT;
+  if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
+  if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
+  if (target_dtype != GLSDM_F32 && target_dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
+  if ((half & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u)) return GLSDM_ERR_ARGUMENT;
+  if (rows == 0) return GLSDM_OK;
+  const BankView v = make_view(*bank);
+#define GLSDM_PROPOSE(T, TT)                                                                   \
+  launch_propose<T, TT>(v, scores, target, beta, log_decay, mass, rows, rows_per_bank, tokens, \
+                        half, kf, kout, chunk_offset, chunk_size, num_layers, layer_index,     \
+                        out_addresses, out_deltas, out_keys, stream)
+  if (bank->dtype == GLSDM_F32) {
+    if (target_dtype == GLSDM_F32) GLSDM_PROPOSE(float, float);
+    else GLSDM_PROPOSE(float, __nv_bfloat16);
+  } else {
+    if (target_dtype == GLSDM_F32) GLSDM_PROPOSE(__nv_bfloat16, float);
+    else GLSDM_PROPOSE(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef GLSDM_PROPOSE
+  GLSDM_CUDA_OK(cudaGetLastError(), "pk_propose launch");
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_gather_rows(const void* flat, int dtype, int64_t bank_rows, int32_t dim,
+                                 const int64_t* addresses, int64_t count, void* out,
+                                 uint32_t* device_status, glsdm_stream_t stream) {
+  if (flat == nullptr || addresses == nullptr || out == nullptr) return GLSDM_ERR_ARGUMENT;
+  if (bank_rows < 1 || dim < 1 || count < 0) return GLSDM_ERR_ARGUMENT;
+  if (dtype != GLSDM_F32 && dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
+  if (count == 0) return GLSDM_OK;
+  const int64_t row_bytes = static_cast<int64_t>(dim) * (dtype == GLSDM_F32 ? 4 : 2);
+  const bool wide = row_bytes % 16 == 0 && ((reinterpret_cast<uintptr_t>(flat) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+  const int64_t unit = wide ? 16 : (dtype == GLSDM_F32 ? 4 : 2);
+  const int units = static_cast<int>(row_bytes / unit);
+  const int64_t total = count * units;
+  const int grid = static_cast<int>(total / 256 + 1 < 148 * 32 ? total / 256 + 1 : 148 * 32);
+  if (unit == 16)
+    gather_rows_kernel<uint4><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(flat), addresses, count, bank_rows, units, static_cast<uint4*>(out), device_status);
+  else if (unit == 4)
+    gather_rows_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(flat), addresses, count, bank_rows, units, static_cast<uint32_t*>(out), device_status);
+  else
+    gather_rows_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(flat), addresses, count, bank_rows, units, static_cast<uint16_t*>(out), device_status);
+  GLSDM_CUDA_OK(cudaGetLastError(), "gather_rows launch");
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_token_propose(const glsdm_bank* bank, const int64_t* requests, const void* index,
+                                   int index_i64, const float* weights, const float* target,
+                                   const float* beta, const float* log_decay, const float* mass,
+                                   int64_t rows, int32_t width, int64_t* out_addresses,
+                                   float* out_deltas, uint32_t* device_status,
+                                   glsdm_stream_t stream) {
+  if (int s = check_bank(bank)) return s;
+  if (requests == nullptr || index == nullptr || weights == nullptr || target == nullptr ||
+      beta == nullptr || log_decay == nullptr || mass == nullptr || out_addresses == nullptr ||
+      out_deltas == nullptr)
+    return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || width < 1) return GLSDM_ERR_ARGUMENT;
+  if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
+  if (rows == 0) return GLSDM_OK;
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+  if (bank->dtype == GLSDM_F32)
+    token_propose_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const float*>(bank->values), bank->banks, bank->heads, bank->slots, bank->dim, requests,
+        index, index_i64, weights, target, beta, log_decay, mass, rows, width, out_addresses, out_deltas, device_status);
+  else
+    token_propose_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(bank->values), bank->banks, bank->heads, bank->slots, bank->dim, requests,
+        index, index_i64, weights, target, beta, log_decay, mass, rows, width, out_addresses, out_deltas, device_status);
+  GLSDM_CUDA_OK(cudaGetLastError(), "token_propose launch");
+  return GLSDM_OK;
+}

@@ -1,0 +1,40 @@
+"""Register this package under the reference's module names.
+
+``gl_sdm/layers/stack.py``, ``global_layer.py``, ``router.py`` and ``model.py`` import
+``gl_sdm.memory`` lazily (model.py:33-34,58), so installing substitutes in ``sys.modules``
+before the model is created makes the unmodified reference stack run on these kernels.
+"""
+import sys
+
+from . import memory
+from .memory import state, transactions, routing, backends
+from .memory.backends import urm, commit, primitives
+
+_NAMES = {
+    "gl_sdm.memory": memory,
+    "gl_sdm.memory.state": state,
+    "gl_sdm.memory.transactions": transactions,
+    "gl_sdm.memory.routing": routing,
+    "gl_sdm.memory.backends": backends,
+    "gl_sdm.memory.backends.urm": urm,
+    "gl_sdm.memory.backends.commit": commit,
+    "gl_sdm.memory.backends.primitives": primitives,
+}
+
+
+def install():
+    """Make ``import gl_sdm.memory`` resolve to gl_sdm_b200.memory. Returns the replaced modules."""
+    previous = {name: sys.modules.get(name) for name in _NAMES}
+    sys.modules.update(_NAMES)
+    parent = sys.modules.get("gl_sdm")
+    if parent is not None:
+        parent.memory = memory
+    return previous
+
+
+def uninstall(previous):
+    for name, module in previous.items():
+        if module is None:
+            sys.modules.pop(name, None)
+        else:
+            sys.modules[name] = module

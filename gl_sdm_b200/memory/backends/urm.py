@@ -1,0 +1,28 @@
+"""The three names the reference calls on its external-read backend
+(gl_sdm/memory/backends/urm.py:40-46,49-82,109-122), served by the in-tree kernels."""
+from ... import _native
+
+
+def verify_dependency():
+    """The reference pins an external package here; this build needs only its own library."""
+    lib = _native.library()
+    return {"repository": "in-tree", "revision": f"glsdm-abi-{lib.glsdm_abi_version()}"}
+
+
+def snapshot_read(values, addresses, weights):
+    """Supplied-route read; addresses are flat rows of values.view(1, 1, -1, dim)."""
+    dim = values.shape[-1]
+    flat = values.reshape(1, 1, -1, dim)
+    lead = weights.shape[:-1]
+    rows = weights.numel() // weights.shape[-1]
+    out = _native.snapshot_read(flat, addresses.reshape(rows, -1).contiguous(),
+                                weights.reshape(rows, -1).float().contiguous(), rows_per_bank=rows)
+    return out.view(*lead, dim)
+
+
+def routed_snapshot_read(values, scores, width, allow_large_route=False):
+    """Fused route + read; int32 indices as the reference's native path returns them."""
+    import torch
+    B, T, H, _ = scores.shape
+    return _native.pk_select_read(values, scores.float().contiguous(), width, rows_per_bank=T * H,
+                                  index_dtype=torch.int32)

@@ -1,0 +1,107 @@
+"""Token-clock reads/proposals and the buffered commit, on the CUDA kernels.
+
+Interface, validation order and error text follow the reference
+(gl_sdm/memory/transactions.py:13-97). ``backend`` is accepted for call compatibility
+("torch" or "urm") but selects nothing: every call runs the sm_100a kernels, and tensors
+that are not on a CUDA device raise. ``reference=True`` asks for an oracle that only a test
+harness provides (see oracle_hook).
+"""
+import torch
+
+from .. import _native
+from . import oracle_hook
+from .state import MemoryView, WriteProposal, WriteBuffer
+
+_BACKENDS = {"torch", "urm"}
+
+
+def _check_backend(backend):
+    if backend not in _BACKENDS:
+        raise ValueError("memory backend must be torch or urm")
+
+
+def _forward_only(*tensors):
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise NotImplementedError(
+            "the B200 memory operator is forward-only: run under torch.no_grad() / inference_mode()")
+
+
+def addresses(view, requests, indices):
+    """Flat bank row of every selected slot: (request*heads + head)*slots + slot."""
+    heads, slots = view.values.shape[1:3]
+    head = torch.arange(heads, device=indices.device).view(1, heads, 1)
+    return (requests.view(-1, 1, 1) * heads + head) * slots + indices
+
+
+def selected(view, requests, indices, reference=False):
+    """Rows [A, H, K, D] of the selected slots (reference transactions.py:19-25)."""
+    if reference:
+        return oracle_hook.get("selected")(view, requests, indices)
+    _native.require_cuda(view.values)
+    return _native.gather_rows(view.values.flatten(0, 2), addresses(view, requests, indices).contiguous())
+
+
+def read(view, requests, indices, weights, reference=False, backend="torch"):
+    """Weighted read of supplied routes: [A, H, K] routes -> [A, H, D]."""
+    _check_backend(backend)
+    if reference:
+        return oracle_hook.get("read")(view, requests, indices, weights)
+    _forward_only(view.values, weights)
+    heads = view.values.shape[1]
+    return _native.snapshot_read(view.values, indices.contiguous(), weights.float().contiguous(),
+                                 rows_per_bank=heads, requests=requests.long().contiguous())
+
+
+def propose_write(view, requests, indices, weights, targets, beta, log_decay,
+                  mass, reference=False, backend="torch"):
+    """One delta update against the immutable snapshot (reference transactions.py:38-59).
+
+    delta_k = mass * (decay*row_k - row_k + w_k * beta * (target - sum_j w_j*decay*row_j)).
+    """
+    _check_backend(backend)
+    if reference:
+        return oracle_hook.get("propose_write")(view, requests, indices, weights, targets, beta, log_decay, mass)
+    _forward_only(view.values, weights, targets, beta, log_decay, mass)
+    flat_addresses, deltas = _native.token_propose(
+        view.values, requests.long().contiguous(), indices.contiguous(), weights.float().contiguous(),
+        targets.float().contiguous(), beta.float().contiguous(), log_decay.float().contiguous(),
+        mass.float().contiguous())
+    return WriteProposal(view.version, flat_addresses, deltas, view.lineage)
+
+
+def merge(view, proposals):
+    proposals = tuple(proposals)
+    stale = any(p.base_version != view.version or p.lineage is not view.lineage for p in proposals)
+    if not proposals or stale:
+        raise ValueError("write buffers must be nonempty and use the same snapshot version")
+    return WriteBuffer(view.version, proposals, view.lineage)
+
+
+def _concat(tensors):
+    return tensors[0] if len(tensors) == 1 else torch.cat(tensors)
+
+
+def commit(view, buffer, reference=False, backend="torch", donate=False, key_bits=0):
+    """Apply a write buffer: stable sort by key, per-address fp32 sums, one write per row.
+
+    Returns a new view (version + 1, same lineage); the input view's tensor is left
+    bit-for-bit unchanged unless ``donate=True``, which updates it in place and hands the
+    same storage to the new view (extension for banks too large to copy per commit; the
+    old view must not be read afterwards). ``key_bits`` optionally bounds the sort keys.
+    """
+    _check_backend(backend)
+    if buffer.base_version != view.version or buffer.lineage is not view.lineage:
+        raise ValueError("stale memory transaction")
+    keyed = [p.sort_keys is not None for p in buffer.proposals]
+    if any(keyed) and not all(keyed):
+        raise ValueError("cannot mix keyed and unkeyed proposals")
+    if reference:
+        return oracle_hook.get("commit")(view, buffer)
+    values = view.values
+    _native.require_cuda(values)
+    _forward_only(values, *(p.deltas for p in buffer.proposals))
+    idx = _concat([p.addresses.reshape(-1) for p in buffer.proposals]).long().contiguous()
+    delta = _concat([p.deltas for p in buffer.proposals]).float().contiguous()
+    keys = _concat([p.sort_keys.reshape(-1) for p in buffer.proposals]).long().contiguous() if all(keyed) else None
+    updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
+    return MemoryView(updated, view.version + 1, view.lineage)

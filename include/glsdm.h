@@ -1,0 +1,187 @@
+/*
+ * glsdm.h — C ABI of the B200-native transactional shared-memory operator.
+ *
+ * The reference project (kreasof-ai/GL-SDM) has no C ABI: its seam for this path is the
+ * Python package projects/gl-sdm/src/gl_sdm/memory, which on its "urm" backend calls
+ * exactly three native functions
+ *   - gl_sdm/memory/backends/urm.py:109-122      routed_snapshot_read(values, scores, width)
+ *   - gl_sdm/memory/backends/urm.py:49-82        snapshot_read(values, addresses, weights)
+ *   - gl_sdm/memory/backends/commit.py:57-58     commit(memory, indices, deltas, keys)
+ * Every entry point below cites the reference interface whose arithmetic it replaces.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless a parameter says "host".
+ *   - Nothing here allocates device memory unless stated; scratch is passed in as
+ *     `workspace`, sized by the matching *_workspace_bytes() query.
+ *   - Kernels are launched on `stream`; calls return after launch (asynchronous).
+ *   - The return value is a glsdm_status. Data-dependent failures (an address outside the
+ *     bank) are reported through a caller-owned device word `device_status`, which the
+ *     kernels OR error bits into; the caller zeroes it and reads it back when it wants.
+ *   - A "row" of routing work is one (request, token, head) triple; rows are laid out
+ *     [batch, token, head] row-major exactly as the reference's score tensor
+ *     [B, T, H, 2*half] (gl_sdm/memory/routing.py:10-14).
+ *   - A bank is [banks, heads, slots, dim] row-major (gl_sdm/memory/state.py:8-9), fp32 as
+ *     in the reference or bf16 (extension). banks == 1 means one bank shared by the batch.
+ */
+#ifndef GLSDM_H_
+#define GLSDM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* glsdm_stream_t; /* same type as cudaStream_t */
+
+typedef enum {
+  GLSDM_OK = 0,
+  GLSDM_ERR_ARGUMENT = 1,    /* null pointer, negative size, misaligned pointer */
+  GLSDM_ERR_UNSUPPORTED = 2, /* shape outside what the kernels cover (e.g. width > 32) */
+  GLSDM_ERR_WORKSPACE = 3,   /* workspace smaller than *_workspace_bytes() */
+  GLSDM_ERR_CUDA = 4,        /* a CUDA runtime call or launch failed */
+  GLSDM_ERR_LIMIT = 5        /* size beyond a fixed built-in capacity */
+} glsdm_status;
+
+typedef enum { GLSDM_F32 = 0, GLSDM_BF16 = 1 } glsdm_dtype;
+
+/* Bits OR-ed into *device_status by kernels. */
+#define GLSDM_DEV_ADDRESS_OUT_OF_RANGE 1u
+#define GLSDM_DEV_WAIT_EXPIRED 2u
+
+int glsdm_abi_version(void);
+const char* glsdm_status_string(int status);
+/* Message of the last CUDA error seen by this library on the calling thread (host string). */
+const char* glsdm_last_cuda_error(void);
+
+/* Describes the bank a routed read gathers from. `values` points at slot `slot_lo` of
+ * partition 0: a rank that owns slots [slot_lo, slot_hi) of every partition passes its
+ * shard, whose partition stride is (slot_hi - slot_lo) rows. An unsharded bank has
+ * slot_lo = 0, slot_hi = slots. Rows whose slot falls outside [slot_lo, slot_hi) add
+ * nothing to the reading (partial read of a slot-sharded bank). */
+typedef struct {
+  const void* values;
+  int dtype;        /* glsdm_dtype */
+  int64_t banks;    /* requests holding their own bank, or 1 for a shared bank */
+  int32_t heads;
+  int64_t slots;    /* logical slots per (bank, head) partition; a perfect square for product keys */
+  int32_t dim;      /* value width D */
+  int64_t slot_lo;
+  int64_t slot_hi;
+} glsdm_bank;
+
+/* Product-key routing, reference gl_sdm/memory/routing.py:10-26 (torch_routed_read, the
+ * part before the row gather) and the route half of backends/urm.py:109-122.
+ *   scores      [rows, 2*half] fp32; first half = left factor (high digit of the slot).
+ *   width       routes requested; out_k = min(width, min(width, half)^2) are produced.
+ *   out_index   [rows, out_k] int64 if index_i64 else int32, slot numbers ascending.
+ *   out_weights [rows, out_k] fp32, softmax of the selected sums in that order.
+ * Equal scores prefer the larger factor index / larger slot; -0.0 ties with +0.0. */
+int glsdm_pk_select(const float* scores, int64_t rows, int32_t half, int32_t width,
+                    void* out_index, int index_i64, float* out_weights, glsdm_stream_t stream);
+
+/* Snapshot read with supplied routes, reference gl_sdm/memory/routing.py:27-28,31-42
+ * (gather_rows + weighted sum), gl_sdm/memory/transactions.py:28-35 (read) and
+ * backends/urm.py:49-82 (snapshot_read).
+ *   index/weights [rows, width]; a row belongs to bank (row / rows_per_bank) when
+ *   bank->banks > 1 and to head (row % heads).
+ *   requests      optional [rows / heads] int64: the bank of each group of `heads` rows
+ *                 (the token-clock API's request indirection, transactions.py:13-16);
+ *                 NULL = derive the bank from rows_per_bank.
+ *   out_read      [rows, dim] fp32. */
+int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, int index_i64,
+                        const float* weights, const int64_t* requests, int64_t rows,
+                        int64_t rows_per_bank, int32_t width, float* out_read,
+                        uint32_t* device_status, glsdm_stream_t stream);
+
+/* Fused route + read: reference gl_sdm/memory/routing.py:10-28 in one pass
+ * (routed_snapshot_read, backends/urm.py:109-122). out_index / out_weights may be NULL when
+ * the caller needs only the readings (the query read of global_layer.py:27). */
+int glsdm_pk_select_read(const glsdm_bank* bank, const float* scores, int64_t rows,
+                         int64_t rows_per_bank, int32_t half, int32_t width, float* out_read,
+                         void* out_index, int index_i64, float* out_weights,
+                         uint32_t* device_status, glsdm_stream_t stream);
+
+/* Fused write proposal: write route + prediction read + row gather + delta + sort key.
+ * Reference gl_sdm/layers/global_layer.py:41-54 with gl_sdm/runtime/dense.py:11-14
+ * (proposal_delta) and gl_sdm/memory/routing.py:31-42.
+ *   scores   [rows, 2*half] fp32 write-router factor scores
+ *   target   [rows, dim] fp32 or bf16 (target_dtype)
+ *   beta     [rows] fp32 (already sigmoid-ed), log_decay [rows] fp32 (<= 0)
+ *   mass     [rows / heads] fp32 per token, or NULL for 1
+ *   position of a row inside its commit chunk = chunk_offset + (row / heads) % tokens
+ *   key      = address * (chunk_size * num_layers) + position * num_layers + layer_index
+ *   out_addresses [rows*out_k] int64 flat bank rows ((bank*heads+head)*slots + slot)
+ *   out_deltas    [rows*out_k, dim] fp32
+ *   out_keys      [rows*out_k] int64 */
+int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, const void* target,
+                     int target_dtype, const float* beta, const float* log_decay,
+                     const float* mass, int64_t rows, int64_t rows_per_bank, int64_t tokens,
+                     int32_t half, int32_t width, int64_t chunk_offset, int64_t chunk_size,
+                     int32_t num_layers, int32_t layer_index, int64_t* out_addresses,
+                     float* out_deltas, int64_t* out_keys, uint32_t* device_status,
+                     glsdm_stream_t stream);
+
+/* Row gather out[n, :] = flat[addresses[n], :] in the bank's dtype, reference
+ * gl_sdm/memory/routing.py:37-42 (gather_rows), gl_sdm/memory/transactions.py:19-25
+ * (selected) and gl_sdm/memory/backends/primitives.py:14-20 (_gather). */
+int glsdm_gather_rows(const void* flat, int dtype, int64_t bank_rows, int32_t dim,
+                      const int64_t* addresses, int64_t count, void* out,
+                      uint32_t* device_status, glsdm_stream_t stream);
+
+/* Token-clock write proposal, reference gl_sdm/memory/transactions.py:38-59 and
+ * gl_sdm/memory/backends/token.py:180-203 (_propose_forward).
+ *   requests [rows/heads] int64, index/weights [rows, width], target [rows, dim] fp32,
+ *   beta/log_decay [rows] fp32, mass [rows/heads] fp32
+ *   out_addresses [rows*width] int64 flat bank rows, out_deltas [rows*width, dim] fp32 */
+int glsdm_token_propose(const glsdm_bank* bank, const int64_t* requests, const void* index,
+                        int index_i64, const float* weights, const float* target,
+                        const float* beta, const float* log_decay, const float* mass,
+                        int64_t rows, int32_t width, int64_t* out_addresses, float* out_deltas,
+                        uint32_t* device_status, glsdm_stream_t stream);
+
+/* Buffered commit: stable sort of the entries by key, per-address fp32 sum in that order,
+ * one read-modify-write per touched bank row, no float atomics. Reference
+ * gl_sdm/memory/transactions.py:69-97 (torch path) and backends/commit.py:12-58 (Triton).
+ *   values_in   bank rows [bank_rows, dim] (dtype), first row = flat address row_base
+ *   values_out  NULL or == values_in: update in place; otherwise the whole bank is copied
+ *               to values_out first and values_in is left untouched (functional commit)
+ *   addresses   [entries] int64 flat bank rows; rows outside [row_base, row_base+bank_rows)
+ *               set GLSDM_DEV_ADDRESS_OUT_OF_RANGE and are dropped
+ *   deltas      [entries, dim] fp32
+ *   keys        [entries] int64 or NULL (= sort by address, arrival order within it)
+ *   key_bits    number of low key bits that can be non-zero, 0 = all 64
+ * Segments no longer than 256 entries are summed strictly left to right; longer ones in
+ * 256-entry blocks whose partial sums are then added left to right. */
+size_t glsdm_commit_workspace_bytes(int64_t entries, int32_t dim);
+int glsdm_commit(const void* values_in, void* values_out, int dtype, int64_t row_base,
+                 int64_t bank_rows, int32_t dim, const int64_t* addresses, const float* deltas,
+                 const int64_t* keys, int64_t entries, int32_t key_bits, void* workspace,
+                 size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
+
+/* Dense-key routing (flat keys): scores = queries x keys^T on the tensor cores, fused with
+ * a running per-row top-k, so the [rows, slots] score matrix is never stored. The
+ * reference has no per-slot key tensor; its nearest interface is the score GEMM of
+ * gl_sdm/layers/global_layer.py:26 followed by routing.py:21-26 (tie rule, softmax).
+ *   queries [rows, dk] bf16, keys [slots, dk] bf16 (this rank's shard), dk in {64,128}
+ *   col_base  global slot number of keys row 0
+ *   out_score [rows, width] fp32 and out_slot [rows, width] int32: the `width` best
+ *   (score, slot) pairs of this shard, best first; ties prefer the larger slot. */
+size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width);
+int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_t slots,
+                     int32_t dk, int32_t width, int64_t col_base, float* out_score,
+                     int32_t* out_slot, void* workspace, size_t workspace_bytes,
+                     uint32_t* device_status, glsdm_stream_t stream);
+
+/* Merge per-shard candidates into the global routes (tie rule and softmax of
+ * gl_sdm/memory/routing.py:21-26 applied to `parts` candidate lists per row).
+ *   cand_score / cand_slot [parts, rows, width]; out_index ascending, out_weights softmax. */
+int glsdm_topk_merge(const float* cand_score, const int32_t* cand_slot, int32_t parts,
+                     int64_t rows, int32_t width, void* out_index, int index_i64,
+                     float* out_weights, glsdm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLSDM_H_ */

@@ -1,0 +1,95 @@
+"""Multi-threaded CPU port (PyTorch tensor ops) of the GL-SDM memory operator.
+
+TEST INFRASTRUCTURE ONLY: the timed CPU baseline of bench.py (cpu_baseline and
+`--impl reference`) and a second checker in tests/. The reference's own CPU path for this
+operator is PyTorch tensor code (projects/gl-sdm/src/gl_sdm/memory/routing.py:10-42,
+memory/transactions.py:69-97, runtime/dense.py:11-14), so its faithful CPU timing is the
+same sequence of library sorts, gathers and segmented sums run on all host threads. The
+reference checkout itself cannot travel to the benchmark machine; this port is pinned
+against the reference's outputs in tests/test_oracle_golden.py.
+"""
+import torch
+
+
+def _rank_desc_prefer_high(values, keep):
+    """Positions of the `keep` largest entries along the last axis, equal values preferring
+    the higher position (routing.py:15-17,21-24): rank the reversed axis stably."""
+    last = values.shape[-1]
+    reversed_rank = torch.sort(values.flip(-1), dim=-1, descending=True, stable=True).indices[..., :keep]
+    return last - 1 - reversed_rank
+
+
+def select_routes(scores, width):
+    """routing.py:10-26 -> (address int64 ascending, softmax weights)."""
+    lead, half = scores.shape[:-1], scores.shape[-1] // 2
+    factors = scores.reshape(*lead, 2, half)
+    picked = _rank_desc_prefer_high(factors, width)
+    best = torch.gather(factors, -1, picked)
+    sums = (best[..., 0, :].unsqueeze(-1) + best[..., 1, :].unsqueeze(-2)).flatten(-2)
+    slots = (picked[..., 0, :].unsqueeze(-1) * half + picked[..., 1, :].unsqueeze(-2)).flatten(-2)
+    # candidates in descending slot order, then a stable ranking of the sums
+    slots, by_slot = torch.sort(slots, dim=-1, descending=True, stable=True)
+    sums = torch.gather(sums, -1, by_slot)
+    winners = torch.sort(sums, dim=-1, descending=True, stable=True).indices[..., :width]
+    slots, sums = torch.gather(slots, -1, winners), torch.gather(sums, -1, winners)
+    slots, ascending = torch.sort(slots, dim=-1)
+    return slots, torch.softmax(torch.gather(sums, -1, ascending), dim=-1)
+
+
+def flat_rows(memory, index):
+    """routing.py:31-34: (b*H + h)*S + slot; a single shared bank uses partition = head."""
+    B, T, H, _ = index.shape
+    S = memory.shape[2]
+    if memory.shape[0] == 1 and B > 1:
+        part = torch.arange(H).view(1, 1, H, 1)
+    else:
+        part = torch.arange(B * H).view(B, 1, H, 1)
+    return part * S + index
+
+
+def routed_read(memory, scores, width):
+    """routing.py:10-28 -> (readings, index, weights)."""
+    index, weights = select_routes(scores.float(), width)
+    rows = memory.flatten(0, 2)[flat_rows(memory, index)].float()
+    return (rows * weights.unsqueeze(-1)).sum(-2), index, weights
+
+
+def delta_rows(rows, weights, prediction, target, beta, log_decay, mass):
+    """runtime/dense.py:11-14."""
+    decay = log_decay.exp()
+    error = beta * (target.float() - decay * prediction)
+    return mass[..., None, None, None] * ((decay.unsqueeze(-1) - 1) * rows + weights.unsqueeze(-1) * error.unsqueeze(-2))
+
+
+def propose(memory, scores, width, target, beta, log_decay, mass, offset, layer_index, chunk_size, num_layers):
+    """layers/global_layer.py:41-54 from the factor scores on -> (addresses, deltas, keys)."""
+    B, T, H, _ = scores.shape
+    prediction, index, weights = routed_read(memory, scores, width)
+    addresses = flat_rows(memory, index)
+    rows = memory.flatten(0, 2)[addresses].float()
+    mass = torch.ones(B, T) if mass is None else mass
+    delta = delta_rows(rows, weights, prediction, target, beta.unsqueeze(-1), log_decay.unsqueeze(-1), mass)
+    position = torch.arange(offset, offset + T).view(1, T, 1, 1)
+    keys = addresses * (chunk_size * num_layers) + position * num_layers + layer_index
+    return addresses.flatten(), delta.flatten(0, 3), keys.flatten()
+
+
+def commit(memory, addresses, deltas, keys=None):
+    """memory/transactions.py:80,90-96: new bank = old + per-address ordered sums."""
+    flat = memory.reshape(-1, memory.shape[-1])
+    if addresses.numel() == 0:
+        return memory.clone()
+    order = torch.sort(addresses if keys is None else keys, stable=True).indices
+    rows, runs = torch.unique_consecutive(addresses[order], return_counts=True)
+    totals = torch.segment_reduce(deltas.float()[order], "sum", lengths=runs)
+    return flat.index_copy(0, rows, (flat[rows].float() + totals).to(flat.dtype)).view_as(memory)
+
+
+def flat_routes(queries, keys, width):
+    """Flat-key mode (no counterpart in the reference): q @ keys^T, then the slot-sum
+    selection rule (routing.py:21-26). -> (slot ascending, softmax weights)."""
+    scores = queries.float() @ keys.float().T
+    slot = _rank_desc_prefer_high(scores, width)
+    best = torch.gather(scores, -1, slot)
+    slot, ascending = torch.sort(slot, dim=-1)
+    return slot, torch.softmax(torch.gather(best, -1, ascending), dim=-1)
