@@ -1,0 +1,52 @@
+"""The C-ABI library loads and exports every symbol include/glsdm.h declares; argument
+checks that run before any launch work without a GPU."""
+import ctypes
+import os
+import re
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "glsdm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(glsdm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(native):
+    lib = ctypes.CDLL(native.LIBRARY_PATH)
+    names = declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in glsdm.h but not exported"
+    assert set(native.SIGNATURES) == set(names), "ctypes signatures and header disagree"
+
+
+def test_status_strings_and_version(native):
+    lib = native.library()
+    assert lib.glsdm_abi_version() >= 1
+    assert lib.glsdm_status_string(0) == b"ok"
+    for code in range(1, 6):
+        assert len(lib.glsdm_status_string(code)) > 4
+    assert lib.glsdm_status_string(99) == b"unknown status"
+
+
+def test_argument_errors_need_no_device(native):
+    lib = native.library()
+    null = ctypes.c_void_p(0)
+    # null scores
+    assert lib.glsdm_pk_select(null, 4, 8, 2, null, 1, null, null) == 1
+    # width beyond the 32 routes a warp keeps
+    fake = ctypes.c_void_p(4096)
+    assert lib.glsdm_pk_select(fake, 4, 64, 33, fake, 1, fake, null) == 2
+    # zero rows is a successful no-op and launches nothing
+    assert lib.glsdm_pk_select(fake, 0, 64, 8, fake, 1, fake, null) == 0
+    bank = native.Bank(4096, 0, 1, 1, 16, 8, 0, 16)
+    assert lib.glsdm_snapshot_read(ctypes.byref(bank), fake, 1, fake, null, 0, 1, 2, fake, null, null) == 0
+    bad = native.Bank(4096, 0, 1, 1, 16, 8, 4, 2)  # empty slot range
+    assert lib.glsdm_snapshot_read(ctypes.byref(bad), fake, 1, fake, null, 1, 1, 2, fake, null, null) == 1
+    assert lib.glsdm_commit_workspace_bytes(1000, 64) > 1000 * 28
+    # commit with a workspace that is too small
+    assert lib.glsdm_commit(fake, fake, 0, 0, 16, 8, fake, fake, null, 10, 0, ctypes.c_void_p(256), 16, null, null) == 3
+    assert lib.glsdm_topk_merge(fake, fake, 2, 0, 8, fake, 1, fake, null) == 0
+    assert lib.glsdm_topk_merge(fake, fake, 2, 4, 40, fake, 1, fake, null) == 2

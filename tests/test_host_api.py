@@ -1,0 +1,120 @@
+"""Host-side logic of the gl_sdm.memory mirror: value objects, validation, error text,
+no CPU fallback, and the module shim - the CPU-checkable parts of the reference's tests
+(projects/gl-sdm/tests/test_global_memory.py:27-54,57-66; test_native_memory.py:141-144)."""
+import sys
+
+import pytest
+import torch
+
+from gl_sdm_b200.memory import (MemoryBank, MemoryCache, MemoryView, WriteBuffer, WriteProposal, commit, merge,
+                                read, propose_write, routing)
+from gl_sdm_b200.memory import oracle_hook
+
+
+def test_view_validation():
+    MemoryView(torch.zeros(1, 1, 4, 2))
+    MemoryView(torch.zeros(1, 1, 4, 2, dtype=torch.bfloat16))  # extension: bf16 storage
+    for bad in (torch.zeros(4, 2), torch.zeros(1, 1, 0, 2), torch.zeros(1, 1, 4, 2, dtype=torch.float64)):
+        with pytest.raises(ValueError, match="memory views require"):
+            MemoryView(bad)
+    with pytest.raises(ValueError, match="nonnegative version"):
+        MemoryView(torch.zeros(1, 1, 4, 2), version=-1)
+    a, b = MemoryView(torch.zeros(1, 1, 4, 2)), MemoryView(torch.zeros(1, 1, 4, 2))
+    assert a.lineage is not b.lineage and a.version == 0
+
+
+def test_merge_and_commit_reject_stale_or_foreign_transactions():
+    view = MemoryView(torch.zeros(1, 1, 4, 1))
+    p = WriteProposal(0, torch.tensor([3]), torch.tensor([[1.0]]), view.lineage)
+    assert isinstance(merge(view, [p]), WriteBuffer)
+    with pytest.raises(ValueError, match="snapshot"):
+        merge(view, [])
+    newer = MemoryView(view.values, 1, view.lineage)
+    with pytest.raises(ValueError, match="snapshot"):
+        merge(newer, [p])
+    with pytest.raises(ValueError, match="snapshot"):
+        merge(MemoryView(view.values), [p])
+    buffer = merge(view, [p])
+    with pytest.raises(ValueError, match="stale"):
+        commit(newer, buffer)
+    with pytest.raises(ValueError, match="stale"):
+        commit(MemoryView(view.values), buffer)
+    keyed = WriteProposal(0, torch.tensor([3]), torch.tensor([[1.0]]), view.lineage, torch.tensor([7]))
+    with pytest.raises(ValueError, match="cannot mix keyed and unkeyed"):
+        commit(view, merge(view, [p, keyed]))
+    with pytest.raises(ValueError, match="memory backend must be torch or urm"):
+        commit(view, buffer, backend="triton")
+    with pytest.raises(ValueError, match="memory backend must be torch or urm"):
+        read(view, torch.tensor([0]), torch.zeros(1, 1, 1, dtype=torch.long), torch.ones(1, 1, 1), backend="x")
+
+
+def test_no_cpu_fallback():
+    """Every compute entry raises on CPU tensors (reference test_native_memory.py:141-144)."""
+    view = MemoryView(torch.zeros(1, 1, 4, 2))
+    p = WriteProposal(0, torch.tensor([3]), torch.tensor([[1.0, 1.0]]), view.lineage)
+    with pytest.raises(ValueError, match="CUDA"):
+        commit(view, merge(view, [p]))
+    with pytest.raises(ValueError, match="CUDA"):
+        routing.torch_routed_read(view.values, torch.zeros(1, 3, 1, 4), 2)
+    with pytest.raises(ValueError, match="CUDA"):
+        routing.gather_rows(view.values, torch.zeros(1, 3, 1, 2, dtype=torch.long))
+    with pytest.raises(ValueError, match="CUDA"):
+        read(view, torch.tensor([0]), torch.zeros(1, 1, 1, dtype=torch.long), torch.ones(1, 1, 1))
+    with pytest.raises(ValueError, match="CUDA"):
+        propose_write(view, torch.tensor([0]), torch.zeros(1, 1, 1, dtype=torch.long), torch.ones(1, 1, 1),
+                      torch.zeros(1, 1, 2), torch.ones(1, 1, 1), torch.zeros(1, 1, 1), torch.ones(1))
+
+
+def test_reference_switch_needs_a_registered_oracle():
+    oracle_hook.clear()
+    view = MemoryView(torch.zeros(1, 1, 4, 2))
+    p = WriteProposal(0, torch.tensor([3]), torch.tensor([[1.0, 1.0]]), view.lineage)
+    with pytest.raises(RuntimeError, match="oracle"):
+        commit(view, merge(view, [p]), reference=True)
+    calls = []
+    oracle_hook.register(commit=lambda v, b: calls.append(1) or MemoryView(v.values + 1, v.version + 1, v.lineage))
+    try:
+        assert commit(view, merge(view, [p]), reference=True).version == 1 and calls == [1]
+    finally:
+        oracle_hook.clear()
+
+
+def test_bank_stays_fp32_and_owns_its_caches():
+    bank = MemoryBank(2, 16, 8)
+    assert bank.memory.shape == (2, 16, 8) and bank.memory._sdm_memory_bank
+    before = bank.memory.detach().clone()
+    bank = bank.to(torch.bfloat16)
+    assert bank.memory.dtype == torch.float32 and torch.equal(bank.memory, before)
+    cache = bank.new_cache(3)
+    assert isinstance(cache, MemoryCache) and cache.view.values.shape == (3, 2, 16, 8) and cache.tokens == 0
+    bank.validate_cache(cache, 3)
+    with pytest.raises(ValueError, match="another model"):
+        bank.validate_cache(cache, 2)
+    with pytest.raises(ValueError, match="another model"):
+        MemoryBank(2, 16, 8).validate_cache(cache, 3)
+    assert [n for n, _ in bank.named_parameters()] == ["memory"]
+
+
+def test_absolute_addresses_and_token_addresses():
+    from gl_sdm_b200.memory.transactions import addresses
+    memory = torch.zeros(2, 3, 5, 1)
+    index = torch.tensor([0, 4]).expand(2, 1, 3, 2)
+    out = routing.absolute_addresses(memory, index)
+    assert out[1, 0, 2].tolist() == [(1 * 3 + 2) * 5, (1 * 3 + 2) * 5 + 4]
+    view = MemoryView(memory)
+    token = addresses(view, torch.tensor([1]), torch.tensor([[[0], [1], [2]]]))
+    assert token.flatten().tolist() == [15, 21, 27]
+
+
+def test_install_shim_binds_reference_module_names():
+    from gl_sdm_b200 import install, memory
+    previous = install.install()
+    try:
+        import importlib
+        assert importlib.import_module("gl_sdm.memory") is memory
+        assert importlib.import_module("gl_sdm.memory.routing") is memory.routing
+        from gl_sdm.memory.backends import commit as native_commit, urm
+        assert callable(native_commit.commit) and callable(urm.routed_snapshot_read) and callable(urm.verify_dependency)
+    finally:
+        install.uninstall(previous)
+    assert sys.modules.get("gl_sdm.memory") is not memory
