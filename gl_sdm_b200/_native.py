@@ -38,6 +38,7 @@ SIGNATURES = {
     "glsdm_abi_version": (ctypes.c_int, []),
     "glsdm_status_string": (ctypes.c_char_p, [_i]),
     "glsdm_last_cuda_error": (ctypes.c_char_p, []),
+    "glsdm_kernel_launches": (ctypes.c_uint64, []),
     "glsdm_pk_select": (_i, [_p, _i64, _i32, _i32, _p, _i, _p, _p]),
     "glsdm_snapshot_read": (_i, [_BANK, _p, _i, _p, _p, _i64, _i64, _i32, _p, _p, _p]),
     "glsdm_pk_select_read": (_i, [_BANK, _p, _i64, _i64, _i32, _i32, _p, _p, _i, _p, _p, _p]),
@@ -45,6 +46,11 @@ SIGNATURES = {
                               _i64, _i32, _i32, _p, _p, _p, _p, _p]),
     "glsdm_gather_rows": (_i, [_p, _i, _i64, _i32, _p, _i64, _p, _p, _p]),
     "glsdm_token_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
+    "glsdm_write_error": (_i, [_p, _p, _i, _p, _p, _i64, _i32, _p, _p, _p]),
+    "glsdm_shard_read": (_i, [_BANK, _p, _p, _i64, _i64, _i64, _i32, _p, _p, _p]),
+    "glsdm_shard_offsets": (_i, [_p, _i64, _i64, _i64, _i32, _i64, _i64, _p, _p]),
+    "glsdm_shard_propose": (_i, [_BANK, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _i64, _i64,
+                                 _i32, _i32, _p, _p, _p, _p]),
     "glsdm_commit_workspace_bytes": (_sz, [_i64, _i32]),
     "glsdm_commit": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p]),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
@@ -147,6 +153,16 @@ def raise_on_device_status(device):
         names = [n for b, n in ((DEV_ADDRESS_OUT_OF_RANGE, "address out of range"),
                                 (DEV_WAIT_EXPIRED, "bounded wait expired")) if bits & b]
         raise RuntimeError("glsdm device status: " + ", ".join(names))
+
+
+def pk_select_into(scores, width, routes, index_at, weights_at):
+    """Routes of `scores` written into an int32 buffer: indices at element index_at, weight
+    bits at element weights_at (the send buffer of the shard all-gather)."""
+    require_cuda(scores, routes)
+    half = scores.shape[-1] // 2
+    rows = scores.numel() // (2 * half)
+    _check(library().glsdm_pk_select(_ptr(scores), rows, half, width, _at(routes, index_at), 0,
+                                     _at(routes, weights_at), _stream(scores.device)))
 
 
 def pk_select(scores, width, index_dtype=torch.int64):
@@ -276,6 +292,73 @@ def token_propose(values, requests, index, weights, target, beta, log_decay, mas
                                          _ptr(addresses), _ptr(deltas), _ptr(status_word(values.device)),
                                          _stream(values.device)))
     return addresses, deltas
+
+
+def write_error(prediction, target, beta, log_decay, packed=None):
+    """Token-owner half of the proposal. Returns `packed`, a float32 buffer of rows*(dim+1)
+    elements: the error rows [rows, dim] followed by (decay - 1) [rows]."""
+    require_cuda(prediction, target, beta, log_decay, packed)
+    dim = prediction.shape[-1]
+    rows = prediction.numel() // dim
+    if packed is None:
+        packed = torch.empty(rows * (dim + 1), dtype=torch.float32, device=prediction.device)
+    elif packed.numel() != rows * (dim + 1) or packed.dtype != torch.float32:
+        raise ValueError("packed error buffer must hold rows*(dim+1) float32 values")
+    _check(library().glsdm_write_error(_ptr(prediction), _ptr(target), _dtype_code(target), _ptr(beta),
+                                       _ptr(log_decay), rows, dim, _at(packed, 0), _at(packed, rows * dim),
+                                       _stream(prediction.device)))
+    return packed
+
+
+def _at(tensor, offset):
+    """Device address of element `offset` of a 4-byte-element tensor."""
+    return ctypes.c_void_p(tensor.data_ptr() + 4 * offset)
+
+
+def shard_read(shard, slot_lo, slots, routes, index_at, weights_at, rows, block_rows, block_stride, width):
+    """Partial readings [rows, dim] of this rank's shard for all-gathered routes.
+
+    `routes` is the int32 all-gather buffer; block b's indices start at element
+    index_at + b*block_stride and its weights (float32 bits) at weights_at + b*block_stride.
+    """
+    require_cuda(shard, routes)
+    bank = bank_of(shard, slot_lo, None, slots)
+    out = torch.empty((rows, shard.shape[-1]), dtype=torch.float32, device=shard.device)
+    _check(library().glsdm_shard_read(ctypes.byref(bank), _at(routes, index_at), _at(routes, weights_at), rows,
+                                      block_rows, block_stride, width, _ptr(out),
+                                      _ptr(status_word(shard.device)), _stream(shard.device)))
+    return out
+
+
+def shard_offsets(routes, index_at, rows, block_rows, block_stride, width, slot_lo, slot_hi):
+    """Exclusive prefix of owned routes per row; element `rows` is the shard's entry count."""
+    require_cuda(routes)
+    offsets = torch.empty(rows + 1, dtype=torch.int32, device=routes.device)
+    _check(library().glsdm_shard_offsets(_at(routes, index_at), rows, block_rows, block_stride, width, slot_lo,
+                                         slot_hi, _ptr(offsets), _stream(routes.device)))
+    return offsets
+
+
+def shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
+                  offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
+                  layer_index, out):
+    """Slot-owner half of the proposal; fills the first `entries` rows of the `out` buffers.
+
+    `errors` is the float32 all-gather buffer of write errors: per block, block_rows error rows
+    [block_rows, dim] followed by block_rows (decay - 1) values, error_stride elements per block.
+    """
+    require_cuda(shard, routes, errors, mass, offsets)
+    bank = bank_of(shard, slot_lo, None, slots)
+    dim = shard.shape[-1]
+    addresses, deltas, keys = out
+    if addresses.numel() < entries or deltas.numel() < entries * dim or keys.numel() < entries:
+        raise ValueError("proposal buffers are smaller than the shard's entry count")
+    _check(library().glsdm_shard_propose(ctypes.byref(bank), _at(routes, index_at), _at(routes, weights_at),
+                                         _at(errors, 0), _at(errors, block_rows * dim), _ptr(mass), _ptr(offsets),
+                                         rows, block_rows, route_stride, error_stride, tokens, width, chunk_offset,
+                                         chunk_size, num_layers, layer_index, _ptr(addresses), _ptr(deltas),
+                                         _ptr(keys), _stream(shard.device)))
+    return addresses[:entries], deltas[:entries], keys[:entries]
 
 
 _workspaces = {}

@@ -1,12 +1,17 @@
 // Status strings, ABI version and the per-thread CUDA error note.
 #include <stdio.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace glsdm {
 namespace {
 thread_local char g_last_cuda_error[256] = "";
+std::atomic<unsigned long long> g_launches{0};
 }
+
+void count_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
 void note_cuda_error(cudaError_t err, const char* where) {
   snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s (%s)", where,
@@ -29,3 +34,5 @@ extern "C" const char* glsdm_status_string(int status) {
 }
 
 extern "C" const char* glsdm_last_cuda_error(void) { return glsdm::g_last_cuda_error; }
+
+extern "C" uint64_t glsdm_kernel_launches(void) { return glsdm::g_launches.load(std::memory_order_relaxed); }

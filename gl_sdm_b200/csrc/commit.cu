@@ -501,6 +501,7 @@ int launch_reduce(const Workspace& w, const ReduceArgs& a, glsdm_stream_t stream
     GLSDM_CUDA_OK(cudaGetLastError(), "commit reduce launch");                              \
     long_segment_kernel<T, V><<<long_grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);         \
     GLSDM_CUDA_OK(cudaGetLastError(), "commit long-segment launch");                        \
+    count_launches(2);                                                                      \
   } while (0)
   if (aligned && a.dim == 32) GLSDM_REDUCE(1);
   else if (aligned && a.dim == 64) GLSDM_REDUCE(2);
@@ -561,6 +562,7 @@ extern "C" int glsdm_commit(const void* values_in, void* values_out, int dtype, 
   }
   gather_address_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, addresses, entries);
   GLSDM_CUDA_OK(cudaGetLastError(), "commit gather launch");
+  count_launches(3 + 3 * passes);
 
   ReduceArgs a;
   a.values_in = values_in;

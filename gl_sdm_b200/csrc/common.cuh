@@ -16,6 +16,8 @@ constexpr int kStageSlots = 64;  // staged candidates per warp (shared memory, 8
 
 // Thread-local record of the last CUDA failure, for glsdm_last_cuda_error().
 void note_cuda_error(cudaError_t err, const char* where);
+// Process-wide count of kernels this library has launched (glsdm_kernel_launches()).
+void count_launches(int n);
 
 #define GLSDM_CUDA_OK(expr, where)                  \
   do {                                              \

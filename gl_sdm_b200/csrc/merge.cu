@@ -54,5 +54,6 @@ extern "C" int glsdm_topk_merge(const float* cand_score, const int32_t* cand_slo
   topk_merge_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
       cand_score, cand_slot, parts, rows, width, out_index, index_i64, out_weights);
   GLSDM_CUDA_OK(cudaGetLastError(), "topk_merge launch");
+  count_launches(1);
   return GLSDM_OK;
 }

@@ -58,14 +58,17 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 snapshot_read_kernel(BankView bank, const void* __restrict__ index, int i64,
                      const float* __restrict__ weights, const int64_t* __restrict__ requests,
                      int64_t rows, int64_t rows_per_bank, int width, bool vec,
-                     float* __restrict__ out_read, uint32_t* device_status) {
+                     float* __restrict__ out_read, uint32_t* device_status, int64_t block_rows,
+                     int64_t block_stride) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
   if (row >= rows) return;
   uint32_t slot = 0;
   float weight = 0.f;
   if (lane < width) {
-    const int64_t at = row * width + lane;
+    // Routes may arrive as per-rank blocks of an all-gather: block b holds block_rows rows
+    // starting block_stride elements after block b-1. A plain [rows, width] array is one block.
+    const int64_t at = (row / block_rows) * block_stride + (row % block_rows) * width + lane;
     const int64_t s = i64 ? static_cast<const int64_t*>(index)[at]
                           : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
     weight = weights[at];
@@ -297,6 +300,7 @@ extern "C" int glsdm_pk_select(const float* scores, int64_t rows, int32_t half, 
   pk_select_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
       scores, rows, half, kf, kout, out_index, index_i64, out_weights);
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_select launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -314,13 +318,38 @@ extern "C" int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, in
   if (bank->dtype == GLSDM_F32) {
     const bool vec = vector_rows<float>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
     snapshot_read_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status);
+        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status, rows, 0);
   } else {
     const bool vec = vector_rows<__nv_bfloat16>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;
     snapshot_read_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
-        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status);
+        v, index, index_i64, weights, requests, rows, rows_per_bank, width, vec, out_read, device_status, rows, 0);
   }
   GLSDM_CUDA_OK(cudaGetLastError(), "snapshot_read launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_shard_read(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                                int64_t rows, int64_t block_rows, int64_t block_stride, int32_t width,
+                                float* out_partial, uint32_t* device_status, glsdm_stream_t stream) {
+  if (int s = check_bank(bank)) return s;
+  if (index == nullptr || weights == nullptr || out_partial == nullptr || rows < 0) return GLSDM_ERR_ARGUMENT;
+  if (width < 1 || block_rows < 1 || block_stride < 0) return GLSDM_ERR_ARGUMENT;
+  if (width > 32 || bank->banks != 1) return GLSDM_ERR_UNSUPPORTED;
+  if (rows == 0) return GLSDM_OK;
+  const BankView v = make_view(*bank);
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+  if (bank->dtype == GLSDM_F32) {
+    const bool vec = vector_rows<float>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_partial) & 15u) == 0;
+    snapshot_read_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, index, 0, weights, nullptr, rows, rows, width, vec, out_partial, device_status, block_rows, block_stride);
+  } else {
+    const bool vec = vector_rows<__nv_bfloat16>(v.dim, v.values) && (reinterpret_cast<uintptr_t>(out_partial) & 15u) == 0;
+    snapshot_read_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, index, 0, weights, nullptr, rows, rows, width, vec, out_partial, device_status, block_rows, block_stride);
+  }
+  GLSDM_CUDA_OK(cudaGetLastError(), "shard_read launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -349,6 +378,7 @@ extern "C" int glsdm_pk_select_read(const glsdm_bank* bank, const float* scores,
         v, scores, rows, rows_per_bank, half, kf, kout, vec, out_read, out_index, index_i64, out_weights);
   }
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_select_read launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -403,6 +433,7 @@ extern "C" int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, con
   }
 #undef GLSDM_PROPOSE
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_propose launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -426,6 +457,7 @@ extern "C" int glsdm_gather_rows(const void* flat, int dtype, int64_t bank_rows,
   else
     gather_rows_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(flat), addresses, count, bank_rows, units, static_cast<uint16_t*>(out), device_status);
   GLSDM_CUDA_OK(cudaGetLastError(), "gather_rows launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -453,5 +485,6 @@ extern "C" int glsdm_token_propose(const glsdm_bank* bank, const int64_t* reques
         static_cast<const __nv_bfloat16*>(bank->values), bank->banks, bank->heads, bank->slots, bank->dim, requests,
         index, index_i64, weights, target, beta, log_decay, mass, rows, width, out_addresses, out_deltas, device_status);
   GLSDM_CUDA_OK(cudaGetLastError(), "token_propose launch");
+  count_launches(1);
   return GLSDM_OK;
 }

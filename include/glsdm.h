@@ -54,6 +54,8 @@ int glsdm_abi_version(void);
 const char* glsdm_status_string(int status);
 /* Message of the last CUDA error seen by this library on the calling thread (host string). */
 const char* glsdm_last_cuda_error(void);
+/* Number of kernels this library has launched in the process so far (host counter). */
+uint64_t glsdm_kernel_launches(void);
 
 /* Describes the bank a routed read gathers from. `values` points at slot `slot_lo` of
  * partition 0: a rank that owns slots [slot_lo, slot_hi) of every partition passes its
@@ -140,6 +142,39 @@ int glsdm_token_propose(const glsdm_bank* bank, const int64_t* requests, const v
                         const float* beta, const float* log_decay, const float* mass,
                         int64_t rows, int32_t width, int64_t* out_addresses, float* out_deltas,
                         uint32_t* device_status, glsdm_stream_t stream);
+
+/* Slot-sharded write proposal (no counterpart in the reference, which is single-GPU; the
+ * arithmetic is gl_sdm/runtime/dense.py:11-14 split between token owner and slot owner).
+ * glsdm_write_error, on the token's rank:
+ *   out_error [rows, dim] = beta * (target - exp(log_decay) * prediction), out_decay_m1 [rows]
+ * glsdm_shard_offsets, on every rank for the all-gathered routes index [rows, width] int32:
+ *   offsets [rows + 1] = exclusive prefix of the number of routes per row whose slot is in
+ *   [slot_lo, slot_hi); offsets[rows] = this rank's entry count
+ * glsdm_shard_propose, on the slot's rank: for each owned route, in (row, route) order,
+ *   delta = mass * (decay_m1 * row + w * error), address = head * slots + slot and the key
+ *   of glsdm_pk_propose; `bank` is this rank's shard of one shared bank (banks == 1);
+ *   out_addresses are rows of that shard, out_keys use the bank-wide address.
+ * glsdm_shard_read: partial reading of this rank's shard for all-gathered int32 routes.
+ * Blocked addressing (all three): row r lives in block r / block_rows; consecutive blocks are
+ * `*_stride` elements apart (the per-rank pieces of an all-gather). Within an error block the
+ * [block_rows, dim] error rows are followed by the block's decay_m1 values; `decay_m1` points at
+ * the first block's decay values, `error` at its first row. */
+int glsdm_shard_read(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                     int64_t rows, int64_t block_rows, int64_t block_stride, int32_t width,
+                     float* out_partial, uint32_t* device_status, glsdm_stream_t stream);
+int glsdm_write_error(const float* prediction, const void* target, int target_dtype,
+                      const float* beta, const float* log_decay, int64_t rows, int32_t dim,
+                      float* out_error, float* out_decay_m1, glsdm_stream_t stream);
+int glsdm_shard_offsets(const int32_t* index, int64_t rows, int64_t block_rows,
+                        int64_t block_stride, int32_t width, int64_t slot_lo, int64_t slot_hi,
+                        uint32_t* offsets, glsdm_stream_t stream);
+int glsdm_shard_propose(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                        const float* error, const float* decay_m1, const float* mass,
+                        const uint32_t* offsets, int64_t rows, int64_t block_rows,
+                        int64_t route_stride, int64_t error_stride, int64_t tokens, int32_t width,
+                        int64_t chunk_offset, int64_t chunk_size, int32_t num_layers,
+                        int32_t layer_index, int64_t* out_addresses, float* out_deltas,
+                        int64_t* out_keys, glsdm_stream_t stream);
 
 /* Buffered commit: stable sort of the entries by key, per-address fp32 sum in that order,
  * one read-modify-write per touched bank row, no float atomics. Reference

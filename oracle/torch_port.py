@@ -74,15 +74,23 @@ def propose(memory, scores, width, target, beta, log_decay, mass, offset, layer_
     return addresses.flatten(), delta.flatten(0, 3), keys.flatten()
 
 
-def commit(memory, addresses, deltas, keys=None):
-    """memory/transactions.py:80,90-96: new bank = old + per-address ordered sums."""
+def commit(memory, addresses, deltas, keys=None, in_place=False):
+    """memory/transactions.py:80,90-96: new bank = old + per-address ordered sums.
+
+    in_place=True skips the reference's whole-bank copy (index_copy_ on the input), which is
+    how the large shared banks are committed; it only makes this CPU baseline faster.
+    """
     flat = memory.reshape(-1, memory.shape[-1])
     if addresses.numel() == 0:
-        return memory.clone()
+        return memory if in_place else memory.clone()
     order = torch.sort(addresses if keys is None else keys, stable=True).indices
     rows, runs = torch.unique_consecutive(addresses[order], return_counts=True)
     totals = torch.segment_reduce(deltas.float()[order], "sum", lengths=runs)
-    return flat.index_copy(0, rows, (flat[rows].float() + totals).to(flat.dtype)).view_as(memory)
+    updated = (flat[rows].float() + totals).to(flat.dtype)
+    if in_place:
+        flat.index_copy_(0, rows, updated)
+        return memory
+    return flat.index_copy(0, rows, updated).view_as(memory)
 
 
 def flat_routes(queries, keys, width):

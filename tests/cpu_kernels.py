@@ -1,0 +1,85 @@
+"""CPU stand-ins (numpy oracle) for the kernel entry points the sharded operator calls.
+
+Used ONLY by tests/test_sharded_cpu.py to run the exchange logic of ShardedBankOperator on
+gloo ranks without a GPU; the product always binds the CUDA library."""
+import numpy as np
+import torch
+
+from oracle import sdm_oracle as oracle
+
+
+def routes_out(width, half):
+    f = min(width, half)
+    return min(width, f * f)
+
+
+def pk_select_into(scores, width, routes, index_at, weights_at):
+    idx, w = oracle.select_routes(scores.numpy(), width)
+    n = idx.size
+    routes[index_at:index_at + n] = torch.from_numpy(idx.reshape(-1).astype(np.int32))
+    routes[weights_at:weights_at + n] = torch.from_numpy(w.reshape(-1)).view(torch.int32)
+
+
+def _blocked(buf, at, rows, block_rows, stride, width):
+    out = []
+    for b in range(rows // block_rows):
+        lo = at + b * stride
+        out.append(buf[lo:lo + block_rows * width].view(block_rows, width))
+    return torch.cat(out)
+
+
+def shard_read(shard, slot_lo, slots, routes, index_at, weights_at, rows, block_rows, block_stride, width):
+    idx = _blocked(routes, index_at, rows, block_rows, block_stride, width).numpy().astype(np.int64)
+    w = _blocked(routes, weights_at, rows, block_rows, block_stride, width).view(torch.float32).numpy()
+    H, local, D = shard.shape[1:]
+    owned = (idx >= slot_lo) & (idx < slot_lo + local)
+    head = (np.arange(rows) % H)[:, None]
+    rows_v = shard.float().numpy()[0][head, np.where(owned, idx - slot_lo, 0)]
+    return torch.from_numpy((rows_v * (w * owned)[..., None]).sum(1).astype(np.float32))
+
+
+def write_error(prediction, target, beta, log_decay, packed):
+    rows, dim = prediction.shape
+    decay = np.exp(log_decay.numpy().reshape(-1, 1).astype(np.float32))
+    err = beta.numpy().reshape(-1, 1) * (target.float().numpy().reshape(rows, dim) - decay * prediction.numpy())
+    packed[:rows * dim] = torch.from_numpy(err.astype(np.float32).reshape(-1))
+    packed[rows * dim:] = torch.from_numpy((decay - np.float32(1)).reshape(-1))
+    return packed
+
+
+def shard_offsets(routes, index_at, rows, block_rows, block_stride, width, slot_lo, slot_hi):
+    idx = _blocked(routes, index_at, rows, block_rows, block_stride, width)
+    counts = ((idx >= slot_lo) & (idx < slot_hi)).sum(1)
+    return torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)]).int()
+
+
+def shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
+                  offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
+                  layer_index, out):
+    idx = _blocked(routes, index_at, rows, block_rows, route_stride, width).numpy().astype(np.int64)
+    w = _blocked(routes, weights_at, rows, block_rows, route_stride, width).view(torch.float32).numpy()
+    H, local, D = shard.shape[1:]
+    bank = shard.float().numpy()[0]
+    addresses, deltas, keys = out
+    e = 0
+    for row in range(rows):
+        b, inner = divmod(row, block_rows)
+        block = errors[b * error_stride:(b + 1) * error_stride].numpy()
+        err = block[inner * D:(inner + 1) * D]
+        gate = block[block_rows * D + inner]
+        head, token = row % H, row // H
+        for k in range(width):
+            s = idx[row, k]
+            if slot_lo <= s < slot_lo + local:
+                deltas[e] = torch.from_numpy(gate * bank[head, s - slot_lo] + w[row, k] * err)
+                addresses[e] = head * local + (s - slot_lo)
+                keys[e] = (head * slots + s) * (chunk_size * num_layers) + (chunk_offset + token % tokens) * num_layers + layer_index
+                e += 1
+    assert e == entries
+    return addresses[:entries], deltas[:entries], keys[:entries]
+
+
+def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_base=0):
+    new = oracle.commit(values.float().numpy(), addresses.numpy(), deltas.numpy(), None if keys is None else keys.numpy())
+    out.copy_(torch.from_numpy(new).to(out.dtype))
+    return out
