@@ -252,7 +252,7 @@ def ours(args, w, rank, world, local, dist):
                 "unique_row_fraction": unique_fraction}
 
     # -- end to end from pinned host memory ------------------------------------------------------
-    e2e = end_to_end(args, w, op, epochs[0], dev, dist, world)
+    e2e = None if args.no_e2e else end_to_end(args, w, op, epochs[0], dev, dist, world)
 
     if rank != 0:
         return
@@ -350,6 +350,7 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-input pass (profiling runs)")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.sequences or args.seq_len:

@@ -361,15 +361,20 @@ def shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_str
     return addresses[:entries], deltas[:entries], keys[:entries]
 
 
-_workspaces = {}
+_workspaces = threading.local()
 
 
 def _workspace(device, nbytes):
+    """Scratch for the commit's sort, one buffer per (host thread, device): two threads that
+    enqueue commits on the same stream must not share it, their launches interleave."""
+    table = getattr(_workspaces, "table", None)
+    if table is None:
+        table = _workspaces.table = {}
     key = torch.device(device).index
-    buf = _workspaces.get(key)
+    buf = table.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
+        table[key] = buf
     return buf
 
 

@@ -24,7 +24,6 @@ constexpr int kSortThreads = 256;
 constexpr int kItems = 8;                           // keys per thread in a tile
 constexpr int kTile = kSortThreads * kItems;        // 2048 keys per block
 constexpr int kLongSegment = 256;                   // entries summed strictly in sequence
-constexpr int kScanThreads = 1024;
 
 struct Plan {
   uint32_t skip[kDigits];    // 1 = all keys share this digit
@@ -145,30 +144,41 @@ count_kernel(Workspace w, int64_t entries, int pass) {
   w.tile_count[static_cast<size_t>(threadIdx.x) * w.tiles + blockIdx.x] = local[threadIdx.x];
 }
 
-// Exclusive scan of tile_count ([digit][tile] flattened) by a single block.
-__global__ void __launch_bounds__(kScanThreads)
+// Exclusive scan of tile_count ([digit][tile] flattened): block d owns digit d. Its base is
+// the number of keys with a smaller digit (from the global histogram of this pass); inside
+// the digit the tiles are scanned 256 at a time with a running carry.
+__global__ void __launch_bounds__(kSortThreads)
 scan_kernel(Workspace w, int pass) {
   if (w.plan->skip[pass]) return;
-  __shared__ uint32_t sums[kScanThreads];
-  const int64_t n = static_cast<int64_t>(kRadix) * w.tiles;
-  const int64_t per = (n + kScanThreads - 1) / kScanThreads;
-  const int64_t lo = per * threadIdx.x;
-  const int64_t hi = (lo + per < n) ? lo + per : n;
-  uint32_t total = 0;
-  for (int64_t i = lo; i < hi; ++i) total += w.tile_count[i];
-  sums[threadIdx.x] = total;
+  __shared__ uint32_t part[kSortThreads];
+  __shared__ uint32_t carry;
+  const int d = blockIdx.x;
+  const uint32_t* __restrict__ hist = w.histogram + pass * kRadix;
+  part[threadIdx.x] = (static_cast<int>(threadIdx.x) < d) ? hist[threadIdx.x] : 0u;
   __syncthreads();
-  for (int off = 1; off < kScanThreads; off <<= 1) {
-    const uint32_t add = (threadIdx.x >= off) ? sums[threadIdx.x - off] : 0u;
-    __syncthreads();
-    sums[threadIdx.x] += add;
+  for (int off = kSortThreads / 2; off > 0; off >>= 1) {
+    if (static_cast<int>(threadIdx.x) < off) part[threadIdx.x] += part[threadIdx.x + off];
     __syncthreads();
   }
-  uint32_t run = sums[threadIdx.x] - total;
-  for (int64_t i = lo; i < hi; ++i) {
-    const uint32_t c = w.tile_count[i];
-    w.tile_count[i] = run;
-    run += c;
+  if (threadIdx.x == 0) carry = part[0];
+  __syncthreads();
+  uint32_t* __restrict__ row = w.tile_count + static_cast<size_t>(d) * w.tiles;
+  for (int t0 = 0; t0 < w.tiles; t0 += kSortThreads) {
+    const int t = t0 + threadIdx.x;
+    const uint32_t c = t < w.tiles ? row[t] : 0u;
+    part[threadIdx.x] = c;
+    __syncthreads();
+    for (int off = 1; off < kSortThreads; off <<= 1) {
+      const uint32_t add = (static_cast<int>(threadIdx.x) >= off) ? part[threadIdx.x - off] : 0u;
+      __syncthreads();
+      part[threadIdx.x] += add;
+      __syncthreads();
+    }
+    const uint32_t base = carry;
+    if (t < w.tiles) row[t] = base + part[threadIdx.x] - c;
+    __syncthreads();
+    if (threadIdx.x == kSortThreads - 1) carry = base + part[threadIdx.x];
+    __syncthreads();
   }
 }
 
@@ -298,15 +308,45 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
   *p = __float2bfloat16_rn(v);
 }
 
-// new_row = old_row + acc (one rounding to the bank dtype), for this lane's columns.
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// new_row = old_row + acc (one rounding to the bank dtype), for this lane's columns, moved
+// in the widest unit the lane's column group allows (4 columns: 16 B fp32 / 8 B bf16).
 template <typename T, int V>
-__device__ __forceinline__ void apply_row(const T* in_row, T* out_row,
-                                          const Slice<V>& acc, int lane) {
-  if constexpr (sizeof(T) == 4 && V == 4) {
-    const float4 o = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in_row) + lane * 4);
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + lane * 4) =
-        make_float4(__fadd_rn(o.x, acc.v[0]), __fadd_rn(o.y, acc.v[1]), __fadd_rn(o.z, acc.v[2]),
-                    __fadd_rn(o.w, acc.v[3]));
+__device__ __forceinline__ void apply_row(const T* in_row, T* out_row, const Slice<V>& acc, int lane) {
+  if constexpr (V % 4 == 0) {
+#pragma unroll
+    for (int c = 0; c < V / 4; ++c) {
+      const int col = column_of<V>(lane, c * 4);
+      const float* a = acc.v + c * 4;
+      if constexpr (sizeof(T) == 4) {
+        const float4 o = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in_row) + col);
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out_row) + col) =
+            make_float4(__fadd_rn(o.x, a[0]), __fadd_rn(o.y, a[1]), __fadd_rn(o.z, a[2]), __fadd_rn(o.w, a[3]));
+      } else {
+        const uint2 o = *reinterpret_cast<const uint2*>(in_row + col);
+        uint2 n;
+        n.x = pack_bf16x2(__fadd_rn(bf16_lo(o.x), a[0]), __fadd_rn(bf16_hi(o.x), a[1]));
+        n.y = pack_bf16x2(__fadd_rn(bf16_lo(o.y), a[2]), __fadd_rn(bf16_hi(o.y), a[3]));
+        *reinterpret_cast<uint2*>(out_row + col) = n;
+      }
+    }
+  } else if constexpr (V == 2) {
+    const int col = lane * 2;
+    if constexpr (sizeof(T) == 4) {
+      const float2 o = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(in_row) + col);
+      *reinterpret_cast<float2*>(reinterpret_cast<float*>(out_row) + col) =
+          make_float2(__fadd_rn(o.x, acc.v[0]), __fadd_rn(o.y, acc.v[1]));
+    } else {
+      const uint32_t o = *reinterpret_cast<const uint32_t*>(in_row + col);
+      *reinterpret_cast<uint32_t*>(out_row + col) =
+          pack_bf16x2(__fadd_rn(bf16_lo(o), acc.v[0]), __fadd_rn(bf16_hi(o), acc.v[1]));
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < V; ++i) {
@@ -405,7 +445,16 @@ reduce_kernel(Workspace w, ReduceArgs a) {
       if (lane == 0 && a.device_status) atomicOr(a.device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
       continue;
     }
-    const int64_t len = segment_length(sorted, start, a.entries, address, lane);
+    // The next head inside this warp's 32 positions ends the segment; only a segment that
+    // runs to the end of the batch has to look at the following positions.
+    int64_t len;
+    if (heads) {
+      len = (__ffs(heads) - 1) - h;
+    } else {
+      const int64_t tail = first + 32 < a.entries ? first + 32 : a.entries;
+      len = tail - start;
+      if (tail < a.entries) len = segment_length(sorted, tail - 1, a.entries, address, lane) + (tail - 1 - start);
+    }
     if (len > kLongSegment) {
       if (lane == 0) {
         const uint32_t slot = atomicAdd(&w.plan->long_count, 1u);
@@ -556,7 +605,7 @@ extern "C" int glsdm_commit(const void* values_in, void* values_out, int dtype, 
   GLSDM_CUDA_OK(cudaGetLastError(), "commit plan launch");
   for (int p = 0; p < passes; ++p) {
     count_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
-    scan_kernel<<<1, kScanThreads, 0, stream>>>(w, p);
+    scan_kernel<<<kRadix, kSortThreads, 0, stream>>>(w, p);
     scatter_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
     GLSDM_CUDA_OK(cudaGetLastError(), "commit sort launch");
   }

@@ -53,19 +53,23 @@ __device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t v, int mask) {
   return __shfl_xor_sync(kFullMask, v, mask);
 }
 
+// One compare-exchange step across lanes: the lane keeps the larger of (own, partner) when
+// keep_max, else the smaller.
+__device__ __forceinline__ uint64_t exchange_step(uint64_t x, int j, bool keep_max) {
+  const uint64_t y = shfl_xor_u64(x, j);
+  const bool take = (y > x) == keep_max;  // equal keys (both empty): either choice is the same
+  return take ? y : x;
+}
+
 // Bitonic sort of one 64-bit key per lane, descending (lane 0 ends with the largest).
 __device__ __forceinline__ uint64_t warp_sort_desc(uint64_t x, int lane) {
 #pragma unroll
   for (int k = 2; k <= 32; k <<= 1) {
 #pragma unroll
     for (int j = k >> 1; j > 0; j >>= 1) {
-      const uint64_t y = shfl_xor_u64(x, j);
       const bool up = (lane & k) == 0;
       const bool lower = (lane & j) == 0;
-      const bool keep_max = (up == lower);
-      const uint64_t hi = x > y ? x : y;
-      const uint64_t lo = x > y ? y : x;
-      x = keep_max ? hi : lo;
+      x = exchange_step(x, j, up == lower);
     }
   }
   return x;
@@ -76,13 +80,7 @@ __device__ __forceinline__ uint64_t warp_merge_desc(uint64_t list, uint64_t sort
   const uint64_t rev = shfl_u64(sorted, 31 - lane);
   uint64_t x = list > rev ? list : rev;  // bitonic, holds the 32 largest of the union
 #pragma unroll
-  for (int j = 16; j > 0; j >>= 1) {
-    const uint64_t y = shfl_xor_u64(x, j);
-    const bool lower = (lane & j) == 0;
-    const uint64_t hi = x > y ? x : y;
-    const uint64_t lo = x > y ? y : x;
-    x = lower ? hi : lo;
-  }
+  for (int j = 16; j > 0; j >>= 1) x = exchange_step(x, j, (lane & j) == 0);
   return x;
 }
 

@@ -1,6 +1,556 @@
+// Dense-key routing: scores = queries x keys^T on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), fused with a running per-row top-k in the
+// epilogue, so the [rows, slots] score matrix never leaves the SM.
+//
+// One persistent CTA per SM, 10 warps:
+//   warp 0     TMA producer: the unit's query tile (2 x 128 rows) once, then key tiles of
+//              128 slots through a 3-stage shared-memory ring (128-byte swizzle, K-major)
+//   warp 1     allocates tensor memory (512 columns) and issues tcgen05.mma from one thread:
+//              per key tile, 2 row blocks x dk/16 instructions of shape 128 x 128 x 16
+//              (bf16 in, fp32 accumulate); accumulators are double-buffered in tensor memory
+//   warps 2-9  epilogue: thread = one query row; tcgen05.ld 32 columns at a time, a running
+//              max against the row's current k-th score rejects most column groups with one
+//              compare; survivors are inserted into the row's sorted list in shared memory
+// A unit is (pair of 128-row blocks, one split of the slot range). Each unit writes its
+// rows' best `width` (score, slot) pairs; with more than one split a small merge kernel
+// reduces the splits. Units are ordered split-major so that the CTAs running at the same time
+// stream the same keys and share them through L2.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out the CTA raises a shared abort
+// flag, sets GLSDM_DEV_WAIT_EXPIRED in the caller's status word, drains its outstanding
+// loads (bounded again), frees its tensor memory and returns.
+//
+// Tie rule (gl_sdm/memory/routing.py:21-24): equal scores prefer the larger slot. Slots are
+// scanned in ascending order, so a score equal to the current k-th one replaces it.
+#include <cuda.h>
+
 #include "common.cuh"
-extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t, int64_t, int32_t, int32_t) { return 0; }
-extern "C" int glsdm_score_topk(const void*, const void*, int64_t, int64_t, int32_t, int32_t, int64_t,
-                                float*, int32_t*, void*, size_t, uint32_t*, glsdm_stream_t) {
-  return GLSDM_ERR_UNSUPPORTED;
+
+namespace glsdm {
+namespace {
+
+constexpr int kBlockRows = 128;                 // rows of one MMA (M)
+constexpr int kUnitRows = 2 * kBlockRows;       // rows handled by one CTA unit
+constexpr int kTileCols = 128;                  // slots per key tile (MMA N)
+constexpr int kStages = 3;
+constexpr int kAtomK = 64;                      // bf16 elements per 128-byte swizzle row
+constexpr int kSubTileBytes = kBlockRows * 128; // one [128 x 64] bf16 sub-tile, 16 KB
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+constexpr int kTmemCols = 512;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct Params {
+  int64_t rows;
+  int64_t slots;
+  int64_t col_base;
+  int dk;
+  int width;
+  int splits;
+  int tiles_per_split;
+  int tiles_total;
+  int unit_pairs;       // ceil(rows / 256)
+  float* out_score;     // [splits][rows][width] (or the final output when splits == 1)
+  int32_t* out_slot;
+  uint32_t* device_status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded wait. Returns false when the wait ran out or another role has aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
+  d |= static_cast<uint64_t>(1) << 46;                            // version
+  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileCols >> 3) << 17) |
+                                ((kBlockRows >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(acc)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct Barriers {
+  uint64_t a_full;
+  uint64_t a_empty;
+  uint64_t b_full[kStages];
+  uint64_t b_empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Shared memory: [A: 2 row blocks x kb sub-tiles][B: stages x kb sub-tiles][lists][barriers]
+template <int KB>
+struct Layout {
+  static constexpr int kA = 2 * KB * kSubTileBytes;
+  static constexpr int kB = kStages * KB * kSubTileBytes;
+  static constexpr int kListOffset = kA + kB;
+  __host__ __device__ static constexpr int list_bytes(int width) { return 8 * width * 32 * kEpilogueWarps; }
+  __host__ __device__ static constexpr int total(int width) { return kListOffset + list_bytes(width) + static_cast<int>(sizeof(Barriers)) + 1024; }
+};
+
+template <int KB>
+__global__ void __launch_bounds__(kThreads, 1)
+score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Params p) {
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + Layout<KB>::kA;
+  float* list_val = reinterpret_cast<float*>(smem + Layout<KB>::kListOffset);
+  int32_t* list_idx = reinterpret_cast<int32_t*>(list_val + p.width * 32 * kEpilogueWarps);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + Layout<KB>::kListOffset + Layout<KB>::list_bytes(p.width));
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->a_full, 1);
+    mbar_init(&bars->a_empty, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->b_full[s], 1);
+      mbar_init(&bars->b_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], kEpilogueWarps);
+    }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int units = p.unit_pairs * p.splits;
+  constexpr uint32_t kTileBytes = KB * kSubTileBytes;
+  // Thread 0 only: for every stage, whether a key tile was ever requested and under which
+  // barrier parity the latest request completes (used to drain loads after an abort).
+  uint32_t issued_mask = 0, issued_parity = 0;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, b_phase = 0, a_phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
+        // the previous unit's MMAs must have finished reading the query tile
+        if (unit != static_cast<int>(blockIdx.x)) {
+          ok = mbar_wait(&bars->a_empty, a_phase, abort_flag);
+          a_phase ^= 1u;
+          if (!ok) break;
+        }
+        mbar_expect_tx(&bars->a_full, 2 * kTileBytes);
+        for (int mb = 0; mb < 2; ++mb)
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_2d(smem_a + (mb * KB + kb) * kSubTileBytes, &map_q, kb * kAtomK,
+                        pair * kUnitRows + mb * kBlockRows, &bars->a_full);
+        const int t0 = split * p.tiles_per_split;
+        const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+        for (int t = t0; t < t1; ++t) {
+          ok = mbar_wait(&bars->b_empty[stage], b_phase ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&bars->b_full[stage], kTileBytes);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_2d(smem_b + (stage * KB + kb) * kSubTileBytes, &map_k, kb * kAtomK, t * kTileCols,
+                        &bars->b_full[stage]);
+          issued_mask |= 1u << stage;
+          issued_parity = (issued_parity & ~(1u << stage)) | (b_phase << stage);
+          if (++stage == kStages) { stage = 0; b_phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, b_phase = 0, a_phase = 0, acc_phase[2] = {0, 0};
+      uint32_t tile_counter = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int split = unit / p.unit_pairs;
+        ok = mbar_wait(&bars->a_full, a_phase, abort_flag);
+        a_phase ^= 1u;
+        if (!ok) break;
+        const int t0 = split * p.tiles_per_split;
+        const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+        for (int t = t0; t < t1; ++t, ++tile_counter) {
+          const uint32_t buf = tile_counter & 1u;
+          ok = mbar_wait(&bars->b_full[stage], b_phase, abort_flag);
+          if (!ok) break;
+          ok = mbar_wait(&bars->acc_empty[buf], acc_phase[buf] ^ 1u, abort_flag);
+          if (!ok) break;
+          acc_phase[buf] ^= 1u;
+          tc_fence_after();
+#pragma unroll
+          for (int mb = 0; mb < 2; ++mb) {
+            const uint32_t d = tmem_base + buf * (2 * kTileCols) + mb * kTileCols;
+#pragma unroll
+            for (int kk = 0; kk < KB * 4; ++kk) {
+              const uint32_t a_addr = smem_u32(smem_a + (mb * KB + kk / 4) * kSubTileBytes) + (kk % 4) * 32;
+              const uint32_t b_addr = smem_u32(smem_b + (stage * KB + kk / 4) * kSubTileBytes) + (kk % 4) * 32;
+              umma_bf16(d, umma_desc(a_addr), umma_desc(b_addr), kk > 0);
+            }
+          }
+          umma_commit(&bars->b_empty[stage]);   // the stage is free once these MMAs have read it
+          umma_commit(&bars->acc_full[buf]);    // the accumulators are complete
+          if (++stage == kStages) { stage = 0; b_phase ^= 1u; }
+        }
+        umma_commit(&bars->a_empty);            // the query tile may be overwritten
+      }
+      // The last commit's arrival must land before this CTA's shared memory is released.
+      if (ok && static_cast<int>(blockIdx.x) < units) {
+        const int done = (units - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1;
+        mbar_wait(&bars->a_empty, static_cast<uint32_t>(done - 1) & 1u, abort_flag);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;                    // 0..7
+    const int mb = ew >> 2;                     // row block of this warp
+    const int quarter = warp & 3;               // tensor-memory lane quarter this warp may read
+    const int row_in_unit = mb * kBlockRows + quarter * 32 + lane;
+    const int et = ew * 32 + lane;              // epilogue thread id, 0..255
+    const int stride = 32 * kEpilogueWarps;
+    float* val = list_val + et;
+    int32_t* idx = list_idx + et;
+    const int K = p.width;
+    uint32_t acc_phase[2] = {0, 0};
+    uint32_t tile_counter = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
+      for (int k = 0; k < K; ++k) { val[k * stride] = -INFINITY; idx[k * stride] = -1; }
+      float floor = -INFINITY;
+      const int t0 = split * p.tiles_per_split;
+      const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+      for (int t = t0; t < t1; ++t, ++tile_counter) {
+        const uint32_t buf = tile_counter & 1u;
+        ok = mbar_wait(&bars->acc_full[buf], acc_phase[buf], abort_flag);
+        if (!ok) break;
+        acc_phase[buf] ^= 1u;
+        tc_fence_after();
+        const int64_t col0 = static_cast<int64_t>(t) * kTileCols;
+        const int64_t left = p.slots - col0;
+        const int live_cols = left < kTileCols ? static_cast<int>(left) : kTileCols;
+#pragma unroll 1
+        for (int c = 0; c < kTileCols / 32; ++c) {
+          uint32_t r[32];
+          tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * (2 * kTileCols) +
+                          mb * kTileCols + c * 32, r);
+          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]),
+                m3 = __uint_as_float(r[3]);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));
+            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+          }
+          const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          if (best >= floor) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float v = __uint_as_float(r[i]);
+              const int col = c * 32 + i;
+              if (v >= floor && col < live_cols) {
+                // insert keeping the list sorted, best first; equal scores rank the new
+                // (larger) slot ahead of the old ones
+                int at = K - 1;
+                while (at > 0 && val[(at - 1) * stride] <= v) {
+                  val[at * stride] = val[(at - 1) * stride];
+                  idx[at * stride] = idx[(at - 1) * stride];
+                  --at;
+                }
+                val[at * stride] = v;
+                idx[at * stride] = static_cast<int32_t>(p.col_base + col0 + col);
+                floor = val[(K - 1) * stride];
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      }
+      if (!ok) break;
+      const int64_t row = static_cast<int64_t>(pair) * kUnitRows + row_in_unit;
+      if (row < p.rows) {
+        float* so = p.out_score + (static_cast<int64_t>(split) * p.rows + row) * K;
+        int32_t* io = p.out_slot + (static_cast<int64_t>(split) * p.rows + row) * K;
+        for (int k = 0; k < K; ++k) { so[k] = val[k * stride]; io[k] = idx[k * stride]; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.device_status != nullptr) atomicOr(p.device_status, GLSDM_DEV_WAIT_EXPIRED);
+    // Key tiles that were requested but never consumed still write shared memory: give
+    // the latest request of each stage a bounded chance to land before the CTA exits.
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        if (!(issued_mask & (1u << s))) continue;
+        for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+          if (mbar_try_wait(&bars->b_full[s], (issued_parity >> s) & 1u)) break;
+      }
+    }
+    __syncthreads();
+  }
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+// Merge of the per-split candidate lists of each row, best first (score desc, slot desc).
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+split_merge_kernel(const float* __restrict__ cand_score, const int32_t* __restrict__ cand_slot, int splits,
+                   int64_t rows, int width, float* __restrict__ out_score, int32_t* __restrict__ out_slot) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  WarpSelect sel;
+  sel.init(stage[warp], width, lane);
+  for (int s = 0; s < splits; ++s) {
+    const int64_t at = (static_cast<int64_t>(s) * rows + row) * width + lane;
+    uint64_t key = 0;
+    if (lane < width) {
+      const int32_t slot = cand_slot[at];
+      if (slot >= 0) key = pack_key(orderable_bits(cand_score[at]), static_cast<uint32_t>(slot));
+    }
+    sel.offer(key);
+  }
+  sel.finish();
+  if (lane < width) {
+    const bool live = sel.list != 0;
+    out_score[row * width + lane] = live ? from_orderable_bits(static_cast<uint32_t>(sel.list >> 32)) : -INFINITY;
+    out_slot[row * width + lane] = live ? static_cast<int32_t>(static_cast<uint32_t>(sel.list)) : -1;
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(sym);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, dk] with a row pitch of `pitch` elements; boxes of [128 rows x 64].
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int dk, int64_t pitch) {
+  EncodeTiled enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(dk), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * 2};
+  const cuuint32_t box[2] = {kAtomK, kBlockRows};
+  const cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Plan {
+  int unit_pairs, tiles_total, splits, tiles_per_split;
+};
+
+// Pick the number of slot-range splits: enough units to fill the SMs in whole waves, while
+// every split keeps at least 32 key tiles.
+Plan make_plan(int64_t rows, int64_t slots, int sms) {
+  Plan pl;
+  pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
+  pl.tiles_total = static_cast<int>((slots + kTileCols - 1) / kTileCols);
+  const int max_splits = pl.tiles_total / 32 > 0 ? (pl.tiles_total / 32 < 64 ? pl.tiles_total / 32 : 64) : 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= max_splits; ++s) {
+    const int64_t units = static_cast<int64_t>(pl.unit_pairs) * s;
+    const int64_t waves = (units + sms - 1) / sms;
+    const double eff = static_cast<double>(units) / static_cast<double>(waves * sms);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+  }
+  pl.splits = best;
+  pl.tiles_per_split = (pl.tiles_total + best - 1) / best;
+  pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
+  return pl;
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+      sms = 148;
+  }
+  return sms;
+}
+
+}  // namespace
+}  // namespace glsdm
+
+using namespace glsdm;
+
+extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
+  (void)dk;
+  if (rows < 1 || slots < 1 || width < 1) return 0;
+  const Plan pl = make_plan(rows, slots, sm_count());
+  if (pl.splits <= 1) return 256;
+  return static_cast<size_t>(pl.splits) * rows * width * 8 + 512;
+}
+
+extern "C" int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_t slots, int32_t dk,
+                                int32_t width, int64_t col_base, float* out_score, int32_t* out_slot,
+                                void* workspace, size_t workspace_bytes, uint32_t* device_status,
+                                glsdm_stream_t stream) {
+  if (queries == nullptr || keys == nullptr || out_score == nullptr || out_slot == nullptr) return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || slots < 1 || width < 1 || col_base < 0) return GLSDM_ERR_ARGUMENT;
+  if (dk != 64 && dk != 128) return GLSDM_ERR_UNSUPPORTED;
+  if (width > 32 || col_base + slots > 0x7fffffffll) return GLSDM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
+  if (rows == 0) return GLSDM_OK;
+  const int sms = sm_count();
+  const Plan pl = make_plan(rows, slots, sms);
+  Params p;
+  p.rows = rows;
+  p.slots = slots;
+  p.col_base = col_base;
+  p.dk = dk;
+  p.width = width;
+  p.splits = pl.splits;
+  p.tiles_per_split = pl.tiles_per_split;
+  p.tiles_total = pl.tiles_total;
+  p.unit_pairs = pl.unit_pairs;
+  p.device_status = device_status;
+  if (pl.splits > 1) {
+    const size_t need = static_cast<size_t>(pl.splits) * rows * width * 8;
+    if (workspace == nullptr || workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
+    p.out_score = static_cast<float*>(workspace);
+    p.out_slot = reinterpret_cast<int32_t*>(static_cast<float*>(workspace) + static_cast<size_t>(pl.splits) * rows * width);
+  } else {
+    p.out_score = out_score;
+    p.out_slot = out_slot;
+  }
+  CUtensorMap map_q, map_k;
+  if (!make_map(&map_q, queries, rows, dk, dk) || !make_map(&map_k, keys, slots, dk, dk)) {
+    note_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+    return GLSDM_ERR_CUDA;
+  }
+  const int units = pl.unit_pairs * pl.splits;
+  const int grid = units < sms ? units : sms;
+  if (dk == 128) {
+    const int smem = Layout<2>::total(width);
+    GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                  "score_topk shared memory");
+    score_topk_kernel<2><<<grid, kThreads, smem, stream>>>(map_q, map_k, p);
+  } else {
+    const int smem = Layout<1>::total(width);
+    GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                  "score_topk shared memory");
+    score_topk_kernel<1><<<grid, kThreads, smem, stream>>>(map_q, map_k, p);
+  }
+  GLSDM_CUDA_OK(cudaGetLastError(), "score_topk launch");
+  count_launches(1);
+  if (pl.splits > 1) {
+    split_merge_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+        p.out_score, p.out_slot, pl.splits, rows, width, out_score, out_slot);
+    GLSDM_CUDA_OK(cudaGetLastError(), "score_topk merge launch");
+    count_launches(1);
+  }
+  return GLSDM_OK;
 }
