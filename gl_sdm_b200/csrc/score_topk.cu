@@ -142,7 +142,29 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Insert the keys of the lanes in `m` into their rows' sorted lists. Lane j holds entry j of
+// the row being updated; a ballot counts the entries above the new key and the tail moves
+// down one lane. Kept out of line: it is called from 128 unrolled column tests per tile.
+__device__ __noinline__ void insert_events(unsigned m, uint64_t mine, uint64_t* list, float* floor_s, int K,
+                                           int lane) {
+  while (m) {
+    const int src = __ffs(m) - 1;
+    m &= m - 1;
+    const uint64_t key = shfl_u64(mine, src);
+    uint64_t* row_list = list + src * 32;
+    const uint64_t e = row_list[lane];
+    const int pos = __popc(__ballot_sync(kFullMask, e > key));
+    if (pos < K) {
+      const uint64_t up = __shfl_up_sync(kFullMask, e, 1);
+      const uint64_t ne = lane < pos ? e : (lane == pos ? key : up);
+      row_list[lane] = ne;
+      if (lane == K - 1) floor_s[src] = ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+    }
+  }
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -165,8 +187,10 @@ struct Layout {
   static constexpr int kA = 2 * KB * kSubTileBytes;
   static constexpr int kB = kStages * KB * kSubTileBytes;
   static constexpr int kListOffset = kA + kB;
-  __host__ __device__ static constexpr int list_bytes(int width) { return 8 * width * 32 * kEpilogueWarps; }
-  __host__ __device__ static constexpr int total(int width) { return kListOffset + list_bytes(width) + static_cast<int>(sizeof(Barriers)) + 1024; }
+  __host__ __device__ static constexpr int list_bytes(int) { return 8 * 32 * 32 * kEpilogueWarps; }
+  __host__ __device__ static constexpr int total(int width) {
+    return kListOffset + list_bytes(width) + static_cast<int>(sizeof(Barriers)) + 4 * 32 * kEpilogueWarps + 1024;
+  }
 };
 
 template <int KB>
@@ -177,7 +201,6 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + Layout<KB>::kA;
   float* list_val = reinterpret_cast<float*>(smem + Layout<KB>::kListOffset);
-  int32_t* list_idx = reinterpret_cast<int32_t*>(list_val + p.width * 32 * kEpilogueWarps);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + Layout<KB>::kListOffset + Layout<KB>::list_bytes(p.width));
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -291,21 +314,27 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    // A warp owns 32 query rows (lane = row). Each row keeps its 32 best keys
+    // (orderable score << 32 | slot - col_base), sorted best first, in shared memory as
+    // list[row][32]. Column groups are rejected with a running max against the row's floor
+    // (its current k-th score). A surviving score is inserted by the WHOLE warp: lane j holds
+    // entry j of that row's list, a ballot counts the entries above the new key, and the
+    // tail shifts down by one lane - about a dozen instructions whatever the list length.
     const int ew = warp - 2;                    // 0..7
     const int mb = ew >> 2;                     // row block of this warp
     const int quarter = warp & 3;               // tensor-memory lane quarter this warp may read
     const int row_in_unit = mb * kBlockRows + quarter * 32 + lane;
-    const int et = ew * 32 + lane;              // epilogue thread id, 0..255
-    const int stride = 32 * kEpilogueWarps;
-    float* val = list_val + et;
-    int32_t* idx = list_idx + et;
+    uint64_t* list = reinterpret_cast<uint64_t*>(list_val) + static_cast<size_t>(ew) * 32 * 32;
+    float* floor_s = reinterpret_cast<float*>(bars + 1) + ew * 32;
     const int K = p.width;
     uint32_t acc_phase[2] = {0, 0};
     uint32_t tile_counter = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
       const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
-      for (int k = 0; k < K; ++k) { val[k * stride] = -INFINITY; idx[k * stride] = -1; }
+      for (int r = 0; r < 32; ++r) list[r * 32 + lane] = 0;
+      floor_s[lane] = -INFINITY;
+      __syncwarp();
       float floor = -INFINITY;
       const int t0 = split * p.tiles_per_split;
       const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
@@ -318,53 +347,59 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int64_t col0 = static_cast<int64_t>(t) * kTileCols;
         const int64_t left = p.slots - col0;
         const int live_cols = left < kTileCols ? static_cast<int>(left) : kTileCols;
-#pragma unroll 1
-        for (int c = 0; c < kTileCols / 32; ++c) {
-          uint32_t r[32];
-          tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * (2 * kTileCols) +
-                          mb * kTileCols + c * 32, r);
-          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]),
-                m3 = __uint_as_float(r[3]);
-#pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(r[i]));
-            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
-          }
-          const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-          if (best >= floor) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float v = __uint_as_float(r[i]);
-              const int col = c * 32 + i;
-              if (v >= floor && col < live_cols) {
-                // insert keeping the list sorted, best first; equal scores rank the new
-                // (larger) slot ahead of the old ones
-                int at = K - 1;
-                while (at > 0 && val[(at - 1) * stride] <= v) {
-                  val[at * stride] = val[(at - 1) * stride];
-                  idx[at * stride] = idx[(at - 1) * stride];
-                  --at;
-                }
-                val[at * stride] = v;
-                idx[at * stride] = static_cast<int32_t>(p.col_base + col0 + col);
-                floor = val[(K - 1) * stride];
-              }
-            }
-          }
-        }
+        // The whole 128-column row slice moves to registers at once; the accumulator buffer
+        // is handed back to the MMA warp before the scan, so inserts never stall the MMAs
+        // unless this warp falls a full tile behind.
+        uint32_t r[kTileCols];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * (2 * kTileCols) +
+                               mb * kTileCols;
+        tmem_load32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_load32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_load32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(&r[64]));
+        tmem_load32(taddr + 96, *reinterpret_cast<uint32_t(*)[32]>(&r[96]));
+        tmem_wait_loads();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+#pragma unroll
+        for (int c = 0; c < kTileCols / 32; ++c) {
+          float m0 = __uint_as_float(r[c * 32]), m1 = __uint_as_float(r[c * 32 + 1]),
+                m2 = __uint_as_float(r[c * 32 + 2]), m3 = __uint_as_float(r[c * 32 + 3]);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[c * 32 + i]));
+            m1 = fmaxf(m1, __uint_as_float(r[c * 32 + i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[c * 32 + i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(r[c * 32 + i + 3]));
+          }
+          const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          if (!__any_sync(kFullMask, best >= floor)) continue;
+          const uint32_t slot0 = static_cast<uint32_t>(col0) + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // every column of the group is tested against the floor the group started with
+            // (no dependency between iterations); the insert itself re-checks the position
+            const float v = __uint_as_float(r[c * 32 + i]);
+            const unsigned m = __ballot_sync(kFullMask, v >= floor && c * 32 + i < live_cols);
+            if (m) insert_events(m, pack_key(orderable_bits(v), slot0 + i), list, floor_s, K, lane);
+          }
+          __syncwarp();
+          floor = floor_s[lane];
+        }
       }
       if (!ok) break;
-      const int64_t row = static_cast<int64_t>(pair) * kUnitRows + row_in_unit;
-      if (row < p.rows) {
-        float* so = p.out_score + (static_cast<int64_t>(split) * p.rows + row) * K;
-        int32_t* io = p.out_slot + (static_cast<int64_t>(split) * p.rows + row) * K;
-        for (int k = 0; k < K; ++k) { so[k] = val[k * stride]; io[k] = idx[k * stride]; }
+      __syncwarp();
+      // lane j writes entry j of each of the warp's rows: coalesced [row][width] stores
+      for (int r = 0; r < 32; ++r) {
+        const int64_t row = static_cast<int64_t>(pair) * kUnitRows + (row_in_unit - lane) + r;
+        if (row < p.rows && lane < K) {
+          const uint64_t e = list[r * 32 + lane];
+          const int64_t at = (static_cast<int64_t>(split) * p.rows + row) * K + lane;
+          p.out_score[at] = e ? from_orderable_bits(static_cast<uint32_t>(e >> 32)) : -INFINITY;
+          p.out_slot[at] = e ? static_cast<int32_t>(p.col_base + static_cast<uint32_t>(e)) : -1;
+        }
       }
+      __syncwarp();
     }
   }
 
@@ -449,13 +484,15 @@ struct Plan {
   int unit_pairs, tiles_total, splits, tiles_per_split;
 };
 
-// Pick the number of slot-range splits: enough units to fill the SMs in whole waves, while
-// every split keeps at least 32 key tiles.
+// Pick the number of slot-range splits. Every split restarts its rows' lists from nothing and
+// pays the insert-heavy start again (about k*ln(columns/k) inserts per row), so the slot range
+// is split only into pieces of at least 8192 key tiles (1M slots), and only as far as that
+// fills the SMs in whole waves.
 Plan make_plan(int64_t rows, int64_t slots, int sms) {
   Plan pl;
   pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
   pl.tiles_total = static_cast<int>((slots + kTileCols - 1) / kTileCols);
-  const int max_splits = pl.tiles_total / 32 > 0 ? (pl.tiles_total / 32 < 64 ? pl.tiles_total / 32 : 64) : 1;
+  const int max_splits = pl.tiles_total / 8192 > 0 ? (pl.tiles_total / 8192 < 64 ? pl.tiles_total / 8192 : 64) : 1;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= max_splits; ++s) {
