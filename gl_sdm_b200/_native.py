@@ -53,6 +53,8 @@ SIGNATURES = {
                                  _i32, _i32, _p, _p, _p, _p]),
     "glsdm_commit_workspace_bytes": (_sz, [_i64, _i32]),
     "glsdm_commit": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p]),
+    "glsdm_commit_static": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _p]),
+    "glsdm_commit_static_max_entries": (_i64, []),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
     "glsdm_score_topk": (_i, [_p, _p, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),

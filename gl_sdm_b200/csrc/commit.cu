@@ -12,6 +12,8 @@
 //                  kLongSegment are queued
 //   6. long        one block per queued segment: fixed 256-entry chunks summed left to
 //                  right by warps, chunk sums added left to right, row updated
+#include <mutex>
+
 #include "common.cuh"
 
 namespace glsdm {
@@ -625,3 +627,62 @@ extern "C" int glsdm_commit(const void* values_in, void* values_out, int dtype, 
   if (dtype == GLSDM_F32) return launch_reduce<float>(w, a, stream);
   return launch_reduce<__nv_bfloat16>(w, a, stream);
 }
+
+// ---- commit without a caller-provided workspace -------------------------------------------
+//
+// Some hosts of this library have nowhere to get the commit's scratch from. A plain C or C++
+// embedder of the C ABI has no tensor allocator to size a workspace with; and a serving loop
+// that shares the GPU with other streams must keep cudaMalloc/cudaFree out of its request path,
+// because those calls synchronise the whole device and stall everybody else's work. For them
+// the scratch lives in the library image itself: a fixed array in device memory that every
+// GPU which loads the library carries until the process exits.
+namespace glsdm {
+namespace {
+
+constexpr int64_t kStaticMaxEntries = 65536;   // entries per commit the built-in scratch covers
+constexpr int32_t kStaticMaxDim = 256;         // widest value row it covers
+constexpr size_t kStaticScratchBytes = 4u << 20;
+
+static __device__ __align__(256) unsigned char g_commit_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_address[kMaxDevices] = {};
+
+// In host code `g_commit_scratch` is only a handle for the symbol, not a device address;
+// the address each device gave the array has to be asked for, once, with that device current.
+int static_scratch(void** out) {
+  int device = -1;
+  GLSDM_CUDA_OK(cudaGetDevice(&device), "commit_static cudaGetDevice");
+  if (device < 0 || device >= kMaxDevices) return GLSDM_ERR_LIMIT;
+  std::lock_guard<std::mutex> hold(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    GLSDM_CUDA_OK(cudaGetSymbolAddress(&address, g_commit_scratch), "commit_static cudaGetSymbolAddress");
+    if (address == nullptr) return GLSDM_ERR_CUDA;
+    g_scratch_address[device] = address;
+  }
+  *out = g_scratch_address[device];
+  return GLSDM_OK;
+}
+
+}  // namespace
+}  // namespace glsdm
+
+extern "C" int glsdm_commit_static(const void* values_in, void* values_out, int dtype, int64_t row_base,
+                                   int64_t bank_rows, int32_t dim, const int64_t* addresses,
+                                   const float* deltas, const int64_t* keys, int64_t entries,
+                                   int32_t key_bits, uint32_t* device_status, glsdm_stream_t stream) {
+  if (entries < 0 || dim < 1) return GLSDM_ERR_ARGUMENT;
+  if (entries > kStaticMaxEntries || dim > kStaticMaxDim) return GLSDM_ERR_LIMIT;
+  if (carve(nullptr, nullptr, entries < 1 ? 1 : entries, dim) > kStaticScratchBytes) return GLSDM_ERR_LIMIT;
+  void* scratch = nullptr;
+  if (int s = static_scratch(&scratch)) return s;
+  // The array still holds whatever the previous call left; glsdm_commit clears the digit
+  // histogram and its plan kernel resets the queue counters, nothing else is read before it
+  // is written.
+  return glsdm_commit(values_in, values_out, dtype, row_base, bank_rows, dim, addresses, deltas, keys, entries,
+                      key_bits, scratch, kStaticScratchBytes, device_status, stream);
+}
+
+extern "C" int64_t glsdm_commit_static_max_entries(void) { return glsdm::kStaticMaxEntries; }

@@ -195,6 +195,26 @@ int glsdm_commit(const void* values_in, void* values_out, int dtype, int64_t row
                  const int64_t* keys, int64_t entries, int32_t key_bits, void* workspace,
                  size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
 
+/* Commit for hosts that cannot provide a workspace. It has no counterpart in the reference
+ * (whose commit allocates freely through PyTorch). Same arguments and result as glsdm_commit,
+ * minus the workspace: the sort/reduce scratch is a 4 MiB array built into the library's
+ * device image, held by every GPU that loads the library until the process exits. Meant for
+ * plain C/C++ embedders without a tensor allocator, and for serving loops that must keep
+ * cudaMalloc/cudaFree (which synchronise the whole device) off their request path. This call
+ * allocates nothing and frees nothing.
+ *   Limits: entries <= glsdm_commit_static_max_entries() (65536) and dim <= 256; larger
+ *   requests return GLSDM_ERR_LIMIT and touch nothing.
+ *   The first call on each device looks up the array's address (cudaGetSymbolAddress) with
+ *   that device current; make that first call before any stream capture begins.
+ *   All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *   (different streams without an ordering between them) race and corrupt each other's
+ *   commit. Issue them on one stream, or order the streams with events. */
+int glsdm_commit_static(const void* values_in, void* values_out, int dtype, int64_t row_base,
+                        int64_t bank_rows, int32_t dim, const int64_t* addresses,
+                        const float* deltas, const int64_t* keys, int64_t entries, int32_t key_bits,
+                        uint32_t* device_status, glsdm_stream_t stream);
+int64_t glsdm_commit_static_max_entries(void);
+
 /* Dense-key routing (flat keys): scores = queries x keys^T on the tensor cores, fused with
  * a running per-row top-k, so the [rows, slots] score matrix is never stored. The
  * reference has no per-slot key tensor; its nearest interface is the score GEMM of
