@@ -408,22 +408,29 @@ def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_
     return out
 
 
-def topk_merge(cand_score, cand_slot, index_dtype=torch.int64):
+def topk_merge(cand_score, cand_slot, index_dtype=torch.int64, out=None):
     """cand_* [parts, rows..., k] -> (index [rows..., k] ascending, softmax weights)."""
     require_cuda(cand_score, cand_slot)
     if cand_score.dtype != torch.float32 or cand_slot.dtype != torch.int32:
         raise ValueError("candidates are float32 scores with int32 slots")
     parts, width = cand_score.shape[0], cand_score.shape[-1]
     rows = cand_score.numel() // (parts * width)
-    index = torch.empty(cand_score.shape[1:], dtype=index_dtype, device=cand_score.device)
-    weights = torch.empty(cand_score.shape[1:], dtype=torch.float32, device=cand_score.device)
+    if out is None:
+        index = torch.empty(cand_score.shape[1:], dtype=index_dtype, device=cand_score.device)
+        weights = torch.empty(cand_score.shape[1:], dtype=torch.float32, device=cand_score.device)
+    else:
+        index, weights = out
+        require_cuda(index, weights)
+        index_dtype = index.dtype
+        if index.numel() != rows * width or weights.numel() != rows * width or weights.dtype != torch.float32:
+            raise ValueError("preallocated route buffers have the wrong size")
     _check(library().glsdm_topk_merge(_ptr(cand_score), _ptr(cand_slot), parts, rows, width, _ptr(index),
                                       int(index_dtype == torch.int64), _ptr(weights),
                                       _stream(cand_score.device)))
     return index, weights
 
 
-def score_topk(queries, keys, width, col_base=0):
+def score_topk(queries, keys, width, col_base=0, out=None):
     """Dense-key routing of one shard: best `width` (score, slot) per query row, best first."""
     require_cuda(queries, keys)
     if queries.dtype != torch.bfloat16 or keys.dtype != torch.bfloat16:
@@ -433,8 +440,14 @@ def score_topk(queries, keys, width, col_base=0):
     lib = library()
     nbytes = lib.glsdm_score_topk_workspace_bytes(rows, slots, dk, width)
     work = _workspace(queries.device, nbytes)
-    score = torch.empty((rows, width), dtype=torch.float32, device=queries.device)
-    slot = torch.empty((rows, width), dtype=torch.int32, device=queries.device)
+    if out is None:
+        score = torch.empty((rows, width), dtype=torch.float32, device=queries.device)
+        slot = torch.empty((rows, width), dtype=torch.int32, device=queries.device)
+    else:
+        score, slot = out
+        require_cuda(score, slot)
+        if score.numel() != rows * width or slot.numel() != rows * width or score.dtype != torch.float32 or slot.dtype != torch.int32:
+            raise ValueError("preallocated candidate buffers have the wrong size or type")
     _check(lib.glsdm_score_topk(_ptr(queries), _ptr(keys), rows, slots, dk, width, col_base, _ptr(score),
                                 _ptr(slot), _ptr(work), work.numel(), _ptr(status_word(queries.device)),
                                 _stream(queries.device)))

@@ -2,19 +2,23 @@
 
 The reference is single-GPU (no torch.distributed anywhere); this is the multi-GPU design of
 the same operator. Rank r of R owns the contiguous slot block [r*S/R, (r+1)*S/R) of every head
-(for product keys: a block of left-factor indices). Tokens are data-parallel: each rank routes
-its own tokens, whose factor scores already cover all slots. Per 512-token commit epoch there
-are three collectives, none of them inside a kernel:
+(and, in dense-key mode, the same block of key rows). Tokens are data-parallel. Per 512-token
+commit epoch, all collectives run between kernels, never inside one:
 
-  1. all-gather of the routes (int32 slot + fp32 weight, query and write side): K candidates
-     per token instead of value rows;
-  2. every rank forms partial readings of ALL tokens over the rows it owns; a reduce-scatter
-     returns each rank the finished readings / write predictions of its own tokens;
-  3. at the commit clock the write operands go to the owning shard: an all-gather of the
-     per-token error vector beta*(target - decay*prediction) and decay-1. The slot owner
-     expands them against its own rows into delta rows (delta_k = (decay-1)*row_k + w_k*err,
-     gl_sdm/runtime/dense.py:11-14) and commits locally. Shipping the factored form moves
-     dim+1 floats per token instead of K*(dim+1) per token of expanded deltas.
+routing, product-key scores (`epoch`): each rank routes its own tokens (their factor scores
+  already cover all slots) and all-gathers the K routes per token (int32 slot + fp32 weight,
+  query and write side): K candidates per token instead of value rows.
+routing, dense keys (`epoch_dense`): the queries are all-gathered (2*dk bytes per token), each
+  rank scores ALL tokens against its own key shard on the tensor cores and keeps a partial
+  top-k (`glsdm_score_topk`), the K candidates per rank are all-gathered, and every rank runs
+  the same deterministic merge (`glsdm_topk_merge`), so all ranks hold identical global routes.
+read: every rank forms partial readings of all tokens over the rows it owns; a reduce-scatter
+  returns each rank the finished readings / write predictions of its own tokens.
+commit clock: the write operands go to the owning shard as an all-gather of the per-token
+  error vector beta*(target - decay*prediction) and decay-1. The slot owner expands them
+  against its own rows into delta rows (delta_k = (decay-1)*row_k + w_k*err,
+  gl_sdm/runtime/dense.py:11-14) and commits locally. The factored form moves dim+1 floats
+  per token over NVLink instead of K*(dim+4) for expanded deltas.
 
 Entry order inside a shard is (global token row, route), so the stable commit sums each
 address in the same order as the unsharded operator.
@@ -31,14 +35,40 @@ def shard_range(slots, rank, world):
     return rank * per, (rank + 1) * per
 
 
+class SingleProcess:
+    """The collectives of a world of one rank (a single GPU running the sharded code path)."""
+
+    @staticmethod
+    def get_world_size(group=None):
+        return 1
+
+    @staticmethod
+    def get_rank(group=None):
+        return 0
+
+    @staticmethod
+    def all_gather_into_tensor(out, inp, group=None):
+        out.view(-1).copy_(inp.reshape(-1))
+
+    @staticmethod
+    def reduce_scatter_tensor(out, inp, group=None):
+        out.view(-1).copy_(inp.reshape(-1))
+
+    @staticmethod
+    def all_gather(outs, inp, group=None):
+        outs[0].copy_(inp)
+
+
 class ShardedBankOperator:
     """Same epoch interface as SharedBankOperator; `values` is the full bank [1, H, S, D]
-    (each rank keeps its slice) or, with ``is_shard=True``, already this rank's slice."""
+    (each rank keeps its slice) or, with ``is_shard=True``, already this rank's slice.
+    `keys` [S, dk] (or this rank's [S/R, dk] slice with is_shard) enables dense-key routing."""
 
-    def __init__(self, values, reads, writes, dist, chunk_size=512, num_layers=1, layer_index=0,
-                 group=None, is_shard=False, slots=None, kernels=_native):
+    def __init__(self, values, reads, writes, dist=None, chunk_size=512, num_layers=1, layer_index=0,
+                 group=None, is_shard=False, slots=None, kernels=_native, keys=None):
         if reads != writes:
             raise ValueError("the sharded operator needs equal read and write widths")
+        dist = SingleProcess if dist is None else dist
         self.dist, self.group, self.k = dist, group, kernels
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -48,10 +78,15 @@ class ShardedBankOperator:
         self.slots = slots if is_shard else values.shape[2]
         self.slot_lo, self.slot_hi = shard_range(self.slots, self.rank, self.world)
         self.shard = values if is_shard else values[:, :, self.slot_lo:self.slot_hi].contiguous()
+        self.keys = None
+        if keys is not None:
+            if self.heads != 1:
+                raise ValueError("dense-key routing is implemented for single-head banks")
+            self.keys = keys if is_shard else keys[self.slot_lo:self.slot_hi].contiguous()
+            if self.keys.shape[0] != self.slot_hi - self.slot_lo:
+                raise ValueError("key shard does not match the slot shard")
         self.half = int(round(self.slots ** 0.5))
-        if self.half * self.half != self.slots:
-            raise ValueError("product-key routing needs a square number of slots")
-        self.width = kernels.routes_out(reads, self.half)
+        self.width = reads if keys is not None else kernels.routes_out(reads, self.half)
         self.reads = reads
         self.chunk_size, self.num_layers, self.layer_index = chunk_size, num_layers, layer_index
         self.key_bits = max(1, (self.heads * self.slots * chunk_size * num_layers - 1).bit_length())
@@ -65,44 +100,104 @@ class ShardedBankOperator:
             self._buf[name] = b
         return b[:numel]
 
-    def epoch(self, q_scores, k_scores, target, beta, log_decay, offset=0):
-        """q_scores/k_scores [sequences_local, tokens, heads, 2*half]; returns the readings of
-        this rank's tokens and commits every rank's proposals into the owning shards."""
-        k, dist, R, K, D = self.k, self.dist, self.world, self.width, self.dim
-        tokens = q_scores.shape[1]
-        n = q_scores.numel() // q_scores.shape[-1]          # local routing rows
+    # -- routing ---------------------------------------------------------------------------------
+
+    def _routes_product_key(self, q_scores, k_scores, n):
+        """Local routes into [idx_q | idx_k | w_q | w_k], all-gathered rank by rank."""
+        if self.half * self.half != self.slots:
+            raise ValueError("product-key routing needs a square number of slots")
+        k, R, K = self.k, self.world, self.width
         region = n * K
-        # 1. local routes straight into the send buffer [idx_q | idx_k | w_q | w_k]
         send = self._buffer("routes_send", 4 * region, torch.int32)
         k.pk_select_into(q_scores, self.reads, send, 0, 2 * region)
         k.pk_select_into(k_scores, self.reads, send, region, 3 * region)
         routes = self._buffer("routes_all", R * 4 * region, torch.int32)
-        dist.all_gather_into_tensor(routes, send, group=self.group)
-        # 2. partial readings of every rank's query and write rows over the owned slots
-        partial = k.shard_read(self.shard, self.slot_lo, self.slots, routes, 0, 2 * region, R * 2 * n, 2 * n,
-                               4 * region, K)
-        mine = torch.empty((2 * n, D), dtype=torch.float32, device=self.shard.device)  # returned to the caller
-        dist.reduce_scatter_tensor(mine, partial, group=self.group)
-        readings = mine[:n].view(*q_scores.shape[:-1], D)
+        self.dist.all_gather_into_tensor(routes, send, group=self.group)
+        return dict(routes=routes, stride=4 * region, read_weights_at=2 * region, write_index_at=region,
+                    write_weights_at=3 * region)
+
+    def _routes_dense(self, queries, write_queries, n):
+        """All-gather queries, partial top-k on this rank's keys, all-gather the K candidates,
+        identical merge on every rank. Rows are ordered (rank, side, token)."""
+        k, R, K = self.k, self.world, self.width
+        dk = queries.shape[-1]
+        send = self._buffer("queries_send", 2 * n * dk, torch.bfloat16).view(2, n, dk)
+        send[0].copy_(queries.reshape(n, dk))
+        send[1].copy_(write_queries.reshape(n, dk))
+        everyone = self._buffer("queries_all", R * 2 * n * dk, torch.bfloat16)
+        self.dist.all_gather_into_tensor(everyone, send.view(-1), group=self.group)
+        rows = R * 2 * n
+        mine = (self._buffer("cand_score", rows * K, torch.float32).view(rows, K),
+                self._buffer("cand_slot", rows * K, torch.int32).view(rows, K))
+        k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo, out=mine)
+        if R > 1:
+            scores = self._buffer("cand_score_all", R * rows * K, torch.float32)
+            slots = self._buffer("cand_slot_all", R * rows * K, torch.int32)
+            self.dist.all_gather_into_tensor(scores, mine[0].view(-1), group=self.group)
+            self.dist.all_gather_into_tensor(slots, mine[1].view(-1), group=self.group)
+            scores, slots = scores.view(R, rows, K), slots.view(R, rows, K)
+        else:
+            scores, slots = mine[0].view(1, rows, K), mine[1].view(1, rows, K)
+        routes = self._buffer("routes_all", 2 * rows * K, torch.int32)
+        k.topk_merge(scores, slots, out=(routes[:rows * K].view(rows, K),
+                                         routes[rows * K:].view(torch.float32).view(rows, K)))
+        region = n * K
+        return dict(routes=routes, stride=2 * region, read_weights_at=rows * K, write_index_at=region,
+                    write_weights_at=rows * K + region)
+
+    # -- read, proposal, commit --------------------------------------------------------------------
+
+    def _finish(self, plan, n, lead, target, beta, log_decay, tokens, offset):
+        k, dist, R, K, D = self.k, self.dist, self.world, self.width, self.dim
+        routes, stride = plan["routes"], plan["stride"]
+        # partial readings of every rank's query and write rows over the owned slots
+        partial = k.shard_read(self.shard, self.slot_lo, self.slots, routes, 0, plan["read_weights_at"], R * 2 * n,
+                               2 * n, stride, K)
+        if R > 1:
+            mine = torch.empty((2 * n, D), dtype=torch.float32, device=self.shard.device)
+            dist.reduce_scatter_tensor(mine, partial, group=self.group)
+        else:
+            mine = partial
+        readings = mine[:n].view(*lead, D)
         prediction = mine[n:]
-        # 3. write operands to the owning shards, expansion and local commit
+        # write operands to the owning shards, expansion and local commit
         packed = k.write_error(prediction, target, beta, log_decay,
                                self._buffer("error_send", n * (D + 1), torch.float32))
-        errors = self._buffer("error_all", R * n * (D + 1), torch.float32)
-        dist.all_gather_into_tensor(errors, packed, group=self.group)
-        offsets = k.shard_offsets(routes, region, R * n, n, 4 * region, K, self.slot_lo, self.slot_hi)
+        if R > 1:
+            errors = self._buffer("error_all", R * n * (D + 1), torch.float32)
+            dist.all_gather_into_tensor(errors, packed, group=self.group)
+        else:
+            errors = packed
+        offsets = k.shard_offsets(routes, plan["write_index_at"], R * n, n, stride, K, self.slot_lo, self.slot_hi)
         entries = int(offsets[-1].item())
         if entries:
             out = (self._buffer("addresses", entries, torch.int64),
                    self._buffer("deltas", entries * D, torch.float32).view(entries, D),
                    self._buffer("keys", entries, torch.int64))
-            a, d, s = k.shard_propose(self.shard, self.slot_lo, self.slots, routes, region, 3 * region, 4 * region,
-                                      errors, n * (D + 1), None, offsets, entries, R * n, n, tokens, K, offset,
-                                      self.chunk_size, self.num_layers, self.layer_index, out)
+            a, d, s = k.shard_propose(self.shard, self.slot_lo, self.slots, routes, plan["write_index_at"],
+                                      plan["write_weights_at"], stride, errors, n * (D + 1), None, offsets, entries,
+                                      R * n, n, tokens, K, offset, self.chunk_size, self.num_layers,
+                                      self.layer_index, out)
             flat = self.shard.view(-1, D)
             k.commit_rows(flat, a, d, s, out=flat, key_bits=self.key_bits)
         self.version += 1
         return readings
+
+    def epoch(self, q_scores, k_scores, target, beta, log_decay, offset=0):
+        """Product-key scores [sequences_local, tokens, heads, 2*half] in; returns the readings
+        of this rank's tokens and commits every rank's proposals into the owning shards."""
+        n = q_scores.numel() // q_scores.shape[-1]
+        plan = self._routes_product_key(q_scores, k_scores, n)
+        return self._finish(plan, n, q_scores.shape[:-1], target, beta, log_decay, q_scores.shape[1], offset)
+
+    def epoch_dense(self, queries, write_queries, target, beta, log_decay, offset=0):
+        """Dense-key routing: queries / write_queries [sequences_local, tokens, dk] bf16."""
+        if self.keys is None:
+            raise ValueError("this operator was built without keys")
+        n = queries.numel() // queries.shape[-1]
+        plan = self._routes_dense(queries, write_queries, n)
+        lead = (*queries.shape[:-1], 1)
+        return self._finish(plan, n, lead, target, beta, log_decay, queries.shape[1], offset)
 
     def gather_bank(self):
         """The whole bank [1, H, S, D] on every rank (tests and checkpoints)."""

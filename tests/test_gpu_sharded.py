@@ -75,3 +75,53 @@ def test_nccl_two_gpus_match_the_unsharded_operator(native):
     done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
     assert "sharded-nccl-ok" in done.stdout
+
+
+# ---- dense-key routing (tensor-core scores) through the sharded operator ------------------------
+
+def _dense_inputs(world, seed=31, slots=4096, dk=128, D=64, K=8, T=32):
+    g = torch.Generator().manual_seed(seed)
+    seqs = 2 * world
+    bank = torch.randn(1, 1, slots, D, generator=g) * 0.05
+    keys = torch.randn(slots, dk, generator=g)
+    keys = (keys / keys.norm(dim=1, keepdim=True)).bfloat16()
+    x = dict(q=torch.randn(seqs, T, dk, generator=g).bfloat16(), kq=torch.randn(seqs, T, dk, generator=g).bfloat16(),
+             target=torch.randn(seqs, T, 1, D, generator=g) * 0.05, beta=torch.rand(seqs, T, 1, generator=g),
+             log_decay=-torch.rand(seqs, T, 1, generator=g) * 0.2)
+    return bank, keys, x, K, T
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_dense_key_epochs_match_the_oracle(native, world):
+    from gl_sdm_b200.sharded import ShardedBankOperator
+    bank, keys, x, K, T = _dense_inputs(world)
+    dx = {k: v.to(DEV) for k, v in x.items()}
+    per = x["q"].shape[0] // world
+    tw = ThreadWorld(world)
+
+    def body(rank, dist):
+        torch.cuda.set_device(0)
+        op = ShardedBankOperator(bank.to(DEV).clone(), K, K, dist if world > 1 else None, chunk_size=T,
+                                 keys=keys.to(DEV))
+        mine = slice(rank * per, (rank + 1) * per)
+        reads = [op.epoch_dense(dx["q"][mine].contiguous(), dx["kq"][mine].contiguous(), dx["target"][mine].contiguous(),
+                                dx["beta"][mine].contiguous(), dx["log_decay"][mine].contiguous()).clone()
+                 for _ in range(2)]
+        return reads, op.gather_bank()
+
+    results = tw.run(body)
+    memory = bank.numpy()
+    for e in range(2):
+        want, memory = oracle.dense_epoch(memory, keys.float().numpy(), x["q"].float().numpy(), x["kq"].float().numpy(), K,
+                                          x["target"].numpy(), x["beta"].numpy(), x["log_decay"].numpy(), T)
+        for rank, (reads, _) in enumerate(results):
+            got = reads[e].cpu().numpy()
+            ref = want[rank * per:(rank + 1) * per]
+            # a row whose k-th and (k+1)-th scores tie within rounding may route differently
+            close = np.isclose(got, ref, rtol=1e-4, atol=1e-5).all(axis=-1)
+            assert close.mean() > 0.97
+    for _, full in results:
+        got = full.cpu().numpy()
+        agree = np.isclose(got, memory, rtol=1e-4, atol=1e-5).all(axis=-1)
+        assert agree.mean() > 0.99
+    native.raise_on_device_status(DEV)
