@@ -1,18 +1,26 @@
 """Benchmark of the GL-SDM memory operator on B200: memory-op tokens/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--routing dense|pk]
+                    [--impl ours|reference]
 
 A step is one pass of the operator over one batch of synthetic input of the chosen
-configuration (default c4: 16,777,216-slot bf16 bank, d_v 256, top-32, 64 x 8192 tokens =
-16 commit epochs of 32,768 tokens): per epoch a query route+read, a write route + prediction
-read + delta proposal, and the buffered commit. Rank 0 prints one JSON line.
+configuration. Default c4: bf16 bank of 16,777,216 slots (d_k 128, d_v 256), top-32, 64 x 8192
+tokens = 16 commit epochs of 32,768 tokens, slot-sharded over the N GPUs. Per epoch: query
+routing + read, write routing + prediction read + delta proposal, buffered commit.
 
+  --routing dense  (default) scores = queries x slot keys on the tensor cores (tcgen05) fused
+                   with the streaming top-k; sharded: query all-gather, per-GPU partial top-k,
+                   K-candidate all-gather + merge, read reduce-scatter, write operands to the
+                   owning shard at the commit clock.
+  --routing pk     the reference's product-key factor scores [tokens, 2*4096] fp32 as input
+                   (the drop-in operator contract); its single-GPU numbers are also attached to
+                   the dense line under "product_key_scores".
+
+Rank 0 prints one JSON line:
   value         device-resident throughput (inputs already in HBM), CUDA events, max over ranks
-  e2e           the same work through the public operator with pinned HOST inputs: per epoch
-                the factor scores / targets / gates are copied host->device and the readings
-                device->host inside the timed region
-  roofline      the dominant kernel's algorithmic bytes / its measured duration vs the measured
-                HBM copy peak (MEASURED_PEAKS.json)
+  e2e           the same through the operator with pinned HOST inputs: H2D of every epoch's
+                inputs and D2H of its readings inside the timed region
+  roofline      the dominant kernel against the measured peak of MEASURED_PEAKS.json
   cpu_baseline  the PyTorch CPU port of the reference path (oracle/torch_port.py) timed on this
                 machine's cores on a bounded token sample of the same workload
 --impl reference times that CPU port alone (the reference's own CPU path cannot travel to the
@@ -32,8 +40,9 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-FALLBACK_HBM_GBS = 6650.0
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 NOMINAL_HBM_GBS = 8000.0
+NOMINAL_BF16_TFLOPS = 2250.0
 
 
 def measured_peaks():
@@ -41,8 +50,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             data = json.load(f)
-        return float(data["hbm_gbs"]), "measured"
-    return FALLBACK_HBM_GBS, "fallback"
+        return {k: float(data[k]) for k in FALLBACK}, "measured"
+    return dict(FALLBACK), "fallback"
 
 
 class ClockSampler:
@@ -72,11 +81,11 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.25)
         self.proc.terminate()
-        clocks, maxes, reasons = [], [], set()
+        clocks, maxes, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             try:
-                clocks.append(float(r[1])), maxes.append(float(r[2]))
+                clocks.append(float(r[1])), maxes.append(float(r[2])), power.append(float(r[3]))
             except (ValueError, IndexError):
                 continue
             for name, cell in zip(names, r[5:9]):
@@ -84,19 +93,17 @@ class ClockSampler:
                     reasons.add(name)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = sorted(clocks)[len(clocks) // 2:]  # upper half: samples taken under load
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        busy = sorted(clocks)[len(clocks) // 2:]  # upper half by clock: samples taken under load
+        return {"sm_mhz": statistics.median(clocks), "sm_mhz_upper_half": statistics.median(busy),
+                "sm_max_mhz": max(maxes), "power_w_max": max(power), "reasons": sorted(reasons), "samples": len(clocks)}
 
 
 def dist_setup(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
+    if world > 1 and args.impl != "reference":
         import torch.distributed as dist
-        if args.impl == "reference":
-            return rank, world, local, None
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         return rank, world, local, dist
@@ -117,25 +124,45 @@ def max_over_ranks(dist, ms, device):
     return float(t.item())
 
 
-# ------------------------------------------------------------------------------------------------
+def bank_dtype_name(w):
+    return str(w.bank_dtype).split(".")[-1]
 
-def run_cpu_port(w, steps, warmup, sample_tokens, threads):
-    """Time the CPU port on `sample_tokens` tokens of one epoch per step. Returns tokens/s."""
+
+def workload_config(w, args, world):
+    routing = ("dense keys: queries [tokens, d_k] bf16 x keys [slots, d_k] bf16 on tcgen05, fused top-k"
+               if args.routing == "dense" else "product-key factor scores [tokens, 2*half] fp32 -> fused top-k")
+    return {"workload": f"{w.name}: {w.description}", "routing": routing, "slots": w.slots, "d_k": w.dk, "d_v": w.dim,
+            "top_k": w.width, "tokens_per_step": w.tokens_per_step, "commit_epochs": w.epochs,
+            "tokens_per_epoch": w.tokens_per_epoch, "bank_dtype": bank_dtype_name(w),
+            "sharding": f"slots over {world} GPUs, tokens data-parallel" if world > 1 else "single GPU",
+            "l2": "inputs larger than L2: every epoch streams the whole key shard (>= 0.5 GB) or >= 1 GB of factor scores"}
+
+
+# ---- CPU port (cpu_baseline and --impl reference) ---------------------------------------------------
+
+def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
+    """Time the CPU port on `sample_tokens` tokens of one epoch per step. Returns (tokens/s, n, s)."""
     from gl_sdm_b200 import workloads
     from oracle import torch_port as port
     torch.set_num_threads(threads)
-    gen_device = "cuda" if torch.cuda.is_available() else "cpu"
-    bank = workloads.make_bank(w, gen_device, banks=1).cpu()
+    gen = "cuda" if torch.cuda.is_available() else "cpu"
+    bank = workloads.make_bank(w, gen, banks=1).cpu()
     seqs = max(1, sample_tokens // w.chunk)
     tokens = min(w.chunk, sample_tokens)
+    keys = workloads.make_keys(w, gen).cpu() if routing == "dense" else None
     times = []
     for i in range(warmup + steps):
-        x = {k: v.cpu() for k, v in workloads.make_epoch_inputs(w, gen_device, 7000 + i, sequences=seqs, tokens=tokens).items()}
-        t0 = time.perf_counter()
-        port.routed_read(bank, x["q_scores"], w.width)
-        a, d, k = port.propose(bank, x["k_scores"], w.width, x["target"].float(), x["beta"], x["log_decay"], None, 0, 0,
-                               w.chunk, 1)
-        port.commit(bank, a, d, k, in_place=True)
+        if routing == "dense":
+            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs_dense(w, gen, 7000 + i, seqs, tokens).items()}
+            t0 = time.perf_counter()
+            port.dense_epoch(bank, keys, x["q"], x["kq"], w.width, x["target"].float(), x["beta"], x["log_decay"], w.chunk)
+        else:
+            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs(w, gen, 7000 + i, seqs, tokens).items()}
+            t0 = time.perf_counter()
+            port.routed_read(bank, x["q_scores"], w.width)
+            a, d, k = port.propose(bank, x["k_scores"], w.width, x["target"].float(), x["beta"], x["log_decay"], None,
+                                   0, 0, w.chunk, 1)
+            port.commit(bank, a, d, k, in_place=True)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
@@ -143,82 +170,102 @@ def run_cpu_port(w, steps, warmup, sample_tokens, threads):
     return n / statistics.median(times), n, statistics.median(times)
 
 
+def cpu_sample_text(w, routing, n, sec):
+    what = "flat-key scores + routes" if routing == "dense" else "product-key routes"
+    return (f"{n} tokens of one commit epoch ({what}, read, proposal, in-place commit) on the full "
+            f"{w.slots}-slot bank, {sec:.2f} s; PyTorch CPU port of the reference path")
+
+
 def reference_arm(args, w, rank):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    value, n, sec = run_cpu_port(w, args.steps, args.warmup, args.cpu_sample_tokens, threads)
+    tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
+    value, n, sec = run_cpu_port(w, args.routing, args.steps, args.warmup, tokens, threads)
     line = {
         "impl": "reference", "metric": "memory-op tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(w, args, 1),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"{n} tokens of one commit epoch per step (route+read, propose, in-place commit) on the "
-                                   f"full {w.slots}-slot bank; PyTorch CPU port of the reference path"},
+                         "sample": cpu_sample_text(w, args.routing, n, sec)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(w, args, world):
-    return {"workload": f"{w.name}: {w.description}", "routing": "product-key factor scores (fp32) -> fused top-k",
-            "slots": w.slots, "d_v": w.dim, "top_k": w.width, "tokens_per_step": w.tokens_per_step,
-            "commit_epochs": w.epochs, "tokens_per_epoch": w.tokens_per_epoch, "bank_dtype": str(w.bank_dtype).split(".")[-1],
-            "sharding": f"slots over {world} GPU(s)" if world > 1 else "single GPU",
-            "l2": "inputs larger than L2 (per-epoch factor scores alone exceed 126 MB)"}
+# ---- our arm ---------------------------------------------------------------------------------------
 
+class Runner:
+    """Binds a workload to the operator for one routing mode: device inputs and one epoch call."""
 
-def ours(args, w, rank, world, local, dist):
-    from gl_sdm_b200 import _native, workloads
-    from gl_sdm_b200.operator import SharedBankOperator
-    if world > 1:
+    def __init__(self, w, routing, dev, rank, world, dist):
+        from gl_sdm_b200 import workloads
+        from gl_sdm_b200.operator import SharedBankOperator
         from gl_sdm_b200.sharded import ShardedBankOperator
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    lib = _native.library()
-    if w.per_request_banks:
-        raise SystemExit("per-request-bank workloads (c1, c2) are measured by tests/bench of the stack API; use c3-c5 here")
-
-    bank = workloads.make_bank(w, dev)
-    if world > 1:
-        op = ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk)
+        self.w, self.routing, self.dev, self.world = w, routing, dev, world
+        seqs_local = w.sequences // world
+        bank = workloads.make_bank(w, dev)
+        if routing == "dense":
+            keys = workloads.make_keys(w, dev)
+            self.op = ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk, keys=keys)
+            del keys
+            self.names = ("q", "kq", "target", "beta", "log_decay")
+            self.epochs = [workloads.make_epoch_inputs_dense(w, dev, 1000 * (rank + 1) + e, seqs_local)
+                           for e in range(w.epochs)]
+        else:
+            self.op = (ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk) if world > 1
+                       else SharedBankOperator(bank, w.width, w.width, chunk_size=w.chunk))
+            self.names = ("q_scores", "k_scores", "target", "beta", "log_decay")
+            self.epochs = [workloads.make_epoch_inputs(w, dev, 1000 * (rank + 1) + e, seqs_local)
+                           for e in range(w.epochs)]
         del bank
-    else:
-        op = SharedBankOperator(bank, w.width, w.width, chunk_size=w.chunk)
-    seqs_local = w.sequences // world
-    epochs = [workloads.make_epoch_inputs(w, dev, 1000 * (rank + 1) + e, sequences=seqs_local) for e in range(w.epochs)]
 
-    def step():
+    def epoch(self, x):
+        a = [x[n] for n in self.names]
+        if self.routing == "dense":
+            return self.op.epoch_dense(*a)
+        return self.op.epoch(*a)
+
+    def step(self):
         out = None
-        for x in epochs:
-            out = op.epoch(x["q_scores"], x["k_scores"], x["target"], x["beta"], x["log_decay"])
+        for x in self.epochs:
+            out = self.epoch(x)
         return out
 
-    for _ in range(args.warmup):
-        step()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = lib.glsdm_kernel_launches()
+
+def timed_steps(runner, steps, warmup, dist, dev):
+    for _ in range(warmup):
+        runner.step()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier(dist)
     start.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        runner.step()
     stop.record()
     barrier(dist)
-    ms = max_over_ranks(dist, start.elapsed_time(stop), dev)
-    launches = lib.glsdm_kernel_launches() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    _native.raise_on_device_status(dev)
-    ms_per_step = ms / args.steps
-    value = w.tokens_per_step / (ms_per_step / 1e3)
+    return max_over_ranks(dist, start.elapsed_time(stop), dev) / steps
 
-    # -- per-phase device times (separate pass; events between the three calls of an epoch) ----
+
+def phase_times_dense(runner):
+    """Device time of every stage of one step (events recorded inside the operator)."""
+    op = runner.op
+    op.marks = []
+    runner.step()
+    torch.cuda.synchronize()
+    marks, op.marks = op.marks, None
+    total = {}
+    for (name, ev), (_, nxt) in zip(marks, marks[1:]):
+        if name != "end":
+            total[name] = total.get(name, 0.0) + ev.elapsed_time(nxt)
+    return {k: v / len(runner.epochs) for k, v in total.items()}
+
+
+def phase_times_pk(runner):
+    op = runner.op
     phase = {"read": 0.0, "propose": 0.0, "commit": 0.0}
-    marks = []
-    for x in epochs:
+    marks, prop = [], None
+    for x in runner.epochs:
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         ev[0].record()
         op.read(x["q_scores"])
@@ -232,67 +279,75 @@ def ours(args, w, rank, world, local, dist):
     for ev in marks:
         for i, name in enumerate(("read", "propose", "commit")):
             phase[name] += ev[i].elapsed_time(ev[i + 1])
-    calls = len(marks)
-    # unique touched rows / entries of the last epoch, for the commit's algorithmic bytes
-    addresses = prop[0]
-    unique_fraction = float(torch.unique(addresses).numel()) / max(1, addresses.numel())
-    peak, peak_kind = measured_peaks()
-    algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique_fraction, layers=1)
-    dominant = max(phase, key=phase.get)
-    per_launch_ms = phase[dominant] / calls
-    achieved = algo[dominant] / (per_launch_ms / 1e3) / 1e9
-    kernel_names = {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel",
-                    "commit": "commit (radix sort + reduce_kernel)"}
-    roofline = {"bound": "hbm", "kernel": kernel_names[dominant], "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "traffic": load_traffic(dominant, w),
-                "algorithmic_bytes_per_launch": algo[dominant], "ms_per_launch": per_launch_ms,
-                "phases": {k: {"ms_per_epoch": phase[k] / calls, "algorithmic_GBs": algo[k] / (phase[k] / calls / 1e3) / 1e9,
-                               "frac": algo[k] / (phase[k] / calls / 1e3) / 1e9 / peak} for k in phase},
-                "unique_row_fraction": unique_fraction}
+    unique = float(torch.unique(prop[0]).numel()) / max(1, prop[0].numel())
+    return {k: v / len(marks) for k, v in phase.items()}, unique
 
-    # -- end to end from pinned host memory ------------------------------------------------------
-    e2e = None if args.no_e2e else end_to_end(args, w, op, epochs[0], dev, dist, world)
 
-    if rank != 0:
-        return
-    cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        threads = os.cpu_count() or 1
-        cv, n, sec = run_cpu_port(w, 1, 1, args.cpu_sample_tokens, threads)
-        cpu = {"value": cv, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"{n} tokens of one commit epoch (route+read, propose, in-place commit), full {w.slots}-slot bank, "
-                         f"{sec:.2f} s; PyTorch CPU port of the reference path"}
-    line = {
-        "metric": "memory-op tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "f32 accumulate over %s bank" % str(w.bank_dtype).split(".")[-1], "data": "synthetic",
-        "config": workload_config(w, args, world), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-        "gpu_launches": int(launches), "clocks": clocks,
+def dense_roofline(w, runner, world, peaks, peak_kind):
+    """score_topk against the measured bf16 tensor peak; the HBM-bound stages alongside."""
+    phases = phase_times_dense(runner)
+    tokens = w.tokens_per_epoch            # every rank scores ALL tokens of the epoch (both sides) ...
+    shard_slots = w.slots // world         # ... against its own shard of the keys
+    flops = 2.0 * (2 * tokens) * shard_slots * w.dk
+    ms = phases["score_topk"]
+    achieved = flops / (ms / 1e3) / 1e12
+    e = 2 if w.bank_dtype == torch.bfloat16 else 4
+    rows = 2 * tokens
+    entries = getattr(runner.op, "last_entries", tokens * w.width // world)
+    hbm = {
+        "read": rows * (w.width * 8 + 4 * w.dim) + rows * w.width * w.dim * e / world,
+        "propose": tokens * (w.dim + 1) * 4 + entries * (w.dim * e + 4 * w.dim + 16) + tokens * w.width * 8,
+        "commit": entries * (4 * w.dim + 16) + entries * 2 * w.dim * e,
     }
-    print(json.dumps(line), flush=True)
+    out = {"bound": "tensor", "kernel": "score_topk_kernel (tcgen05 + TMEM + TMA, fused top-k)", "achieved": achieved,
+           "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
+           "peak_kind": f"of {peak_kind} sustained cuBLAS bf16 (the kernel runs for >0.1 s inside a multi-second step)",
+           "frac_of_burst_peak": achieved / peaks["bf16_tflops"], "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
+           "traffic": load_traffic("score_topk", w), "algorithmic_flops_per_launch": flops, "ms_per_launch": ms,
+           "phases": {k: {"ms_per_epoch": v} for k, v in phases.items()}}
+    for name, nbytes in hbm.items():
+        if name in phases and phases[name] > 0:
+            gbs = nbytes / (phases[name] / 1e3) / 1e9
+            out["phases"][name].update({"algorithmic_GBs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]})
+    return out
 
 
-def load_traffic(phase, w):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+def pk_roofline(w, runner, world, peaks, peak_kind):
+    from gl_sdm_b200 import workloads
+    phase, unique = phase_times_pk(runner)
+    algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1)
+    dominant = max(phase, key=phase.get)
+    achieved = algo[dominant] / (phase[dominant] / 1e3) / 1e9
+    names = {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"}
+    return {"bound": "hbm", "kernel": names[dominant], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}",
+            "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": load_traffic(dominant, w),
+            "algorithmic_bytes_per_launch": algo[dominant], "ms_per_launch": phase[dominant],
+            "phases": {k: {"ms_per_epoch": phase[k], "algorithmic_GBs": algo[k] / (phase[k] / 1e3) / 1e9,
+                           "frac_of_hbm_peak": algo[k] / (phase[k] / 1e3) / 1e9 / peaks["hbm_gbs"]} for k in phase},
+            "unique_row_fraction": unique}
+
+
+def load_traffic(kernel, w):
+    """DRAM bytes per launch of a kernel from the committed ncu summary (profiles/traffic.json)."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(path):
         return None
     with open(path) as f:
         table = json.load(f)
-    entry = table.get(f"{w.name}:{phase}")
+    entry = table.get(f"{w.name}:{kernel}")
     return None if entry is None else entry.get("dram_bytes_per_launch")
 
 
-def end_to_end(args, w, op, template, dev, dist, world):
-    """Host-resident inputs: per epoch H2D of scores/targets/gates (double-buffered on a copy
+def end_to_end(args, w, runner, dev, dist, world):
+    """Host-resident inputs: per epoch H2D of the operator inputs (double-buffered on a copy
     stream), the operator epoch, and D2H of the readings, all inside the timed region."""
-    names = ("q_scores", "k_scores", "target", "beta", "log_decay")
+    names, template = runner.names, runner.epochs[0]
     host = {k: torch.empty(template[k].shape, dtype=template[k].dtype).pin_memory() for k in names}
     for k in names:
         host[k].copy_(template[k])
     slots = [{k: torch.empty_like(template[k]) for k in names} for _ in range(2)]
-    readings_host = torch.empty((*template["beta"].shape, w.dim), dtype=torch.float32).pin_memory()
+    readings_host = torch.empty((*template["beta"].shape[:2], w.heads, w.dim), dtype=torch.float32).pin_memory()
     copy_stream = torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
     ready = [torch.cuda.Event() for _ in range(2)]
@@ -314,10 +369,9 @@ def end_to_end(args, w, op, template, dev, dist, world):
             if e + 1 < w.epochs:
                 upload((e + 1) % 2)
             main.wait_event(ready[cur])
-            x = slots[cur]
-            out = op.epoch(x["q_scores"], x["k_scores"], x["target"], x["beta"], x["log_decay"])
+            out = runner.epoch(slots[cur])
             freed[cur].record(main)
-            readings_host.copy_(out, non_blocking=True)
+            readings_host.copy_(out.view(readings_host.shape), non_blocking=True)
         return readings_host
 
     steps = max(1, min(args.steps, args.e2e_steps))
@@ -337,6 +391,64 @@ def end_to_end(args, w, op, template, dev, dist, world):
             "note": "one epoch of pinned host inputs re-sent for each of the step's epochs; uploads overlap compute on a copy stream"}
 
 
+def ours(args, w, rank, world, local, dist):
+    from gl_sdm_b200 import _native
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    lib = _native.library()
+    if w.per_request_banks:
+        raise SystemExit("c1/c2 hold one bank per request (replicas only); this benchmark covers the shared-bank "
+                         "configurations c3-c5")
+    peaks, peak_kind = measured_peaks()
+    runner = Runner(w, args.routing, dev, rank, world, dist)
+    for _ in range(args.warmup):
+        runner.step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.glsdm_kernel_launches()
+    ms_per_step = timed_steps(runner, args.steps, 0, dist, dev)
+    launches = lib.glsdm_kernel_launches() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    _native.raise_on_device_status(dev)
+    value = w.tokens_per_step / (ms_per_step / 1e3)
+    roofline = (dense_roofline if args.routing == "dense" else pk_roofline)(w, runner, world, peaks, peak_kind)
+    e2e = None if args.no_e2e else end_to_end(args, w, runner, dev, dist, world)
+
+    extra = None
+    if args.routing == "dense" and world == 1 and not args.no_pk_block:
+        del runner
+        torch.cuda.empty_cache()
+        pk = Runner(w, "pk", dev, rank, world, dist)
+        pk_ms = timed_steps(pk, args.steps, args.warmup, dist, dev)
+        extra = {"note": "same workload with the reference's operator contract: factor scores [tokens, 2*half] fp32 in",
+                 "value": w.tokens_per_step / (pk_ms / 1e3), "unit": "tokens/s", "ms_per_step": pk_ms,
+                 "roofline": pk_roofline(w, pk, world, peaks, peak_kind)}
+        del pk
+        torch.cuda.empty_cache()
+
+    if rank != 0:
+        return
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
+        cv, n, sec = run_cpu_port(w, args.routing, 1, 1, tokens, threads)
+        cpu = {"value": cv, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": cpu_sample_text(w, args.routing, n, sec)}
+    line = {
+        "metric": "memory-op tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": ("bf16 tensor-core scores, " if args.routing == "dense" else "") + "f32 accumulate over %s bank" % bank_dtype_name(w),
+        "data": "synthetic", "config": workload_config(w, args, world), "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if extra is not None:
+        line["product_key_scores"] = extra
+    print(json.dumps(line), flush=True)
+
+
 def main():
     from gl_sdm_b200 import workloads
     ap = argparse.ArgumentParser()
@@ -345,12 +457,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--routing", default="dense", choices=["dense", "pk"])
     ap.add_argument("--sequences", type=int, default=None, help="override the batch (sequences per step)")
     ap.add_argument("--seq-len", type=int, default=None)
-    ap.add_argument("--cpu-sample-tokens", type=int, default=8192)
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=0, help="0 = 256 (dense) / 8192 (pk)")
+    ap.add_argument("--e2e-steps", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input pass (profiling runs)")
+    ap.add_argument("--no-pk-block", action="store_true", help="skip the attached product-key-scores measurement")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.sequences or args.seq_len:

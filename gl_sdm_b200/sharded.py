@@ -92,6 +92,13 @@ class ShardedBankOperator:
         self.key_bits = max(1, (self.heads * self.slots * chunk_size * num_layers - 1).bit_length())
         self.version = 0
         self._buf = {}
+        self.marks = None   # set to a list to collect (stage name, CUDA event) pairs for profiling
+
+    def _mark(self, name):
+        if self.marks is not None:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            self.marks.append((name, event))
 
     def _buffer(self, name, numel, dtype):
         b = self._buf.get(name)
@@ -129,7 +136,9 @@ class ShardedBankOperator:
         rows = R * 2 * n
         mine = (self._buffer("cand_score", rows * K, torch.float32).view(rows, K),
                 self._buffer("cand_slot", rows * K, torch.int32).view(rows, K))
+        self._mark("score_topk")
         k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo, out=mine)
+        self._mark("merge")
         if R > 1:
             scores = self._buffer("cand_score_all", R * rows * K, torch.float32)
             slots = self._buffer("cand_slot_all", R * rows * K, torch.int32)
@@ -150,6 +159,7 @@ class ShardedBankOperator:
     def _finish(self, plan, n, lead, target, beta, log_decay, tokens, offset):
         k, dist, R, K, D = self.k, self.dist, self.world, self.width, self.dim
         routes, stride = plan["routes"], plan["stride"]
+        self._mark("read")
         # partial readings of every rank's query and write rows over the owned slots
         partial = k.shard_read(self.shard, self.slot_lo, self.slots, routes, 0, plan["read_weights_at"], R * 2 * n,
                                2 * n, stride, K)
@@ -161,6 +171,7 @@ class ShardedBankOperator:
         readings = mine[:n].view(*lead, D)
         prediction = mine[n:]
         # write operands to the owning shards, expansion and local commit
+        self._mark("propose")
         packed = k.write_error(prediction, target, beta, log_decay,
                                self._buffer("error_send", n * (D + 1), torch.float32))
         if R > 1:
@@ -179,7 +190,10 @@ class ShardedBankOperator:
                                       R * n, n, tokens, K, offset, self.chunk_size, self.num_layers,
                                       self.layer_index, out)
             flat = self.shard.view(-1, D)
+            self._mark("commit")
             k.commit_rows(flat, a, d, s, out=flat, key_bits=self.key_bits)
+        self._mark("end")
+        self.last_entries = entries
         self.version += 1
         return readings
 

@@ -112,6 +112,33 @@ def make_epoch_inputs(w, device, seed, sequences=None, tokens=None, plant=4.0):
     return out
 
 
+def make_keys(w, device, seed=4321):
+    """Slot keys [slots, dk] bf16: N(0,1) rows scaled to unit L2 norm, drawn in slabs."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    out = torch.empty((w.slots, w.dk), dtype=torch.bfloat16, device=device)
+    slab = 1 << 20
+    for lo in range(0, w.slots, slab):
+        hi = min(lo + slab, w.slots)
+        x = torch.randn((hi - lo, w.dk), generator=g, device=device)
+        out[lo:hi] = (x / x.norm(dim=1, keepdim=True)).to(torch.bfloat16)
+    return out
+
+
+def make_epoch_inputs_dense(w, device, seed, sequences=None, tokens=None):
+    """Queries (read and write side) N(0,1) bf16 and the write operands of one commit epoch."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n, t = sequences or w.sequences, tokens or w.chunk
+    out = {
+        "q": torch.randn((n, t, w.dk), generator=g, device=device).to(torch.bfloat16),
+        "kq": torch.randn((n, t, w.dk), generator=g, device=device).to(torch.bfloat16),
+        "target": (torch.randn((n, t, 1, w.dim), generator=g, device=device) * 0.02).to(
+            torch.bfloat16 if w.bank_dtype == torch.bfloat16 else torch.float32),
+        "beta": torch.randn((n, t, 1), generator=g, device=device).sigmoid(),
+        "log_decay": -F.softplus(torch.randn((n, t, 1), generator=g, device=device) - 4),
+    }
+    return out
+
+
 def algorithmic_bytes(w, tokens, unique_fraction=1.0, layers=None):
     """Bytes each stage must move for `tokens` tokens (per-unit figures: see DESIGN.md):
     query read K*D*e + 4*D plus 8*half of factor scores; proposal K*D*e + 8*half + target +

@@ -93,11 +93,47 @@ def commit(memory, addresses, deltas, keys=None, in_place=False):
     return flat.index_copy(0, rows, updated).view_as(memory)
 
 
-def flat_routes(queries, keys, width):
+def flat_routes(queries, keys, width, chunk=262144):
     """Flat-key mode (no counterpart in the reference): q @ keys^T, then the slot-sum
-    selection rule (routing.py:21-26). -> (slot ascending, softmax weights)."""
-    scores = queries.float() @ keys.float().T
-    slot = _rank_desc_prefer_high(scores, width)
-    best = torch.gather(scores, -1, slot)
+    selection rule (routing.py:21-26). -> (slot ascending, softmax weights).
+
+    Keys are visited in chunks so the [tokens, slots] score matrix is never held whole: per
+    chunk a library top-k keeps `width` candidates, and the surviving candidates are ranked
+    with the exact rule (score descending, larger slot first). Equal scores inside one chunk
+    are cut by torch.topk's own order, which only matters for bit-equal scores.
+    """
+    q = queries.float()
+    cand_score, cand_slot = [], []
+    for lo in range(0, keys.shape[0], chunk):
+        block = keys[lo:lo + chunk].float()
+        scores = q @ block.T
+        top = torch.topk(scores, min(width, block.shape[0]), dim=-1)
+        cand_score.append(top.values)
+        cand_slot.append(top.indices + lo)
+    score, slot = torch.cat(cand_score, -1), torch.cat(cand_slot, -1)
+    slot, by_slot = torch.sort(slot, dim=-1, descending=True, stable=True)
+    score = torch.gather(score, -1, by_slot)
+    winners = torch.sort(score, dim=-1, descending=True, stable=True).indices[..., :width]
+    slot, score = torch.gather(slot, -1, winners), torch.gather(score, -1, winners)
     slot, ascending = torch.sort(slot, dim=-1)
-    return slot, torch.softmax(torch.gather(best, -1, ascending), dim=-1)
+    return slot, torch.softmax(torch.gather(score, -1, ascending), dim=-1)
+
+
+def dense_epoch(memory, keys, queries, write_queries, width, target, beta, log_decay, chunk_size, in_place=True):
+    """One commit epoch with flat-key routing on a single-head shared bank [1,1,S,D]:
+    read, write proposal (global_layer.py:44-54 with dense.py:11-14) and commit.
+    queries [B,T,dk]. Returns (readings [B,T,1,D], memory)."""
+    B, T, dk = queries.shape
+    flat = memory.flatten(0, 2)
+    index, weights = flat_routes(queries.reshape(-1, dk), keys, width)
+    readings = (flat[index].float() * weights.unsqueeze(-1)).sum(-2).view(B, T, 1, -1)
+    windex, wweights = flat_routes(write_queries.reshape(-1, dk), keys, width)
+    rows = flat[windex].float()
+    prediction = (rows * wweights.unsqueeze(-1)).sum(-2)
+    delta = delta_rows(rows.view(B, T, 1, width, -1), wweights.view(B, T, 1, width), prediction.view(B, T, 1, -1),
+                       target.view(B, T, 1, -1), beta.view(B, T, 1, 1), log_decay.view(B, T, 1, 1), torch.ones(B, T))
+    address = windex.view(B, T, 1, width)
+    position = torch.arange(T).view(1, T, 1, 1)
+    key = address * chunk_size + position
+    memory = commit(memory, address.flatten(), delta.flatten(0, 3), key.flatten(), in_place=in_place)
+    return readings, memory
