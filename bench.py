@@ -104,6 +104,7 @@ def dist_setup(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1 and args.impl != "reference":
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout for the one JSON line
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         return rank, world, local, dist
@@ -247,8 +248,8 @@ def timed_steps(runner, steps, warmup, dist, dev):
     return max_over_ranks(dist, start.elapsed_time(stop), dev) / steps
 
 
-def phase_times_dense(runner):
-    """Device time of every stage of one step (events recorded inside the operator)."""
+def phase_times_marks(runner):
+    """Device time of every stage of one step (events recorded inside the sharded operator)."""
     op = runner.op
     op.marks = []
     runner.step()
@@ -285,7 +286,7 @@ def phase_times_pk(runner):
 
 def dense_roofline(w, runner, world, peaks, peak_kind):
     """score_topk against the measured bf16 tensor peak; the HBM-bound stages alongside."""
-    phases = phase_times_dense(runner)
+    phases = phase_times_marks(runner)
     tokens = w.tokens_per_epoch            # every rank scores ALL tokens of the epoch (both sides) ...
     shard_slots = w.slots // world         # ... against its own shard of the keys
     flops = 2.0 * (2 * tokens) * shard_slots * w.dk
@@ -314,6 +315,8 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
 
 def pk_roofline(w, runner, world, peaks, peak_kind):
     from gl_sdm_b200 import workloads
+    if world > 1:
+        return pk_sharded_roofline(w, runner, world, peaks, peak_kind)
     phase, unique = phase_times_pk(runner)
     algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1)
     dominant = max(phase, key=phase.get)
@@ -326,6 +329,32 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
             "phases": {k: {"ms_per_epoch": phase[k], "algorithmic_GBs": algo[k] / (phase[k] / 1e3) / 1e9,
                            "frac_of_hbm_peak": algo[k] / (phase[k] / 1e3) / 1e9 / peaks["hbm_gbs"]} for k in phase},
             "unique_row_fraction": unique}
+
+
+def pk_sharded_roofline(w, runner, world, peaks, peak_kind):
+    """Sharded product-key mode: local routing of the rank's own tokens, then the shared
+    read / proposal / commit stages over the rank's slots."""
+    phases = phase_times_marks(runner)
+    e = 2 if w.bank_dtype == torch.bfloat16 else 4
+    local_rows = 2 * w.tokens_per_epoch * w.heads // world
+    rows = 2 * w.tokens_per_epoch * w.heads
+    entries = getattr(runner.op, "last_entries", w.tokens_per_epoch * w.width // world)
+    algo = {
+        "route": local_rows * (8 * w.half + 8 * w.width),
+        "read": rows * (w.width * 8 + 4 * w.dim) + rows * w.width * w.dim * e / world,
+        "propose": w.tokens_per_epoch * (w.dim + 1) * 4 + entries * (w.dim * e + 4 * w.dim + 16),
+        "commit": entries * (4 * w.dim + 16) + entries * 2 * w.dim * e,
+    }
+    dominant = max((k for k in algo if k in phases), key=lambda k: phases[k])
+    achieved = algo[dominant] / (phases[dominant] / 1e3) / 1e9
+    return {"bound": "hbm", "kernel": {"route": "pk_select_kernel", "read": "snapshot_read_kernel (shard)",
+                                       "propose": "shard_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"}[dominant],
+            "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": None,
+            "algorithmic_bytes_per_launch": algo[dominant], "ms_per_launch": phases[dominant],
+            "phases": {k: {"ms_per_epoch": v, **({"algorithmic_GBs": algo[k] / (v / 1e3) / 1e9,
+                                                   "frac_of_hbm_peak": algo[k] / (v / 1e3) / 1e9 / peaks["hbm_gbs"]}
+                                                  if k in algo and v > 0 else {})} for k, v in phases.items()}}
 
 
 def load_traffic(kernel, w):

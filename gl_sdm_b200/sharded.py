@@ -116,6 +116,7 @@ class ShardedBankOperator:
         k, R, K = self.k, self.world, self.width
         region = n * K
         send = self._buffer("routes_send", 4 * region, torch.int32)
+        self._mark("route")
         k.pk_select_into(q_scores, self.reads, send, 0, 2 * region)
         k.pk_select_into(k_scores, self.reads, send, region, 3 * region)
         routes = self._buffer("routes_all", R * 4 * region, torch.int32)
