@@ -2,15 +2,20 @@
 // (tcgen05.mma, accumulators in tensor memory), fused with a running per-row top-k in the
 // epilogue, so the [rows, slots] score matrix never leaves the SM.
 //
-// One persistent CTA per SM, 10 warps:
+// One persistent CTA per SM, 14 warps:
 //   warp 0     TMA producer: the unit's query tile (2 x 128 rows) once, then key tiles of
 //              128 slots through a 3-stage shared-memory ring (128-byte swizzle, K-major)
 //   warp 1     allocates tensor memory (512 columns) and issues tcgen05.mma from one thread:
 //              per key tile, 2 row blocks x dk/16 instructions of shape 128 x 128 x 16
 //              (bf16 in, fp32 accumulate); accumulators are double-buffered in tensor memory
-//   warps 2-9  epilogue: thread = one query row; tcgen05.ld 32 columns at a time, a running
-//              max against the row's current k-th score rejects most column groups with one
-//              compare; survivors are inserted into the row's sorted list in shared memory
+//   warps 2-9  scanners: thread = one query row; tcgen05.ld moves 64 columns at a time to
+//              registers, a running max against the row's floor (its current k-th score)
+//              rejects most 32-column groups with one compare; survivors are pushed into a
+//              small shared-memory queue and the accumulator buffer goes back to the MMA warp
+//   warps 10-13 inserters: each drains the queue of two scanner warps (64 rows) and inserts
+//              the candidates into the rows' sorted lists in shared memory, the whole warp
+//              working on one list at a time; they publish the new floors to the scanners.
+//              Scanning thus never waits for an insertion (only for queue space).
 // A unit is (pair of 128-row blocks, one split of the slot range). Each unit writes its
 // rows' best `width` (score, slot) pairs; with more than one split a small merge kernel
 // reduces the splits. Units are ordered split-major so that the CTAs running at the same time
@@ -35,8 +40,11 @@ constexpr int kTileCols = 128;                  // slots per key tile (MMA N)
 constexpr int kStages = 3;
 constexpr int kAtomK = 64;                      // bf16 elements per 128-byte swizzle row
 constexpr int kSubTileBytes = kBlockRows * 128; // one [128 x 64] bf16 sub-tile, 16 KB
-constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+constexpr int kEpilogueWarps = 8;                // scanner warps
+constexpr int kInsertWarps = 4;                  // one per pair of scanner warps (64 rows)
+constexpr int kThreads = 32 * (2 + kEpilogueWarps + kInsertWarps);
+constexpr int kQueueSlots = 32;                  // entries per inserter queue (one per lane)
+constexpr int64_t kMaxSlotsPerCall = 1 << 24;    // a queue entry carries a 24-bit slot
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
@@ -144,27 +152,43 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ uint32_t tmem_load1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  return r;
+}
+
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Insert the keys of the lanes in `m` into their rows' sorted lists. Lane j holds entry j of
-// the row being updated; a ballot counts the entries above the new key and the tail moves
-// down one lane. Kept out of line: it is called from 128 unrolled column tests per tile.
-__device__ __noinline__ void insert_events(unsigned m, uint64_t mine, uint64_t* list, float* floor_s, int K,
-                                           int lane) {
-  while (m) {
-    const int src = __ffs(m) - 1;
-    m &= m - 1;
-    const uint64_t key = shfl_u64(mine, src);
-    uint64_t* row_list = list + src * 32;
-    const uint64_t e = row_list[lane];
-    const int pos = __popc(__ballot_sync(kFullMask, e > key));
-    if (pos < K) {
-      const uint64_t up = __shfl_up_sync(kFullMask, e, 1);
-      const uint64_t ne = lane < pos ? e : (lane == pos ? key : up);
-      row_list[lane] = ne;
-      if (lane == K - 1) floor_s[src] = ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+// Candidate queue of one inserter warp (multi-producer: two scanner warps; one consumer).
+// An entry is orderable score << 32 | row (6 bits) << 24 | slot (24 bits); 0 = empty slot.
+struct Queue {
+  uint64_t slot[kQueueSlots];
+  uint32_t tail;    // entries reserved so far (producers, atomicAdd)
+  uint32_t head;    // entries consumed so far (consumer)
+  uint32_t done;    // scanner warps that have finished pushing, summed over units
+  uint32_t epoch;   // units whose lists the consumer has written out and reset
+};
+
+// Push the entries of the lanes in `m` (warp-uniform). Space is reserved with one atomic per
+// call; a lane waits (bounded) until the consumer has freed the ring slot it was given.
+__device__ __forceinline__ bool queue_push(Queue* q, unsigned m, bool pass, uint64_t entry, int lane,
+                                           volatile int* abort_flag) {
+  uint32_t base = 0;
+  if (lane == 0) base = atomicAdd(&q->tail, static_cast<uint32_t>(__popc(m)));
+  base = __shfl_sync(kFullMask, base, 0);
+  bool ok = true;
+  if (pass) {
+    const uint32_t at = base + __popc(m & ((1u << lane) - 1u));
+    uint32_t spin = 0;
+    while (static_cast<int32_t>(at - *reinterpret_cast<volatile uint32_t*>(&q->head)) >= kQueueSlots) {
+      if (++spin >= kSpinLimit || ((spin & 1023u) == 0 && *abort_flag)) { ok = false; break; }
     }
+    if (ok) *reinterpret_cast<volatile uint64_t*>(&q->slot[at & (kQueueSlots - 1)]) = entry;
   }
+  if (!__all_sync(kFullMask, ok)) { *abort_flag = 1; return false; }
+  return true;
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -189,19 +213,24 @@ struct Layout {
   static constexpr int kListOffset = kA + kB;
   __host__ __device__ static constexpr int list_bytes(int) { return 8 * 32 * 32 * kEpilogueWarps; }
   __host__ __device__ static constexpr int total(int width) {
-    return kListOffset + list_bytes(width) + static_cast<int>(sizeof(Barriers)) + 4 * 32 * kEpilogueWarps + 1024;
+    return kListOffset + list_bytes(width) + static_cast<int>(sizeof(Barriers)) + 4 * 32 * kEpilogueWarps +
+           kInsertWarps * static_cast<int>(sizeof(Queue)) + 64;
   }
 };
 
 template <int KB>
 __global__ void __launch_bounds__(kThreads, 1)
 score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Params p) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  // The 128-byte-swizzled tiles need a 1024-byte aligned base; dynamic shared memory starts
+  // at the alignment the declaration asks for (checked below, the kernel refuses otherwise).
+  extern __shared__ __align__(1024) uint8_t raw_smem[];
+  uint8_t* smem = raw_smem;
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + Layout<KB>::kA;
   float* list_val = reinterpret_cast<float*>(smem + Layout<KB>::kListOffset);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + Layout<KB>::kListOffset + Layout<KB>::list_bytes(p.width));
+  float* floors = reinterpret_cast<float*>(bars + 1);                       // [256] current k-th score per row
+  Queue* queues = reinterpret_cast<Queue*>(floors + 32 * kEpilogueWarps);   // [kInsertWarps]
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -217,9 +246,11 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_init(&bars->acc_full[b], 1);
       mbar_init(&bars->acc_empty[b], kEpilogueWarps);
     }
-    bars->abort_flag = 0;
+    bars->abort_flag = (smem_u32(raw_smem) & 1023u) ? 1 : 0;   // misaligned base: every role leaves at once
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (int i = threadIdx.x; i < kInsertWarps * static_cast<int>(sizeof(Queue) / 4); i += kThreads)
+    reinterpret_cast<uint32_t*>(queues)[i] = 0;
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
                  "r"(kTmemCols));
@@ -312,33 +343,28 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_wait(&bars->a_empty, static_cast<uint32_t>(done - 1) & 1u, abort_flag);
       }
     }
-  } else {
-    // ---------------------------------------------------------------- epilogue
-    // A warp owns 32 query rows (lane = row). Each row keeps its 32 best keys
-    // (orderable score << 32 | slot - col_base), sorted best first, in shared memory as
-    // list[row][32]. Column groups are rejected with a running max against the row's floor
-    // (its current k-th score). A surviving score is inserted by the WHOLE warp: lane j holds
-    // entry j of that row's list, a ballot counts the entries above the new key, and the
-    // tail shifts down by one lane - about a dozen instructions whatever the list length.
+  } else if (warp < 2 + kEpilogueWarps) {
+    // ---------------------------------------------------------------- scanners
+    // Scanner: lane = one query row of the unit. Row lists live with the inserter; the
+    // scanner only compares against the row's published floor and queues what passes.
     const int ew = warp - 2;                    // 0..7
     const int mb = ew >> 2;                     // row block of this warp
     const int quarter = warp & 3;               // tensor-memory lane quarter this warp may read
-    const int row_in_unit = mb * kBlockRows + quarter * 32 + lane;
-    uint64_t* list = reinterpret_cast<uint64_t*>(list_val) + static_cast<size_t>(ew) * 32 * 32;
-    float* floor_s = reinterpret_cast<float*>(bars + 1) + ew * 32;
-    const int K = p.width;
+    Queue* q = queues + (ew >> 1);
+    volatile float* my_floor = floors + ew * 32 + lane;
+    const uint32_t row_tag = static_cast<uint32_t>((ew & 1) * 32 + lane) << 24;
     uint32_t acc_phase[2] = {0, 0};
-    uint32_t tile_counter = 0;
+    uint32_t tile_counter = 0, unit_local = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-      const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
-      for (int r = 0; r < 32; ++r) list[r * 32 + lane] = 0;
-      floor_s[lane] = -INFINITY;
-      __syncwarp();
-      float floor = -INFINITY;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++unit_local) {
+      const int split = unit / p.unit_pairs;
+      // the inserter must have written out and reset the previous unit's lists
+      for (uint32_t spin = 0; *reinterpret_cast<volatile uint32_t*>(&q->epoch) < unit_local; ++spin)
+        if (spin >= kSpinLimit || ((spin & 1023u) == 1023u && *abort_flag)) { *abort_flag = 1; ok = false; break; }
+      if (!__all_sync(kFullMask, ok)) { ok = false; break; }
       const int t0 = split * p.tiles_per_split;
       const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
-      for (int t = t0; t < t1; ++t, ++tile_counter) {
+      for (int t = t0; t < t1 && ok; ++t, ++tile_counter) {
         const uint32_t buf = tile_counter & 1u;
         ok = mbar_wait(&bars->acc_full[buf], acc_phase[buf], abort_flag);
         if (!ok) break;
@@ -347,59 +373,131 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int64_t col0 = static_cast<int64_t>(t) * kTileCols;
         const int64_t left = p.slots - col0;
         const int live_cols = left < kTileCols ? static_cast<int>(left) : kTileCols;
-        // The whole 128-column row slice moves to registers at once; the accumulator buffer
-        // is handed back to the MMA warp before the scan, so inserts never stall the MMAs
-        // unless this warp falls a full tile behind.
-        uint32_t r[kTileCols];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * (2 * kTileCols) +
                                mb * kTileCols;
-        tmem_load32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-        tmem_load32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-        tmem_load32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(&r[64]));
-        tmem_load32(taddr + 96, *reinterpret_cast<uint32_t(*)[32]>(&r[96]));
-        tmem_wait_loads();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {           // two halves of 64 columns
+          uint32_t r[64];
+          tmem_load32(taddr + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_load32(taddr + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tmem_wait_loads();
+          const float floor = *my_floor;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            float m0 = __uint_as_float(r[c * 32]), m1 = __uint_as_float(r[c * 32 + 1]),
+                  m2 = __uint_as_float(r[c * 32 + 2]), m3 = __uint_as_float(r[c * 32 + 3]);
+#pragma unroll
+            for (int i = 4; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(r[c * 32 + i]));
+              m1 = fmaxf(m1, __uint_as_float(r[c * 32 + i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(r[c * 32 + i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(r[c * 32 + i + 3]));
+            }
+            const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            if (!__any_sync(kFullMask, best >= floor)) continue;
+            // Rare path. Registers cannot be indexed by a run-time column, and handling every
+            // column inline would bloat the loop, so: one bit per passing column, then a short
+            // loop over the columns that passed in any row, re-reading that single column
+            // from tensor memory (the buffer is released only after the tile's events).
+            const int first = h * 64 + c * 32;
+            uint32_t mine = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              mine |= (__uint_as_float(r[c * 32 + i]) >= floor && first + i < live_cols) ? (1u << i) : 0u;
+            uint32_t cols = __reduce_or_sync(kFullMask, mine);
+            const uint32_t slot0 = static_cast<uint32_t>(col0) + first;
+            while (cols && ok) {
+              const int i = __ffs(cols) - 1;
+              cols &= cols - 1;
+              const float v = __uint_as_float(tmem_load1(taddr + first + i));
+              const bool pass = (mine >> i) & 1u;
+              const unsigned m = __ballot_sync(kFullMask, pass);
+              ok = queue_push(q, m, pass, pack_key(orderable_bits(v), row_tag | (slot0 + i)), lane, abort_flag);
+            }
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
-#pragma unroll
-        for (int c = 0; c < kTileCols / 32; ++c) {
-          float m0 = __uint_as_float(r[c * 32]), m1 = __uint_as_float(r[c * 32 + 1]),
-                m2 = __uint_as_float(r[c * 32 + 2]), m3 = __uint_as_float(r[c * 32 + 3]);
-#pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(r[c * 32 + i]));
-            m1 = fmaxf(m1, __uint_as_float(r[c * 32 + i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(r[c * 32 + i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(r[c * 32 + i + 3]));
-          }
-          const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-          if (!__any_sync(kFullMask, best >= floor)) continue;
-          const uint32_t slot0 = static_cast<uint32_t>(col0) + c * 32;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            // every column of the group is tested against the floor the group started with
-            // (no dependency between iterations); the insert itself re-checks the position
-            const float v = __uint_as_float(r[c * 32 + i]);
-            const unsigned m = __ballot_sync(kFullMask, v >= floor && c * 32 + i < live_cols);
-            if (m) insert_events(m, pack_key(orderable_bits(v), slot0 + i), list, floor_s, K, lane);
-          }
-          __syncwarp();
-          floor = floor_s[lane];
+      }
+      // this warp has pushed everything of the unit
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) atomicAdd(&q->done, 1u);
+    }
+  } else {
+    // ---------------------------------------------------------------- inserters
+    // Inserter: drains one queue, keeps the sorted lists of its 64 rows (32 entries each, best
+    // first; lane j holds entry j of the list being updated), publishes floors, and at the end
+    // of a unit writes the lists out and resets them.
+    const int iw = warp - 2 - kEpilogueWarps;   // 0..3
+    Queue* q = queues + iw;
+    uint64_t* lists = reinterpret_cast<uint64_t*>(list_val) + static_cast<size_t>(iw) * 64 * 32;
+    float* floor_s = floors + iw * 64;
+    const int K = p.width;
+    uint32_t head = 0, units_done = 0;
+    bool ok = true;
+    for (int r = 0; r < 64; ++r) lists[r * 32 + lane] = 0;
+    floor_s[lane] = -INFINITY;
+    floor_s[32 + lane] = -INFINITY;
+    __syncwarp();
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
+      uint32_t idle = 0;
+      for (;;) {
+        const uint64_t e = *reinterpret_cast<volatile uint64_t*>(&q->slot[(head + lane) & (kQueueSlots - 1)]);
+        const unsigned ready = __ballot_sync(kFullMask, e != 0);
+        const int count = (ready == kFullMask) ? 32 : __ffs(~ready) - 1;   // contiguous ready prefix
+        if (count == 0) {
+          const uint32_t finished = *reinterpret_cast<volatile uint32_t*>(&q->done);
+          const uint32_t tail = *reinterpret_cast<volatile uint32_t*>(&q->tail);
+          if (finished == 2u * (units_done + 1u) && tail == head) break;    // unit complete, queue empty
+          if (++idle >= kSpinLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
+          continue;
         }
+        idle = 0;
+        for (int j = 0; j < count; ++j) {
+          const uint64_t entry = shfl_u64(e, j);
+          const int row = static_cast<int>(entry >> 24) & 63;
+          const uint64_t key = (entry & 0xffffffff00000000ull) | (entry & 0xffffffull);
+          uint64_t* row_list = lists + row * 32;
+          const uint64_t cur = row_list[lane];
+          const int pos = __popc(__ballot_sync(kFullMask, cur > key));
+          if (pos < K) {
+            const uint64_t up = __shfl_up_sync(kFullMask, cur, 1);
+            const uint64_t ne = lane < pos ? cur : (lane == pos ? key : up);
+            row_list[lane] = ne;
+            if (lane == K - 1)
+              *reinterpret_cast<volatile float*>(&floor_s[row]) =
+                  ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+          }
+        }
+        if (lane < count) *reinterpret_cast<volatile uint64_t*>(&q->slot[(head + lane) & (kQueueSlots - 1)]) = 0;
+        __threadfence_block();
+        __syncwarp();
+        head += count;
+        if (lane == 0) *reinterpret_cast<volatile uint32_t*>(&q->head) = head;
       }
       if (!ok) break;
       __syncwarp();
-      // lane j writes entry j of each of the warp's rows: coalesced [row][width] stores
-      for (int r = 0; r < 32; ++r) {
-        const int64_t row = static_cast<int64_t>(pair) * kUnitRows + (row_in_unit - lane) + r;
+      // lane j writes entry j of each row: coalesced [row][width] stores, then reset the list
+      for (int r = 0; r < 64; ++r) {
+        const int ew = 2 * iw + (r >> 5);
+        const int64_t row = static_cast<int64_t>(pair) * kUnitRows + (ew >> 2) * kBlockRows + ((ew + 2) & 3) * 32 + (r & 31);
+        const uint64_t e = lists[r * 32 + lane];
         if (row < p.rows && lane < K) {
-          const uint64_t e = list[r * 32 + lane];
           const int64_t at = (static_cast<int64_t>(split) * p.rows + row) * K + lane;
           p.out_score[at] = e ? from_orderable_bits(static_cast<uint32_t>(e >> 32)) : -INFINITY;
-          p.out_slot[at] = e ? static_cast<int32_t>(p.col_base + static_cast<uint32_t>(e)) : -1;
+          p.out_slot[at] = e ? static_cast<int32_t>(p.col_base + static_cast<int64_t>(e & 0xffffffull)) : -1;
         }
+        lists[r * 32 + lane] = 0;
       }
+      floor_s[lane] = -INFINITY;
+      floor_s[32 + lane] = -INFINITY;
+      __threadfence_block();
       __syncwarp();
+      ++units_done;
+      if (lane == 0) *reinterpret_cast<volatile uint32_t*>(&q->epoch) = units_done;
     }
   }
 
@@ -538,7 +636,7 @@ extern "C" int glsdm_score_topk(const void* queries, const void* keys, int64_t r
   if (queries == nullptr || keys == nullptr || out_score == nullptr || out_slot == nullptr) return GLSDM_ERR_ARGUMENT;
   if (rows < 0 || slots < 1 || width < 1 || col_base < 0) return GLSDM_ERR_ARGUMENT;
   if (dk != 64 && dk != 128) return GLSDM_ERR_UNSUPPORTED;
-  if (width > 32 || col_base + slots > 0x7fffffffll) return GLSDM_ERR_UNSUPPORTED;
+  if (width > 32 || col_base + slots > 0x7fffffffll || slots > kMaxSlotsPerCall) return GLSDM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
   const int sms = sm_count();
