@@ -584,13 +584,13 @@ struct Plan {
 
 // Pick the number of slot-range splits. Every split restarts its rows' lists from nothing and
 // pays the insert-heavy start again (about k*ln(columns/k) inserts per row), so the slot range
-// is split only into pieces of at least 8192 key tiles (1M slots), and only as far as that
+// is split only into pieces of at least 32768 key tiles (4M slots), and only as far as that
 // fills the SMs in whole waves.
 Plan make_plan(int64_t rows, int64_t slots, int sms) {
   Plan pl;
   pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
   pl.tiles_total = static_cast<int>((slots + kTileCols - 1) / kTileCols);
-  const int max_splits = pl.tiles_total / 8192 > 0 ? (pl.tiles_total / 8192 < 64 ? pl.tiles_total / 8192 : 64) : 1;
+  const int max_splits = pl.tiles_total / 32768 > 0 ? (pl.tiles_total / 32768 < 64 ? pl.tiles_total / 32768 : 64) : 1;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= max_splits; ++s) {
