@@ -116,3 +116,20 @@ def test_flat_selection_rule_equals_product_key_rule():
         slot, w = oracle.canonical_routes(slot, score)
         assert np.array_equal(slot.reshape(index.shape), index)
         np.testing.assert_allclose(w.reshape(weights.shape), weights, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_oracle_replays_the_recorded_stack_calls(dtype):
+    """Every routed_read / commit call of a reference stack prefill (tests/golden/stack_trace_*)."""
+    t = load_golden(f"stack_trace_{dtype}")
+    for i in range(int(t["reads"])):
+        readings, index, weights = oracle.routed_read(t[f"bank{int(t[f'read{i}_bank'])}"], t[f"read{i}_scores"],
+                                                      int(t[f"read{i}_width"]))
+        assert np.array_equal(index, t[f"read{i}_index"])
+        np.testing.assert_allclose(weights, t[f"read{i}_weights"], rtol=1e-6, atol=1e-7)
+        np.testing.assert_allclose(readings, t[f"read{i}_readings"], rtol=1e-5, atol=1e-6)
+    for i in range(int(t["commits"])):
+        n = int(t[f"commit{i}_proposals"])
+        cat = lambda name: np.concatenate([t[f"commit{i}_{name}{j}"] for j in range(n)])  # noqa: E731
+        out = oracle.commit(t[f"bank{int(t[f'commit{i}_bank'])}"], cat("addresses"), cat("deltas"), cat("keys"))
+        np.testing.assert_array_equal(out, t[f"bank{int(t[f'commit{i}_result'])}"])
