@@ -358,6 +358,51 @@ __device__ __forceinline__ void apply_row(const T* in_row, T* out_row, const Sli
   }
 }
 
+// The same update split in two, so that several rows' old values can be in flight at once:
+// load_bank returns this lane's columns of a bank row as fp32, store_bank rounds and stores.
+template <typename T, int V>
+__device__ __forceinline__ void load_bank(const T* row, Slice<V>& out, int lane) {
+  if constexpr (V % 4 == 0) {
+#pragma unroll
+    for (int c = 0; c < V / 4; ++c) {
+      const int col = column_of<V>(lane, c * 4);
+      if constexpr (sizeof(T) == 4) {
+        const float4 o = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + col);
+        out.v[c * 4] = o.x; out.v[c * 4 + 1] = o.y; out.v[c * 4 + 2] = o.z; out.v[c * 4 + 3] = o.w;
+      } else {
+        const uint2 o = *reinterpret_cast<const uint2*>(row + col);
+        out.v[c * 4] = bf16_lo(o.x); out.v[c * 4 + 1] = bf16_hi(o.x);
+        out.v[c * 4 + 2] = bf16_lo(o.y); out.v[c * 4 + 3] = bf16_hi(o.y);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) out.v[i] = load_value<T>(row + column_of<V>(lane, i));
+  }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void store_bank(T* row, const Slice<V>& in, int lane) {
+  if constexpr (V % 4 == 0) {
+#pragma unroll
+    for (int c = 0; c < V / 4; ++c) {
+      const int col = column_of<V>(lane, c * 4);
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + col) =
+            make_float4(in.v[c * 4], in.v[c * 4 + 1], in.v[c * 4 + 2], in.v[c * 4 + 3]);
+      } else {
+        uint2 n;
+        n.x = pack_bf16x2(in.v[c * 4], in.v[c * 4 + 1]);
+        n.y = pack_bf16x2(in.v[c * 4 + 2], in.v[c * 4 + 3]);
+        *reinterpret_cast<uint2*>(row + col) = n;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) store_value<T>(row + column_of<V>(lane, i), in.v[i]);
+  }
+}
+
 // Sum entries [start, start+count) of the sorted order, strictly left to right.
 template <int V>
 __device__ __forceinline__ void sum_run(Slice<V>& acc, const uint32_t* __restrict__ ids,
@@ -436,7 +481,43 @@ reduce_kernel(Workspace w, ReduceArgs a) {
   const int64_t at = first + lane;
   const int64_t mine = at < a.entries ? sorted[at] : -1;
   const int64_t prev = (at > 0 && at < a.entries) ? sorted[at - 1] : -2;
-  unsigned heads = __ballot_sync(kFullMask, at < a.entries && (at == 0 || mine != prev));
+  const bool is_head = at < a.entries && (at == 0 || mine != prev);
+  const unsigned all_heads = __ballot_sync(kFullMask, is_head);
+  unsigned heads = all_heads;
+  if constexpr (V > 0) {
+    // Fast path for addresses that received exactly one entry (the common case): four such
+    // rows at a time, all their delta rows and old bank rows requested before any is used.
+    const int64_t next = (at + 1 < a.entries) ? sorted[at + 1] : -3;
+    const int64_t mine_local = mine - a.row_base;
+    const uint32_t my_id = at < a.entries ? ids[at] : 0u;
+    unsigned singles = __ballot_sync(kFullMask, is_head && mine != next && mine_local >= 0 && mine_local < a.bank_rows);
+    heads &= ~singles;
+    while (singles) {
+      int pick[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        pick[j] = singles ? __ffs(singles) - 1 : -1;
+        if (singles) singles &= singles - 1;
+      }
+      Slice<V> delta[4], old[4];
+      int64_t where[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (pick[j] < 0) continue;
+        const uint32_t e = __shfl_sync(kFullMask, my_id, pick[j]);
+        where[j] = __shfl_sync(kFullMask, mine_local, pick[j]);
+        load_delta<V>(delta[j], a.deltas + static_cast<int64_t>(e) * a.dim, lane);
+        load_bank<T, V>(static_cast<const T*>(a.values_in) + where[j] * a.dim, old[j], lane);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (pick[j] < 0) continue;
+#pragma unroll
+        for (int i = 0; i < V; ++i) old[j].v[i] = __fadd_rn(old[j].v[i], __fadd_rn(0.f, delta[j].v[i]));
+        store_bank<T, V>(static_cast<T*>(a.values_out) + where[j] * a.dim, old[j], lane);
+      }
+    }
+  }
   while (heads) {
     const int h = __ffs(heads) - 1;
     heads &= heads - 1;
@@ -450,8 +531,9 @@ reduce_kernel(Workspace w, ReduceArgs a) {
     // The next head inside this warp's 32 positions ends the segment; only a segment that
     // runs to the end of the batch has to look at the following positions.
     int64_t len;
-    if (heads) {
-      len = (__ffs(heads) - 1) - h;
+    const unsigned later = h == 31 ? 0u : (all_heads & (0xffffffffu << (h + 1)));
+    if (later) {
+      len = (__ffs(later) - 1) - h;
     } else {
       const int64_t tail = first + 32 < a.entries ? first + 32 : a.entries;
       len = tail - start;
