@@ -154,7 +154,8 @@ def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
     times = []
     for i in range(warmup + steps):
         if routing == "dense":
-            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs_dense(w, gen, 7000 + i, seqs, tokens).items()}
+            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs_dense(w, gen, 7000 + i, seqs, tokens,
+                                                                          keys=keys.to(gen)).items()}
             t0 = time.perf_counter()
             port.dense_epoch(bank, keys, x["q"], x["kq"], w.width, x["target"].float(), x["beta"], x["log_decay"], w.chunk)
         else:
@@ -210,10 +211,10 @@ class Runner:
         if routing == "dense":
             keys = workloads.make_keys(w, dev)
             self.op = ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk, keys=keys)
-            del keys
             self.names = ("q", "kq", "target", "beta", "log_decay")
-            self.epochs = [workloads.make_epoch_inputs_dense(w, dev, 1000 * (rank + 1) + e, seqs_local)
+            self.epochs = [workloads.make_epoch_inputs_dense(w, dev, 1000 * (rank + 1) + e, seqs_local, keys=keys)
                            for e in range(w.epochs)]
+            del keys
         else:
             self.op = (ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk) if world > 1
                        else SharedBankOperator(bank, w.width, w.width, chunk_size=w.chunk))

@@ -583,21 +583,24 @@ struct Plan {
 };
 
 // Pick the number of slot-range splits. Every split restarts its rows' lists from nothing and
-// pays the insert-heavy start again (about k*ln(columns/k) inserts per row), so the slot range
-// is split only into pieces of at least 32768 key tiles (4M slots), and only as far as that
-// fills the SMs in whole waves.
-Plan make_plan(int64_t rows, int64_t slots, int sms) {
+// pays the insert-heavy start again (about k*ln(columns/k) inserts per row, measured at
+// roughly 220*k key-tile times per unit), so the model is
+//   time(s) = waves(s) * (tiles per split + 220*k),  waves = ceil(row pairs * s / SMs),
+// minimised over s with at least 1024 key tiles per split; ties prefer fewer splits.
+Plan make_plan(int64_t rows, int64_t slots, int sms, int width) {
   Plan pl;
   pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
   pl.tiles_total = static_cast<int>((slots + kTileCols - 1) / kTileCols);
-  const int max_splits = pl.tiles_total / 32768 > 0 ? (pl.tiles_total / 32768 < 64 ? pl.tiles_total / 32768 : 64) : 1;
+  const int64_t restart = 220ll * width;
   int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= max_splits; ++s) {
+  int64_t best_cost = -1;
+  for (int s = 1; s <= 64; ++s) {
+    const int64_t per = (pl.tiles_total + s - 1) / s;
+    if (s > 1 && per < 1024) break;
     const int64_t units = static_cast<int64_t>(pl.unit_pairs) * s;
     const int64_t waves = (units + sms - 1) / sms;
-    const double eff = static_cast<double>(units) / static_cast<double>(waves * sms);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    const int64_t cost = waves * (per + restart);
+    if (best_cost < 0 || cost * 100 < best_cost * 97) { best_cost = cost; best = s; }
   }
   pl.splits = best;
   pl.tiles_per_split = (pl.tiles_total + best - 1) / best;
@@ -624,7 +627,7 @@ using namespace glsdm;
 extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;
-  const Plan pl = make_plan(rows, slots, sm_count());
+  const Plan pl = make_plan(rows, slots, sm_count(), width);
   if (pl.splits <= 1) return 256;
   return static_cast<size_t>(pl.splits) * rows * width * 8 + 512;
 }
@@ -640,7 +643,7 @@ extern "C" int glsdm_score_topk(const void* queries, const void* keys, int64_t r
   if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
   const int sms = sm_count();
-  const Plan pl = make_plan(rows, slots, sms);
+  const Plan pl = make_plan(rows, slots, sms, width);
   Params p;
   p.rows = rows;
   p.slots = slots;

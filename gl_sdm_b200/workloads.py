@@ -124,13 +124,25 @@ def make_keys(w, device, seed=4321):
     return out
 
 
-def make_epoch_inputs_dense(w, device, seed, sequences=None, tokens=None):
-    """Queries (read and write side) N(0,1) bf16 and the write operands of one commit epoch."""
+def make_epoch_inputs_dense(w, device, seed, sequences=None, tokens=None, keys=None, plant=6.0):
+    """Queries (read and write side) N(0,1) bf16 and the write operands of one commit epoch.
+
+    With w.zipf > 0 and the slot keys given, every query is pulled toward the key of a target
+    slot drawn from the Zipf popularity (q = plant * key[target] + N(0,1)), so routes pile up
+    on hot slots."""
     g = torch.Generator(device=device).manual_seed(seed)
     n, t = sequences or w.sequences, tokens or w.chunk
+
+    def queries():
+        x = torch.randn((n, t, w.dk), generator=g, device=device)
+        if w.zipf > 0 and keys is not None:
+            target = zipf_targets(w, n * t, g, device)
+            x = x + plant * keys[target].float().view(n, t, w.dk)
+        return x.to(torch.bfloat16)
+
     out = {
-        "q": torch.randn((n, t, w.dk), generator=g, device=device).to(torch.bfloat16),
-        "kq": torch.randn((n, t, w.dk), generator=g, device=device).to(torch.bfloat16),
+        "q": queries(),
+        "kq": queries(),
         "target": (torch.randn((n, t, 1, w.dim), generator=g, device=device) * 0.02).to(
             torch.bfloat16 if w.bank_dtype == torch.bfloat16 else torch.float32),
         "beta": torch.randn((n, t, 1), generator=g, device=device).sigmoid(),
