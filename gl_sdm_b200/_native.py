@@ -57,6 +57,8 @@ SIGNATURES = {
     "glsdm_commit_static_max_entries": (_i64, []),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
     "glsdm_score_topk": (_i, [_p, _p, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
+    "glsdm_score_topk_pitched": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
+    "glsdm_pk_combine": (_i, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),
 }
 
@@ -452,3 +454,39 @@ def score_topk(queries, keys, width, col_base=0, out=None):
                                 _ptr(slot), _ptr(work), work.numel(), _ptr(status_word(queries.device)),
                                 _stream(queries.device)))
     return score, slot
+
+
+def pk_gemm_select(queries, codebooks, width, index_dtype=torch.int64):
+    """Product-key routing without materialising factor scores.
+
+    queries [rows, dk] bf16 (left sub-query in the first dk/2 columns), codebooks
+    [2, half, dk/2] bf16. Each factor's scores are computed on the tensor cores with a fused
+    top-k (glsdm_score_topk_pitched), then combined (glsdm_pk_combine).
+    Returns (index [rows, k] ascending, softmax weights [rows, k]).
+    """
+    require_cuda(queries, codebooks)
+    if queries.dtype != torch.bfloat16 or codebooks.dtype != torch.bfloat16:
+        raise ValueError("queries and codebooks must be bfloat16")
+    rows, dk = queries.shape
+    _, half, sub = codebooks.shape
+    if codebooks.shape[0] != 2 or sub * 2 != dk:
+        raise ValueError("codebooks must be [2, half, dk/2]")
+    lib = library()
+    kf = min(width, half)
+    k = routes_out(width, half)
+    dev = queries.device
+    lists = []
+    for f in range(2):
+        score = torch.empty((rows, kf), dtype=torch.float32, device=dev)
+        index = torch.empty((rows, kf), dtype=torch.int32, device=dev)
+        nbytes = lib.glsdm_score_topk_workspace_bytes(rows, half, sub, kf)
+        work = _workspace(dev, nbytes)
+        _check(lib.glsdm_score_topk_pitched(ctypes.c_void_p(queries.data_ptr() + 2 * f * sub), dk, _ptr(codebooks[f]), sub,
+                                            rows, half, sub, kf, 0, _ptr(score), _ptr(index), _ptr(work), work.numel(),
+                                            _ptr(status_word(dev)), _stream(dev)))
+        lists.append((score, index))
+    out_index = torch.empty((rows, k), dtype=index_dtype, device=dev)
+    out_weights = torch.empty((rows, k), dtype=torch.float32, device=dev)
+    _check(lib.glsdm_pk_combine(_ptr(lists[0][0]), _ptr(lists[0][1]), _ptr(lists[1][0]), _ptr(lists[1][1]), rows, half,
+                                width, _ptr(out_index), int(index_dtype == torch.int64), _ptr(out_weights), _stream(dev)))
+    return out_index, out_weights

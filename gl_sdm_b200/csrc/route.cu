@@ -271,6 +271,28 @@ token_propose_kernel(const T* __restrict__ values, int64_t banks, int heads, int
   }
 }
 
+// Product-key routing from per-factor candidate lists (the output of two glsdm_score_topk
+// calls, one per sub-key codebook): combine, select, canonical order, softmax.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+pk_combine_kernel(const float* __restrict__ left_score, const int32_t* __restrict__ left_index,
+                  const float* __restrict__ right_score, const int32_t* __restrict__ right_index,
+                  int64_t rows, int half, int kf, int kout, void* out_index, int i64, float* out_weights) {
+  __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  uint64_t left = 0, right = 0;
+  if (lane < kf) {
+    const int64_t at = row * kf + lane;
+    left = pack_key(orderable_bits(left_score[at]), static_cast<uint32_t>(left_index[at]));
+    right = pack_key(orderable_bits(right_score[at]), static_cast<uint32_t>(right_index[at]));
+  }
+  uint32_t slot;
+  float weight;
+  pk_combine_lists(left, right, half, kf, kout, stage[warp], lane, slot, weight);
+  store_routes(out_index, i64 != 0, out_weights, row, kout, lane, slot, weight);
+}
+
 int route_shape(int32_t half, int32_t width, int* kf, int* kout) {
   if (half < 1 || width < 1) return GLSDM_ERR_ARGUMENT;
   if (half > 65536) return GLSDM_ERR_UNSUPPORTED;
@@ -485,6 +507,22 @@ extern "C" int glsdm_token_propose(const glsdm_bank* bank, const int64_t* reques
         static_cast<const __nv_bfloat16*>(bank->values), bank->banks, bank->heads, bank->slots, bank->dim, requests,
         index, index_i64, weights, target, beta, log_decay, mass, rows, width, out_addresses, out_deltas, device_status);
   GLSDM_CUDA_OK(cudaGetLastError(), "token_propose launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_pk_combine(const float* left_score, const int32_t* left_index, const float* right_score,
+                                const int32_t* right_index, int64_t rows, int32_t half, int32_t width,
+                                void* out_index, int index_i64, float* out_weights, glsdm_stream_t stream) {
+  int kf, kout;
+  if (int s = route_shape(half, width, &kf, &kout)) return s;
+  if (left_score == nullptr || left_index == nullptr || right_score == nullptr || right_index == nullptr ||
+      out_index == nullptr || out_weights == nullptr || rows < 0)
+    return GLSDM_ERR_ARGUMENT;
+  if (rows == 0) return GLSDM_OK;
+  pk_combine_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+      left_score, left_index, right_score, right_index, rows, half, kf, kout, out_index, index_i64, out_weights);
+  GLSDM_CUDA_OK(cudaGetLastError(), "pk_combine launch");
   count_launches(1);
   return GLSDM_OK;
 }

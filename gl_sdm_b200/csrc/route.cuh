@@ -67,6 +67,9 @@ __device__ __forceinline__ void offer_factor(WarpSelect& sel, const float* __res
   sel.finish();
 }
 
+__device__ __forceinline__ void pk_combine_lists(uint64_t left, uint64_t right, int half, int kf, int kout,
+                                                 uint64_t* stage, int lane, uint32_t& slot, float& weight);
+
 // Product-key selection for one row (reference gl_sdm/memory/routing.py:10-26).
 //   per factor: the kf = min(width, half) best (score desc, index desc);
 //   candidates: all kf*kf sums left[i] + right[j] (one fp32 add) at slot i*half + j;
@@ -82,7 +85,16 @@ __device__ __forceinline__ void pk_route_row(const float* __restrict__ row_score
   sel.init(stage, kf, lane);
   offer_factor(sel, row_scores + half, half, lane);
   const uint64_t right = sel.list;
+  pk_combine_lists(left, right, half, kf, kout, stage, lane, slot, weight);
+}
 
+// Second stage of the product-key selection: lanes [0, kf) hold the factor lists (key =
+// orderable score << 32 | factor index, best first). All kf*kf sums left[i] + right[j] (one
+// fp32 add) at slot i*half + j compete; the kout best (sum desc, slot desc) come back
+// slot-ascending with softmax weights (reference gl_sdm/memory/routing.py:19-26).
+__device__ __forceinline__ void pk_combine_lists(uint64_t left, uint64_t right, int half, int kf, int kout,
+                                                 uint64_t* stage, int lane, uint32_t& slot, float& weight) {
+  WarpSelect sel;
   const bool right_live = lane < kf;
   const float right_score = from_orderable_bits(static_cast<uint32_t>(right >> 32));
   const uint32_t right_index = static_cast<uint32_t>(right);

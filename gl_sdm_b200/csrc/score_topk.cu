@@ -636,6 +636,15 @@ extern "C" int glsdm_score_topk(const void* queries, const void* keys, int64_t r
                                 int32_t width, int64_t col_base, float* out_score, int32_t* out_slot,
                                 void* workspace, size_t workspace_bytes, uint32_t* device_status,
                                 glsdm_stream_t stream) {
+  return glsdm_score_topk_pitched(queries, dk, keys, dk, rows, slots, dk, width, col_base, out_score, out_slot,
+                                  workspace, workspace_bytes, device_status, stream);
+}
+
+extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch, const void* keys,
+                                        int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                                        int64_t col_base, float* out_score, int32_t* out_slot, void* workspace,
+                                        size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream) {
+  if (query_pitch < dk || key_pitch < dk || (query_pitch % 8) || (key_pitch % 8)) return GLSDM_ERR_ARGUMENT;
   if (queries == nullptr || keys == nullptr || out_score == nullptr || out_slot == nullptr) return GLSDM_ERR_ARGUMENT;
   if (rows < 0 || slots < 1 || width < 1 || col_base < 0) return GLSDM_ERR_ARGUMENT;
   if (dk != 64 && dk != 128) return GLSDM_ERR_UNSUPPORTED;
@@ -665,7 +674,7 @@ extern "C" int glsdm_score_topk(const void* queries, const void* keys, int64_t r
     p.out_slot = out_slot;
   }
   CUtensorMap map_q, map_k;
-  if (!make_map(&map_q, queries, rows, dk, dk) || !make_map(&map_k, keys, slots, dk, dk)) {
+  if (!make_map(&map_q, queries, rows, dk, query_pitch) || !make_map(&map_k, keys, slots, dk, key_pitch)) {
     note_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
     return GLSDM_ERR_CUDA;
   }

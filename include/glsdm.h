@@ -229,6 +229,23 @@ int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_
                      int32_t* out_slot, void* workspace, size_t workspace_bytes,
                      uint32_t* device_status, glsdm_stream_t stream);
 
+/* The same with row pitches (in elements, multiples of 8): a query matrix whose rows hold
+ * several sub-queries, e.g. the two halves of a product-key query. */
+int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch, const void* keys,
+                             int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                             int64_t col_base, float* out_score, int32_t* out_slot, void* workspace,
+                             size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
+
+/* Product-key routing from per-factor candidate lists: second stage of
+ * gl_sdm/memory/routing.py:19-26 (candidate sums, selection, canonical order, softmax). The
+ * lists [rows, min(width, half)] (score, factor index; best first) are what two
+ * glsdm_score_topk calls produce for queries x sub-key codebooks [half, dk/2], so the factor
+ * score matrix [rows, 2*half] that gl_sdm/layers/global_layer.py:26 materialises is never
+ * written. out_index / out_weights as in glsdm_pk_select. */
+int glsdm_pk_combine(const float* left_score, const int32_t* left_index, const float* right_score,
+                     const int32_t* right_index, int64_t rows, int32_t half, int32_t width,
+                     void* out_index, int index_i64, float* out_weights, glsdm_stream_t stream);
+
 /* Merge per-shard candidates into the global routes (tie rule and softmax of
  * gl_sdm/memory/routing.py:21-26 applied to `parts` candidate lists per row).
  *   cand_score / cand_slot [parts, rows, width]; out_index ascending, out_weights softmax. */

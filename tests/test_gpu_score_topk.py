@@ -101,3 +101,29 @@ def test_score_topk_feeds_the_merge_and_read(native):
     want = oracle.weighted_read(bank.cpu().numpy(), index.cpu().numpy().reshape(1, 128, 1, 8),
                                 weights.cpu().numpy().reshape(1, 128, 1, 8))
     np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("rows,half,width", [(300, 256, 8), (1024, 1024, 32), (130, 64, 16)])
+def test_pk_gemm_select_matches_the_product_key_oracle(native, rows, half, width):
+    """Product-key routing straight from queries and sub-key codebooks (factor scores never
+    materialised): routes equal the oracle's except on rows with a near-tie at a boundary."""
+    g = torch.Generator().manual_seed(rows + half)
+    q = torch.randn(rows, 128, generator=g).bfloat16()
+    books = torch.randn(2, half, 64, generator=g)
+    books = (books / books.norm(dim=-1, keepdim=True)).bfloat16()
+    index, weights = native.pk_gemm_select(q.to(DEV), books.to(DEV), width)
+    native.raise_on_device_status(DEV)
+    scores = oracle.pk_gemm_scores(q.float().numpy(), books.float().numpy())
+    want_index, want_weights = oracle.select_routes(scores.reshape(1, rows, 1, -1), width)
+    want_index, want_weights = want_index.reshape(rows, -1), want_weights.reshape(rows, -1)
+    got = index.cpu().numpy()
+    assert (np.diff(got, axis=1) > 0).all() and got.min() >= 0 and got.max() < half * half
+    same = (got == want_index).all(1)
+    assert same.mean() > 0.95, f"{(~same).sum()} of {rows} rows differ"
+    np.testing.assert_allclose(weights.cpu().numpy()[same], want_weights[same], rtol=1e-4, atol=1e-5)
+    # rows that differ must differ only through candidates whose sums tie within rounding
+    left, right = scores[:, :half], scores[:, half:]
+    for r in np.flatnonzero(~same):
+        boundary = np.sort((left[r][:, None] + right[r][None, :]).ravel())[-width]
+        for s in set(got[r]) ^ set(want_index[r]):
+            assert abs(left[r, s // half] + right[r, s % half] - boundary) <= 2 * EPS
