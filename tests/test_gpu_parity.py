@@ -282,3 +282,51 @@ def test_topk_merge_matches_oracle(native):
     want_slot, want_w = oracle.merge_candidates(slot.numpy(), score.numpy(), width)
     np.testing.assert_array_equal(cpu(index), want_slot)
     np.testing.assert_allclose(cpu(weights), want_w, rtol=1e-5, atol=1e-6)
+
+
+# ---- edge cases -----------------------------------------------------------------------------------
+
+def test_empty_and_minimal_shapes(native):
+    """Zero rows launch nothing; one slot, one route and width > slots behave as the reference
+    (projects/gl-sdm/src/gl_sdm/memory/routing.py slices what exists)."""
+    bank = torch.randn(1, 1, 1, 4, device=DEV)
+    out, index, weights = native.pk_select_read(bank, torch.zeros(1, 3, 1, 2, device=DEV), 1, rows_per_bank=3)
+    assert index.flatten().tolist() == [0, 0, 0] and weights.flatten().tolist() == [1.0, 1.0, 1.0]
+    assert torch.equal(out, bank.expand(1, 3, 1, 4))
+    empty_scores = torch.zeros(1, 0, 1, 2, device=DEV)
+    out, index, weights = native.pk_select_read(bank, empty_scores, 1, rows_per_bank=1)
+    assert out.shape == (1, 0, 1, 4) and index.numel() == 0
+    # width larger than the slots of a 2 x 2 product: all four slots, ascending
+    bank4 = torch.randn(1, 1, 4, 8, device=DEV)
+    scores = torch.tensor([[[[0.5, -1.0, 2.0, 0.25]]]], device=DEV)
+    out, index, weights = native.pk_select_read(bank4, scores, 7, rows_per_bank=1)
+    want_read, want_index, want_w = oracle.routed_read(bank4.cpu().numpy(), scores.cpu().numpy(), 7)
+    np.testing.assert_array_equal(cpu(index), want_index)
+    np.testing.assert_allclose(cpu(weights), want_w, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(cpu(out), want_read, rtol=1e-5, atol=1e-6)
+
+
+def test_unsupported_shapes_are_refused_not_approximated(native):
+    bank = torch.zeros(1, 1, 64 * 64, 8, device=DEV)
+    with pytest.raises(ValueError, match="not supported"):
+        native.pk_select(torch.zeros(2, 128, device=DEV), 33)          # more than 32 routes
+    with pytest.raises(ValueError, match="invalid argument"):
+        native.pk_select_read(bank, torch.zeros(1, 2, 1, 64, device=DEV), 4, rows_per_bank=2)  # half^2 != slots
+    with pytest.raises(ValueError, match="float32"):
+        native.pk_select(torch.zeros(2, 128, device=DEV, dtype=torch.bfloat16), 4)
+    with pytest.raises(ValueError, match="contiguous CUDA"):
+        native.pk_select(torch.zeros(2, 256, device=DEV)[:, ::2], 4)
+
+
+def test_nan_and_infinite_scores_follow_the_sort_order_of_the_reference(native):
+    """torch sorts NaN above +inf; -inf stays last; the selection must agree on the slots."""
+    g = torch.Generator().manual_seed(2)
+    scores = torch.randn(1, 16, 1, 32, generator=g)
+    scores[0, 0, 0, 3] = float("inf")
+    scores[0, 1, 0, 5] = float("-inf")
+    scores[0, 2, 0, :16] = float("-inf")
+    scores[0, 3, 0, 20] = float("inf")
+    scores[0, 3, 0, 2] = float("inf")
+    index, _ = native.pk_select(scores.to(DEV), 4)
+    want, _ = oracle.select_routes(scores.numpy(), 4)
+    np.testing.assert_array_equal(cpu(index), want)
