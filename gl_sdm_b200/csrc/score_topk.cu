@@ -27,172 +27,12 @@
 //
 // Tie rule (gl_sdm/memory/routing.py:21-24): equal scores prefer the larger slot. Slots are
 // scanned in ascending order, so a score equal to the current k-th one replaces it.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "score_topk_pair.cuh"
 
 namespace glsdm {
 namespace {
 
-constexpr int kBlockRows = 128;                 // rows of one MMA (M)
-constexpr int kUnitRows = 2 * kBlockRows;       // rows handled by one CTA unit
-constexpr int kTileCols = 128;                  // slots per key tile (MMA N)
-constexpr int kStages = 3;
-constexpr int kAtomK = 64;                      // bf16 elements per 128-byte swizzle row
-constexpr int kSubTileBytes = kBlockRows * 128; // one [128 x 64] bf16 sub-tile, 16 KB
-constexpr int kEpilogueWarps = 8;                // scanner warps
-constexpr int kInsertWarps = 4;                  // one per pair of scanner warps (64 rows)
-constexpr int kThreads = 32 * (2 + kEpilogueWarps + kInsertWarps);
-constexpr int kQueueSlots = 32;                  // entries per inserter queue (one per lane)
-constexpr int64_t kMaxSlotsPerCall = 1 << 24;    // a queue entry carries a 24-bit slot
-constexpr int kTmemCols = 512;
-constexpr uint32_t kSpinLimit = 1u << 24;
-
-struct Params {
-  int64_t rows;
-  int64_t slots;
-  int64_t col_base;
-  int dk;
-  int width;
-  int splits;
-  int tiles_per_split;
-  int tiles_total;
-  int unit_pairs;       // ceil(rows / 256)
-  float* out_score;     // [splits][rows][width] (or the final output when splits == 1)
-  int32_t* out_slot;
-  uint32_t* device_status;
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
-// Bounded wait. Returns false when the wait ran out or another role has aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
-// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
-  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
-  d |= static_cast<uint64_t>(1) << 46;                            // version
-  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 128.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kTileCols >> 3) << 17) |
-                                ((kBlockRows >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, bool accumulate) {
-  const uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(acc)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-
-__device__ __forceinline__ uint32_t tmem_load1(uint32_t taddr) {
-  uint32_t r;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-  return r;
-}
-
-__device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Candidate queue of one inserter warp (multi-producer: two scanner warps; one consumer).
-// An entry is orderable score << 32 | row (6 bits) << 24 | slot (24 bits); 0 = empty slot.
-struct Queue {
-  uint64_t slot[kQueueSlots];
-  uint32_t tail;    // entries reserved so far (producers, atomicAdd)
-  uint32_t head;    // entries consumed so far (consumer)
-  uint32_t done;    // scanner warps that have finished pushing, summed over units
-  uint32_t epoch;   // units whose lists the consumer has written out and reset
-};
-
-// Push the entries of the lanes in `m` (warp-uniform). Space is reserved with one atomic per
-// call; a lane waits (bounded) until the consumer has freed the ring slot it was given.
-__device__ __forceinline__ bool queue_push(Queue* q, unsigned m, bool pass, uint64_t entry, int lane,
-                                           volatile int* abort_flag) {
-  uint32_t base = 0;
-  if (lane == 0) base = atomicAdd(&q->tail, static_cast<uint32_t>(__popc(m)));
-  base = __shfl_sync(kFullMask, base, 0);
-  bool ok = true;
-  if (pass) {
-    const uint32_t at = base + __popc(m & ((1u << lane) - 1u));
-    uint32_t spin = 0;
-    while (static_cast<int32_t>(at - *reinterpret_cast<volatile uint32_t*>(&q->head)) >= kQueueSlots) {
-      if (++spin >= kSpinLimit || ((spin & 1023u) == 0 && *abort_flag)) { ok = false; break; }
-    }
-    if (ok) *reinterpret_cast<volatile uint64_t*>(&q->slot[at & (kQueueSlots - 1)]) = entry;
-  }
-  if (!__all_sync(kFullMask, ok)) { *abort_flag = 1; return false; }
-  return true;
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+using namespace dense;
 
 struct Barriers {
   uint64_t a_full;
@@ -384,16 +224,7 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const float floor = *my_floor;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            float m0 = __uint_as_float(r[c * 32]), m1 = __uint_as_float(r[c * 32 + 1]),
-                  m2 = __uint_as_float(r[c * 32 + 2]), m3 = __uint_as_float(r[c * 32 + 3]);
-#pragma unroll
-            for (int i = 4; i < 32; i += 4) {
-              m0 = fmaxf(m0, __uint_as_float(r[c * 32 + i]));
-              m1 = fmaxf(m1, __uint_as_float(r[c * 32 + i + 1]));
-              m2 = fmaxf(m2, __uint_as_float(r[c * 32 + i + 2]));
-              m3 = fmaxf(m3, __uint_as_float(r[c * 32 + i + 3]));
-            }
-            const float best = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            const float best = max_of_32(&r[c * 32]);
             if (!__any_sync(kFullMask, best >= floor)) continue;
             // Rare path. Registers cannot be indexed by a run-time column, and handling every
             // column inline would bloat the loop, so: one bit per passing column, then a short
@@ -587,10 +418,10 @@ struct Plan {
 // roughly 220*k key-tile times per unit), so the model is
 //   time(s) = waves(s) * (tiles per split + 220*k),  waves = ceil(row pairs * s / SMs),
 // minimised over s with at least 1024 key tiles per split; ties prefer fewer splits.
-Plan make_plan(int64_t rows, int64_t slots, int sms, int width) {
+Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = kTileCols) {
   Plan pl;
   pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
-  pl.tiles_total = static_cast<int>((slots + kTileCols - 1) / kTileCols);
+  pl.tiles_total = static_cast<int>((slots + tile_cols - 1) / tile_cols);
   const int64_t restart = 220ll * width;
   int best = 1;
   int64_t best_cost = -1;
@@ -606,6 +437,19 @@ Plan make_plan(int64_t rows, int64_t slots, int sms, int width) {
   pl.tiles_per_split = (pl.tiles_total + best - 1) / best;
   pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
   return pl;
+}
+
+// Which kernel runs: 0 = one CTA per unit (cta_group::1, the default: measured faster on
+// B200), 1 = a CTA pair per unit (cta_group::2). Set by glsdm_score_topk_variant() or by
+// GLSDM_SCORE_TOPK_PAIR=1 in the environment.
+int g_variant = -1;
+
+bool use_pair() {
+  if (g_variant < 0) {
+    const char* env = getenv("GLSDM_SCORE_TOPK_PAIR");
+    g_variant = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  return g_variant == 1;
 }
 
 int sm_count() {
@@ -624,10 +468,17 @@ int sm_count() {
 
 using namespace glsdm;
 
+extern "C" int glsdm_score_topk_variant(int pair) {
+  const int before = use_pair() ? 1 : 0;
+  if (pair == 0 || pair == 1) g_variant = pair;
+  return before;
+}
+
 extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;
-  const Plan pl = make_plan(rows, slots, sm_count(), width);
+  const Plan pl = use_pair() ? make_plan(rows, slots, sm_count() / 2, width, kPairTileCols)
+                             : make_plan(rows, slots, sm_count(), width);
   if (pl.splits <= 1) return 256;
   return static_cast<size_t>(pl.splits) * rows * width * 8 + 512;
 }
@@ -652,7 +503,8 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
   const int sms = sm_count();
-  const Plan pl = make_plan(rows, slots, sms, width);
+  const bool pair = use_pair();
+  const Plan pl = pair ? make_plan(rows, slots, sms / 2, width, kPairTileCols) : make_plan(rows, slots, sms, width);
   Params p;
   p.rows = rows;
   p.slots = slots;
@@ -680,7 +532,31 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   }
   const int units = pl.unit_pairs * pl.splits;
   const int grid = units < sms ? units : sms;
-  if (dk == 128) {
+  if (pair) {
+    const int clusters = units < sms / 2 ? units : sms / 2;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * clusters);
+    config.blockDim = dim3(kPairThreads);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    if (dk == 128) {
+      config.dynamicSmemBytes = PairLayout<2>::total();
+      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairLayout<2>::total()), "score_topk pair shared memory");
+      GLSDM_CUDA_OK(cudaLaunchKernelEx(&config, score_topk_pair_kernel<2>, map_q, map_k, p), "score_topk pair launch");
+    } else {
+      config.dynamicSmemBytes = PairLayout<1>::total();
+      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairLayout<1>::total()), "score_topk pair shared memory");
+      GLSDM_CUDA_OK(cudaLaunchKernelEx(&config, score_topk_pair_kernel<1>, map_q, map_k, p), "score_topk pair launch");
+    }
+  } else if (dk == 128) {
     const int smem = Layout<2>::total(width);
     GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                   "score_topk shared memory");

@@ -229,6 +229,11 @@ int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_
                      int32_t* out_slot, void* workspace, size_t workspace_bytes,
                      uint32_t* device_status, glsdm_stream_t stream);
 
+/* Choose the kernel behind glsdm_score_topk: 0 = one CTA per unit (tcgen05 cta_group::1,
+ * default), 1 = a CTA pair per unit (cta_group::2, each CTA loads half of every key tile).
+ * Any other value only queries. Returns the previous setting. Same results either way. */
+int glsdm_score_topk_variant(int pair);
+
 /* The same with row pitches (in elements, multiples of 8): a query matrix whose rows hold
  * several sub-queries, e.g. the two halves of a product-key query. */
 int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch, const void* keys,

@@ -54,16 +54,25 @@ def _check(q, keys, width, got_score, got_slot, col_base=0):
     return near_tie_rows
 
 
+@pytest.fixture(params=[0, 1], ids=["one-cta", "cta-pair"])
+def variant(native, request):
+    """Run a test under both kernels behind glsdm_score_topk (cta_group::1 and cta_group::2)."""
+    lib = native.library()
+    before = lib.glsdm_score_topk_variant(request.param)
+    yield request.param
+    lib.glsdm_score_topk_variant(before)
+
+
 @pytest.mark.parametrize("rows,slots,dk,width", [(300, 5000, 128, 32), (256, 4096, 64, 16), (1000, 70000, 128, 32),
                                                  (40, 1000, 128, 8), (513, 16384, 64, 32)])
-def test_score_topk_matches_oracle(native, rows, slots, dk, width):
+def test_score_topk_matches_oracle(native, variant, rows, slots, dk, width):
     q, keys = _case(rows, slots, dk, seed=rows + slots)
     score, slot = native.score_topk(q.to(DEV), keys.to(DEV), width)
     native.raise_on_device_status(DEV)
     _check(q, keys, width, score, slot)
 
 
-def test_score_topk_tie_rule_and_shard_offset(native):
+def test_score_topk_tie_rule_and_shard_offset(native, variant):
     """Duplicated keys give bit-equal scores at slot s and s + slots - 500: the larger slot
     must come first; col_base shifts the reported slots of a shard."""
     q, keys = _case(200, 3000, 128, seed=5, duplicate=500)
