@@ -44,6 +44,7 @@ SIGNATURES = {
     "glsdm_pk_select_read": (_i, [_BANK, _p, _i64, _i64, _i32, _i32, _p, _p, _i, _p, _p, _p]),
     "glsdm_pk_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _i64,
                               _i64, _i32, _i32, _p, _p, _p, _p, _p]),
+    "glsdm_read_backward": (_i, [_BANK, _p, _p, _p, _i, _p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
     "glsdm_gather_rows": (_i, [_p, _i, _i64, _i32, _p, _i64, _p, _p, _p]),
     "glsdm_token_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
     "glsdm_write_error": (_i, [_p, _p, _i, _p, _p, _i64, _i32, _p, _p, _p]),
@@ -491,3 +492,21 @@ def pk_gemm_select(queries, codebooks, width, index_dtype=torch.int64):
     _check(lib.glsdm_pk_combine(_ptr(lists[0][0]), _ptr(lists[0][1]), _ptr(lists[1][0]), _ptr(lists[1][1]), rows, half,
                                 width, _ptr(out_index), int(index_dtype == torch.int64), _ptr(out_weights), _stream(dev)))
     return out_index, out_weights
+
+
+def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half):
+    """Backward of the routed read: (grad_scores [..., 2*half], addresses [rows*k] int64,
+    grad_rows [rows*k, dim]) - the bank gradient stays compact, one row per route."""
+    require_cuda(values, grad_out, grad_weights, index, weights)
+    bank = bank_of(values)
+    width = index.shape[-1]
+    rows = index.numel() // width
+    dim = values.shape[-1]
+    grad_scores = torch.empty((*index.shape[:-1], 2 * half), dtype=torch.float32, device=values.device)
+    grad_rows = torch.empty((rows * width, dim), dtype=torch.float32, device=values.device)
+    addresses = torch.empty(rows * width, dtype=torch.int64, device=values.device)
+    _check(library().glsdm_read_backward(ctypes.byref(bank), _ptr(grad_out), _ptr(grad_weights), _ptr(index),
+                                         int(index.dtype == torch.int64),
+                                         _ptr(weights), rows, rows_per_bank, width, half, _ptr(grad_scores),
+                                         _ptr(grad_rows), _ptr(addresses), _stream(values.device)))
+    return grad_scores, addresses, grad_rows

@@ -293,6 +293,71 @@ pk_combine_kernel(const float* __restrict__ left_score, const int32_t* __restric
   store_routes(out_index, i64 != 0, out_weights, row, kout, lane, slot, weight);
 }
 
+// Backward of the routed read (reference: autograd through gl_sdm/memory/routing.py:19-28;
+// native counterparts gl_sdm/memory/backends/token.py:69-82,134-144). One warp per row.
+//   gw_k   = <g, row_k>                       (gradient of the softmax weights)
+//   gs_k   = w_k * (gw_k - sum_j w_j gw_j)    (softmax backward = gradient of the selected sums)
+//   grad_scores[row, left_k] += gs_k,  grad_scores[row, half + right_k] += gs_k
+//   grad_rows[row*K + k, :] = w_k * g         (compact bank gradient: one row per route)
+// Routes of one row that share a factor index are summed in route order by one lane, so the
+// result does not depend on scheduling. grad_scores is written whole (zeros elsewhere).
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+read_backward_kernel(BankView bank, const float* __restrict__ grad_out, const float* __restrict__ grad_weights,
+                     const void* __restrict__ index, int i64, const float* __restrict__ weights, int64_t rows, int64_t rows_per_bank, int width, int half,
+                     float* __restrict__ grad_scores, float* __restrict__ grad_rows,
+                     int64_t* __restrict__ out_addresses) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  const int dim = bank.dim;
+  const int64_t part = partition_of(bank, row, rows_per_bank, nullptr);
+  const T* base = static_cast<const T*>(bank.values) + part * bank.part_stride_rows * dim;
+  const float* __restrict__ g = grad_out + row * dim;
+  int64_t slot = 0;
+  float w = 0.f;
+  if (lane < width) {
+    const int64_t at = row * width + lane;
+    slot = i64 ? static_cast<const int64_t*>(index)[at] : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
+    w = weights[at];
+    out_addresses[at] = part * bank.slots + slot;
+  }
+  float gw = 0.f;
+  for (int k = 0; k < width; ++k) {
+    const int64_t a = __shfl_sync(kFullMask, slot, k);
+    const float wk = __shfl_sync(kFullMask, w, k);
+    const T* vrow = base + a * dim;
+    float* grow = grad_rows + (row * width + k) * dim;
+    float partial = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+      const float gd = g[d];
+      partial = fmaf(gd, Unit<T>::scalar(vrow + d), partial);
+      grow[d] = __fmul_rn(wk, gd);
+    }
+    const float total = warp_sum(partial);
+    if (lane == k) gw = total;
+  }
+  // the weights are an output too (the write proposal uses them): add their own gradient
+  if (grad_weights != nullptr && lane < width) gw += grad_weights[row * width + lane];
+  const float mean = warp_sum(lane < width ? w * gw : 0.f);
+  const float gs = lane < width ? w * (gw - mean) : 0.f;
+  float* __restrict__ srow = grad_scores + row * 2 * half;
+  for (int c = lane; c < 2 * half; c += 32) srow[c] = 0.f;
+  __syncwarp();
+  const int left = static_cast<int>(slot / half), right = static_cast<int>(slot % half);
+  for (int f = 0; f < 2; ++f) {
+    const int mine = lane < width ? (f == 0 ? left : right) : -1 - lane;   // unused lanes match nobody
+    const unsigned peers = __match_any_sync(kFullMask, mine);
+    // every lane walks all routes (the shuffle needs the whole warp) and keeps its peers' terms
+    float sum = 0.f;
+    for (int k = 0; k < width; ++k) {
+      const float term = __shfl_sync(kFullMask, gs, k);
+      if ((peers >> k) & 1u) sum += term;
+    }
+    if (lane < width && (peers & ((1u << lane) - 1u)) == 0) srow[f * half + mine] = sum;
+  }
+}
+
 int route_shape(int32_t half, int32_t width, int* kf, int* kout) {
   if (half < 1 || width < 1) return GLSDM_ERR_ARGUMENT;
   if (half > 65536) return GLSDM_ERR_UNSUPPORTED;
@@ -314,6 +379,7 @@ using namespace glsdm;
 extern "C" int glsdm_pk_select(const float* scores, int64_t rows, int32_t half, int32_t width,
                                void* out_index, int index_i64, float* out_weights,
                                glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   int kf, kout;
   if (int s = route_shape(half, width, &kf, &kout)) return s;
   if (rows < 0 || scores == nullptr) return GLSDM_ERR_ARGUMENT;
@@ -330,6 +396,7 @@ extern "C" int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, in
                                    const float* weights, const int64_t* requests, int64_t rows,
                                    int64_t rows_per_bank, int32_t width, float* out_read,
                                    uint32_t* device_status, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (int s = check_bank(bank)) return s;
   if (index == nullptr || weights == nullptr || out_read == nullptr || rows < 0) return GLSDM_ERR_ARGUMENT;
   if (width < 1 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
@@ -354,6 +421,7 @@ extern "C" int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, in
 extern "C" int glsdm_shard_read(const glsdm_bank* bank, const int32_t* index, const float* weights,
                                 int64_t rows, int64_t block_rows, int64_t block_stride, int32_t width,
                                 float* out_partial, uint32_t* device_status, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (int s = check_bank(bank)) return s;
   if (index == nullptr || weights == nullptr || out_partial == nullptr || rows < 0) return GLSDM_ERR_ARGUMENT;
   if (width < 1 || block_rows < 1 || block_stride < 0) return GLSDM_ERR_ARGUMENT;
@@ -380,6 +448,7 @@ extern "C" int glsdm_pk_select_read(const glsdm_bank* bank, const float* scores,
                                     float* out_read, void* out_index, int index_i64,
                                     float* out_weights, uint32_t* device_status,
                                     glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   (void)device_status;
   if (int s = check_bank(bank)) return s;
   int kf, kout;
@@ -426,6 +495,7 @@ extern "C" int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, con
                                 int64_t chunk_size, int32_t num_layers, int32_t layer_index,
                                 int64_t* out_addresses, float* out_deltas, int64_t* out_keys,
                                 uint32_t* device_status, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   (void)device_status;
   if (int s = check_bank(bank)) return s;
   int kf, kout;
@@ -489,6 +559,7 @@ extern "C" int glsdm_token_propose(const glsdm_bank* bank, const int64_t* reques
                                    int64_t rows, int32_t width, int64_t* out_addresses,
                                    float* out_deltas, uint32_t* device_status,
                                    glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (int s = check_bank(bank)) return s;
   if (requests == nullptr || index == nullptr || weights == nullptr || target == nullptr ||
       beta == nullptr || log_decay == nullptr || mass == nullptr || out_addresses == nullptr ||
@@ -514,6 +585,7 @@ extern "C" int glsdm_token_propose(const glsdm_bank* bank, const int64_t* reques
 extern "C" int glsdm_pk_combine(const float* left_score, const int32_t* left_index, const float* right_score,
                                 const int32_t* right_index, int64_t rows, int32_t half, int32_t width,
                                 void* out_index, int index_i64, float* out_weights, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   int kf, kout;
   if (int s = route_shape(half, width, &kf, &kout)) return s;
   if (left_score == nullptr || left_index == nullptr || right_score == nullptr || right_index == nullptr ||
@@ -523,6 +595,36 @@ extern "C" int glsdm_pk_combine(const float* left_score, const int32_t* left_ind
   pk_combine_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
       left_score, left_index, right_score, right_index, rows, half, kf, kout, out_index, index_i64, out_weights);
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_combine launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
+                                   const void* index, int index_i64,
+                                   const float* weights, int64_t rows, int64_t rows_per_bank, int32_t width,
+                                   int32_t half, float* grad_scores, float* grad_rows, int64_t* out_addresses,
+                                   glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
+  if (int s = check_bank(bank)) return s;
+  if (grad_out == nullptr || index == nullptr || weights == nullptr || grad_scores == nullptr ||
+      grad_rows == nullptr || out_addresses == nullptr)
+    return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || rows_per_bank < 1 || width < 1 || half < 1) return GLSDM_ERR_ARGUMENT;
+  if (width > 32) return GLSDM_ERR_UNSUPPORTED;
+  if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
+  if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
+  if (rows == 0) return GLSDM_OK;
+  const BankView v = make_view(*bank);
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+  if (bank->dtype == GLSDM_F32)
+    read_backward_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, grad_out, grad_weights, index, index_i64, weights, rows, rows_per_bank, width, half, grad_scores, grad_rows,
+        out_addresses);
+  else
+    read_backward_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        v, grad_out, grad_weights, index, index_i64, weights, rows, rows_per_bank, width, half, grad_scores, grad_rows,
+        out_addresses);
+  GLSDM_CUDA_OK(cudaGetLastError(), "read_backward launch");
   count_launches(1);
   return GLSDM_OK;
 }

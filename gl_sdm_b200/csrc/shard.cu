@@ -149,6 +149,7 @@ using namespace glsdm;
 extern "C" int glsdm_write_error(const float* prediction, const void* target, int target_dtype,
                                  const float* beta, const float* log_decay, int64_t rows, int32_t dim,
                                  float* out_error, float* out_decay_m1, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (prediction == nullptr || target == nullptr || beta == nullptr || log_decay == nullptr ||
       out_error == nullptr || out_decay_m1 == nullptr)
     return GLSDM_ERR_ARGUMENT;
@@ -193,6 +194,7 @@ extern "C" int glsdm_shard_propose(const glsdm_bank* bank, const int32_t* index,
                                    int32_t width, int64_t chunk_offset, int64_t chunk_size, int32_t num_layers,
                                    int32_t layer_index, int64_t* out_addresses, float* out_deltas,
                                    int64_t* out_keys, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (int s = check_bank(bank)) return s;
   if (index == nullptr || weights == nullptr || error == nullptr || decay_m1 == nullptr ||
       offsets == nullptr || out_addresses == nullptr || out_deltas == nullptr || out_keys == nullptr)

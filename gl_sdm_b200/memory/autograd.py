@@ -1,0 +1,87 @@
+"""Differentiable wrappers of the CUDA operator (forward AND backward on the kernels).
+
+The reference differentiates its torch path with autograd and its native path with custom
+backward kernels that fill a dense, zero-initialised bank gradient per read
+(gl_sdm/memory/backends/token.py:134-168, OPTIMIZATION_PLAN.md:45-54). Here the bank gradient
+of a read or a row gather stays compact - one (flat address, row) pair per route - and is
+folded into the dense tensor autograd expects by the same deterministic sort + segmented sum
+the commit uses, so gradients are reproducible bit for bit.
+"""
+import torch
+
+from .. import _native
+
+
+def _dense_bank_gradient(shape, device, addresses, rows):
+    """Scatter-add compact row gradients into a zero fp32 bank of the given shape."""
+    zero = torch.zeros(shape, dtype=torch.float32, device=device)
+    if addresses.numel() == 0:
+        return zero
+    flat = zero.view(-1, shape[-1])
+    _native.commit_rows(flat, addresses.reshape(-1), rows.reshape(-1, shape[-1]).contiguous(), None, out=flat)
+    return zero
+
+
+class RoutedRead(torch.autograd.Function):
+    """(readings, index, weights) = routed read of factor scores [B, T, H, 2*half]."""
+
+    @staticmethod
+    def forward(ctx, memory, scores, width):
+        B, T, H, L = scores.shape
+        scores = scores.detach().float().contiguous()
+        readings, index, weights = _native.pk_select_read(memory.detach(), scores, width, rows_per_bank=T * H)
+        ctx.save_for_backward(memory.detach(), index, weights)
+        ctx.geometry = (T * H, L // 2)
+        ctx.mark_non_differentiable(index)
+        return readings, index, weights
+
+    @staticmethod
+    def backward(ctx, grad_readings, _grad_index, grad_weights):
+        memory, index, weights = ctx.saved_tensors
+        rows_per_bank, half = ctx.geometry
+        if grad_readings is None:
+            grad_readings = torch.zeros((*index.shape[:-1], memory.shape[-1]), device=memory.device)
+        grad_weights = None if grad_weights is None else grad_weights.float().contiguous()
+        grad_scores, addresses, rows = _native.read_backward(memory, grad_readings.float().contiguous(), grad_weights,
+                                                             index, weights, rows_per_bank, half)
+        grad_memory = (_dense_bank_gradient(memory.shape, memory.device, addresses, rows).to(memory.dtype)
+                       if ctx.needs_input_grad[0] else None)
+        return grad_memory, grad_scores if ctx.needs_input_grad[1] else None, None
+
+
+class GatherRows(torch.autograd.Function):
+    """rows = flat[addresses]; the backward folds the row gradients back deterministically."""
+
+    @staticmethod
+    def forward(ctx, memory, addresses):
+        ctx.save_for_backward(addresses)
+        ctx.bank = (memory.shape, memory.device, memory.dtype)
+        return _native.gather_rows(memory.detach().flatten(0, 2), addresses)
+
+    @staticmethod
+    def backward(ctx, grad_rows):
+        (addresses,) = ctx.saved_tensors
+        shape, device, dtype = ctx.bank
+        return _dense_bank_gradient(shape, device, addresses, grad_rows.float()).to(dtype), None
+
+
+class Commit(torch.autograd.Function):
+    """new bank = commit(bank, addresses, deltas, keys) (reference backends/commit.py:36-54)."""
+
+    @staticmethod
+    def forward(ctx, values, addresses, deltas, keys, key_bits):
+        ctx.save_for_backward(addresses)
+        return _native.commit_rows(values.detach(), addresses, deltas.detach(), keys, key_bits=key_bits)
+
+    @staticmethod
+    def backward(ctx, incoming):
+        (addresses,) = ctx.saved_tensors
+        incoming = incoming.contiguous()
+        grad_deltas = None
+        if ctx.needs_input_grad[2]:
+            grad_deltas = _native.gather_rows(incoming.float().view(-1, incoming.shape[-1]), addresses)
+        return incoming if ctx.needs_input_grad[0] else None, None, grad_deltas, None, None
+
+
+def needs_grad(*tensors):
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)

@@ -7,13 +7,7 @@ scores prefer the larger address; indices come back ascending with softmax weigh
 import torch
 
 from .. import _native
-from . import oracle_hook
-
-
-def _forward_only(*tensors):
-    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
-        raise NotImplementedError(
-            "the B200 memory operator is forward-only: run under torch.no_grad() / inference_mode()")
+from . import autograd, oracle_hook
 
 
 def torch_routed_read(memory, scores, width, reference=False):
@@ -27,10 +21,11 @@ def torch_routed_read(memory, scores, width, reference=False):
     _native.require_cuda(memory)
     if not scores.is_cuda:
         raise ValueError("GL-SDM native kernels require contiguous CUDA tensors")
-    _forward_only(memory, scores)
     B, T, H, _ = scores.shape
     if memory.shape[0] not in (1, B) or memory.shape[1] != H:
         raise ValueError("scores and memory disagree on batch or heads")
+    if autograd.needs_grad(memory, scores):
+        return autograd.RoutedRead.apply(memory, scores, width)
     return _native.pk_select_read(memory, scores.float().contiguous(), width, rows_per_bank=T * H)
 
 
@@ -46,7 +41,10 @@ def gather_rows(memory, index, reference=False):
     if reference:
         return oracle_hook.get("gather_rows")(memory, index)
     _native.require_cuda(memory)
-    return _native.gather_rows(memory.flatten(0, 2), absolute_addresses(memory, index).contiguous())
+    addresses = absolute_addresses(memory, index).contiguous()
+    if autograd.needs_grad(memory):
+        return autograd.GatherRows.apply(memory, addresses)
+    return _native.gather_rows(memory.flatten(0, 2), addresses)
 
 
 def routed_read(block, memory, scores, width, physical=None):

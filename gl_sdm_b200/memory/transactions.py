@@ -9,7 +9,7 @@ harness provides (see oracle_hook).
 import torch
 
 from .. import _native
-from . import oracle_hook
+from . import autograd, oracle_hook
 from .state import MemoryView, WriteProposal, WriteBuffer
 
 _BACKENDS = {"torch", "urm"}
@@ -99,9 +99,13 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
         return oracle_hook.get("commit")(view, buffer)
     values = view.values
     _native.require_cuda(values)
-    _forward_only(values, *(p.deltas for p in buffer.proposals))
     idx = _concat([p.addresses.reshape(-1) for p in buffer.proposals]).long().contiguous()
     delta = _concat([p.deltas for p in buffer.proposals]).float().contiguous()
     keys = _concat([p.sort_keys.reshape(-1) for p in buffer.proposals]).long().contiguous() if all(keyed) else None
-    updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
+    if autograd.needs_grad(values, delta):
+        if donate:
+            raise ValueError("a donated (in-place) commit cannot be differentiated")
+        updated = autograd.Commit.apply(values, idx, delta, keys, key_bits)
+    else:
+        updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
     return MemoryView(updated, view.version + 1, view.lineage)

@@ -14,6 +14,8 @@
  *   - Nothing here allocates device memory unless stated; scratch is passed in as
  *     `workspace`, sized by the matching *_workspace_bytes() query.
  *   - Kernels are launched on `stream`; calls return after launch (asynchronous).
+ *   - A call with rows == 0 returns GLSDM_OK without a launch; its array pointers may be null
+ *     (an empty array has no storage).
  *   - The return value is a glsdm_status. Data-dependent failures (an address outside the
  *     bank) are reported through a caller-owned device word `device_status`, which the
  *     kernels OR error bits into; the caller zeroes it and reads it back when it wants.
@@ -124,6 +126,21 @@ int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, const void* ta
                      int32_t num_layers, int32_t layer_index, int64_t* out_addresses,
                      float* out_deltas, int64_t* out_keys, uint32_t* device_status,
                      glsdm_stream_t stream);
+
+/* Backward of the routed read with compact bank gradients: reference autograd through
+ * gl_sdm/memory/routing.py:19-28; native counterparts gl_sdm/memory/backends/token.py:69-82
+ * (_route_backward) and :134-144 (_read_backward), which write a dense zero-filled bank
+ * gradient per read. Here the bank gradient stays compact: one row per route.
+ *   grad_out [rows, dim] fp32; grad_weights [rows, width] fp32 or NULL (gradient arriving at
+ *   the returned softmax weights); index/weights [rows, width] as the forward returned them
+ *   grad_scores [rows, 2*half] fp32, written whole (softmax backward scattered to the factors)
+ *   grad_rows [rows*width, dim] fp32 = w_k * grad_out, out_addresses [rows*width] int64 flat
+ *   bank rows: feed them to glsdm_commit on a zero (or accumulating) gradient bank. */
+int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
+                        const void* index, int index_i64,
+                        const float* weights, int64_t rows, int64_t rows_per_bank, int32_t width,
+                        int32_t half, float* grad_scores, float* grad_rows, int64_t* out_addresses,
+                        glsdm_stream_t stream);
 
 /* Row gather out[n, :] = flat[addresses[n], :] in the bank's dtype, reference
  * gl_sdm/memory/routing.py:37-42 (gather_rows), gl_sdm/memory/transactions.py:19-25

@@ -132,3 +132,33 @@ def token_case():
         log_decay=torch.full((2, 2, 1), -0.12),
         mass=torch.tensor([0.0, 0.7]),
     )
+
+
+GRAD_CASES = ("grad_tiny", "grad_c1")
+
+
+def grad_case(name):
+    """Inputs of the routed-read gradient cases (projects/gl-sdm/tests/test_chunk_memory.py:86-121
+    check the same gradients on the reference's native path)."""
+    if name == "grad_tiny":
+        torch.manual_seed(42)
+        return torch.randn(2, 2, 16, 8), torch.randn(2, 17, 2, 8), 2
+    if name == "grad_c1":
+        torch.manual_seed(4242)
+        return torch.randn(2, 4, 4096, 64) * 0.02, torch.randn(2, 16, 4, 128).bfloat16().float(), 8
+    raise KeyError(name)
+
+
+def cotangents(name, readings_shape, weights_shape):
+    g = torch.Generator().manual_seed(len(name) + 100)
+    return torch.randn(readings_shape, generator=g), torch.randn(weights_shape, generator=g)
+
+
+def chain_case():
+    """A tiny write chain (read -> gather -> delta -> commit) with colliding addresses."""
+    g = torch.Generator().manual_seed(99)
+    B, T, H, half, D, K = 1, 6, 2, 4, 8, 2
+    return dict(memory=torch.randn(B, H, half * half, D, generator=g), scores=torch.randn(B, T, H, 2 * half, generator=g),
+                target=torch.randn(B, T, H, D, generator=g), beta=torch.rand(B, T, H, generator=g),
+                log_decay=-torch.rand(B, T, H, generator=g) * 0.3, width=K,
+                cotangent=torch.randn(B, H, half * half, D, generator=g))

@@ -86,6 +86,38 @@ def main(reference_root):
         rec[f"{name}_dense"] = dense.values.numpy()
     np.savez_compressed(os.path.join(HERE, "commit_cases.npz"), **rec)
 
+    # -- gradients (reference autograd on the torch path) ----------------------------------------
+    rec = {}
+    for name in gi.GRAD_CASES:
+        memory, scores, width = gi.grad_case(name)
+        memory.requires_grad_(), scores.requires_grad_()
+        readings, index, weights = torch_routed_read(memory, scores, width)
+        cot_r, cot_w = gi.cotangents(name, readings.shape, weights.shape)
+        g_memory, g_scores = torch.autograd.grad((readings * cot_r).sum() + (weights * cot_w).sum(), (memory, scores))
+        touched = torch.unique(absolute_addresses(memory, index))
+        assert g_memory.flatten(0, 2).abs().sum(-1).nonzero().numel() <= touched.numel()
+        rec[f"{name}_grad_scores"] = g_scores.numpy()
+        rec[f"{name}_touched"] = touched.numpy()
+        rec[f"{name}_grad_rows"] = g_memory.flatten(0, 2)[touched].numpy()
+    # the whole write chain: routed read -> gather -> delta -> commit, gradient of the new bank
+    chain = gi.chain_case()
+    memory, scores, target = (chain[k].clone().requires_grad_() for k in ("memory", "scores", "target"))
+    B, T, H, _ = scores.shape
+    prediction, index, weights = torch_routed_read(memory, scores, chain["width"])
+    rows = gather_rows(memory, index)
+    addresses = absolute_addresses(memory, index)
+    delta = proposal_delta(rows, weights, prediction, target, chain["beta"].unsqueeze(-1),
+                           chain["log_decay"].unsqueeze(-1), torch.ones(B, T))
+    positions = torch.arange(T).view(1, T, 1, 1)
+    keys = addresses * (T * 2) + positions * 2 + 1
+    view = MemoryView(memory)
+    after = commit(view, merge(view, [WriteProposal(0, addresses.flatten(), delta.flatten(0, 3), view.lineage, keys.flatten())]))
+    grads = torch.autograd.grad((after.values * chain["cotangent"]).sum(), (memory, scores, target))
+    rec["chain_after"] = after.values.detach().numpy()
+    for k, g in zip(("memory", "scores", "target"), grads):
+        rec[f"chain_grad_{k}"] = g.numpy()
+    np.savez_compressed(os.path.join(HERE, "gradients.npz"), **rec)
+
     # -- token-clock API ------------------------------------------------------------------------
     t = gi.token_case()
     view = MemoryView(t["memory"])

@@ -1,0 +1,61 @@
+"""Backward of the operator on the CUDA kernels against the reference's autograd
+(tests/golden/gradients.npz, generated from the reference's torch path; the reference checks
+the same gradients on its native path in projects/gl-sdm/tests/test_chunk_memory.py:86-121).
+Tolerances are the reference's: atol 1e-5, rtol 1e-5 (looser only where sums are long)."""
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+from conftest import load_golden
+from oracle import torch_port as port
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("name", gi.GRAD_CASES)
+def test_routed_read_gradients_match_reference_autograd(native, name):
+    from gl_sdm_b200.memory import routing
+    gold = load_golden("gradients")
+    memory, scores, width = gi.grad_case(name)
+    memory, scores = memory.to(DEV).requires_grad_(), scores.to(DEV).requires_grad_()
+    readings, index, weights = routing.torch_routed_read(memory, scores, width)
+    assert readings.requires_grad and weights.requires_grad and not index.requires_grad
+    cot_r, cot_w = gi.cotangents(name, readings.shape, weights.shape)
+    loss = (readings * cot_r.to(DEV)).sum() + (weights * cot_w.to(DEV)).sum()
+    g_memory, g_scores = torch.autograd.grad(loss, (memory, scores), retain_graph=True)
+    np.testing.assert_allclose(g_scores.cpu().numpy(), gold[f"{name}_grad_scores"], rtol=1e-4, atol=1e-5)
+    flat = g_memory.flatten(0, 2).cpu().numpy()
+    np.testing.assert_allclose(flat[gold[f"{name}_touched"]], gold[f"{name}_grad_rows"], rtol=1e-4, atol=1e-5)
+    untouched = np.ones(flat.shape[0], bool)
+    untouched[gold[f"{name}_touched"]] = False
+    assert not flat[untouched].any()
+    # deterministic: the same backward again is bit-identical
+    again = torch.autograd.grad(loss, (memory, scores))
+    assert torch.equal(again[0], g_memory) and torch.equal(again[1], g_scores)
+
+
+def test_write_chain_gradients_match_reference_autograd(native):
+    """routed read -> gather_rows -> delta (dense.py:11-14, torch ops) -> commit; gradient of
+    the committed bank w.r.t. the old bank, the write scores and the targets."""
+    from gl_sdm_b200.memory import MemoryView, WriteProposal, commit, merge, routing
+    gold = load_golden("gradients")
+    chain = gi.chain_case()
+    memory, scores, target = (chain[k].to(DEV).requires_grad_() for k in ("memory", "scores", "target"))
+    B, T, H, _ = scores.shape
+    prediction, index, weights = routing.torch_routed_read(memory, scores, chain["width"])
+    rows = routing.gather_rows(memory, index)
+    addresses = routing.absolute_addresses(memory, index)
+    delta = port.delta_rows(rows, weights, prediction, target, chain["beta"].to(DEV).unsqueeze(-1),
+                            chain["log_decay"].to(DEV).unsqueeze(-1), torch.ones(B, T, device=DEV))
+    keys = addresses * (T * 2) + torch.arange(T, device=DEV).view(1, T, 1, 1) * 2 + 1
+    view = MemoryView(memory)
+    after = commit(view, merge(view, [WriteProposal(0, addresses.flatten(), delta.flatten(0, 3), view.lineage, keys.flatten())]))
+    np.testing.assert_allclose(after.values.detach().cpu().numpy(), gold["chain_after"], rtol=1e-5, atol=1e-6)
+    grads = torch.autograd.grad((after.values * chain["cotangent"].to(DEV)).sum(), (memory, scores, target))
+    for name, g in zip(("memory", "scores", "target"), grads):
+        np.testing.assert_allclose(g.cpu().numpy(), gold[f"chain_grad_{name}"], rtol=1e-4, atol=1e-5, err_msg=name)
+    with pytest.raises(ValueError, match="donated"):
+        commit(view, merge(view, [WriteProposal(0, addresses.flatten(), delta.flatten(0, 3), view.lineage, keys.flatten())]),
+               donate=True)

@@ -133,3 +133,19 @@ def test_oracle_replays_the_recorded_stack_calls(dtype):
         cat = lambda name: np.concatenate([t[f"commit{i}_{name}{j}"] for j in range(n)])  # noqa: E731
         out = oracle.commit(t[f"bank{int(t[f'commit{i}_bank'])}"], cat("addresses"), cat("deltas"), cat("keys"))
         np.testing.assert_array_equal(out, t[f"bank{int(t[f'commit{i}_result'])}"])
+
+
+@pytest.mark.parametrize("name", gi.GRAD_CASES)
+def test_oracle_backward_matches_reference_autograd(name):
+    gold = load_golden("gradients")
+    memory, scores, width = gi.grad_case(name)
+    readings, index, weights = oracle.routed_read(memory.numpy(), scores.numpy(), width)
+    cot_r, cot_w = gi.cotangents(name, readings.shape, weights.shape)
+    grad_routes, grad_memory = oracle.routed_read_backward(memory.numpy(), index, weights, cot_r.numpy(), cot_w.numpy())
+    grad_scores = oracle.scatter_route_gradients(grad_routes, index, scores.shape[-1] // 2)
+    np.testing.assert_allclose(grad_scores, gold[f"{name}_grad_scores"], rtol=1e-4, atol=1e-6)
+    flat = grad_memory.reshape(-1, memory.shape[-1])
+    np.testing.assert_allclose(flat[gold[f"{name}_touched"]], gold[f"{name}_grad_rows"], rtol=1e-4, atol=1e-6)
+    untouched = np.ones(flat.shape[0], bool)
+    untouched[gold[f"{name}_touched"]] = False
+    assert not flat[untouched].any()
