@@ -172,6 +172,43 @@ def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
     return n / statistics.median(times), n, statistics.median(times)
 
 
+def run_torch_on_gpu(w, dev, sequences=16):
+    """The reference's tensor-op sequence (the port) on CUDA tensors of the same device: a
+    second comparison beside the CPU baseline. Product-key scores in, `sequences` x chunk
+    tokens of one epoch, functional commit as the reference does it (whole-bank copy) and the
+    in-place variant. Returns a dict of per-stage milliseconds and tokens/s."""
+    from gl_sdm_b200 import workloads
+    from oracle import torch_port as port
+    bank = workloads.make_bank(w, dev, banks=1)
+    x = workloads.make_epoch_inputs(w, dev, 9000, sequences, w.chunk)
+    marks = {}
+
+    def timed(name, fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        marks[name] = a.elapsed_time(b)
+        return out
+
+    for attempt in range(2):   # the first round is the warm-up
+        timed("read_ms", lambda: port.routed_read(bank, x["q_scores"], w.width))
+        a, d, k = timed("proposal_ms", lambda: port.propose(bank, x["k_scores"], w.width, x["target"].float(), x["beta"],
+                                                             x["log_decay"], None, 0, 0, w.chunk, 1))
+        out = timed("commit_copy_ms", lambda: port.commit(bank, a, d, k, in_place=False))
+        del out
+        timed("commit_in_place_ms", lambda: port.commit(bank, a, d, k, in_place=True))
+        del a, d, k
+    n = sequences * w.chunk
+    total = marks["read_ms"] + marks["proposal_ms"] + marks["commit_in_place_ms"]
+    marks = {k: round(v, 3) for k, v in marks.items()}
+    marks.update({"value": n / (total / 1e3), "unit": "tokens/s",
+                  "sample": f"{n} tokens of one commit epoch, product-key scores in, in-place commit counted; "
+                            "PyTorch CUDA tensor ops of the reference path (port) on the same GPU"})
+    return marks
+
+
 def cpu_sample_text(w, routing, n, sec):
     what = "flat-key scores + routes" if routing == "dense" else "product-key routes"
     return (f"{n} tokens of one commit epoch ({what}, read, proposal, in-place commit) on the full "
@@ -456,6 +493,9 @@ def ours(args, w, rank, world, local, dist):
                  "roofline": pk_roofline(w, pk, world, peaks, peak_kind)}
         del pk
         torch.cuda.empty_cache()
+        if not args.no_cpu_baseline:
+            extra["torch_on_gpu"] = run_torch_on_gpu(w, dev)
+            torch.cuda.empty_cache()
 
     if rank != 0:
         return

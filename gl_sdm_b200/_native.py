@@ -54,6 +54,9 @@ SIGNATURES = {
                                  _i32, _i32, _p, _p, _p, _p]),
     "glsdm_commit_workspace_bytes": (_sz, [_i64, _i32]),
     "glsdm_commit": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p]),
+    "glsdm_commit_undo": (_i, [_p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p, _p, _p]),
+    "glsdm_undo_apply": (_i, [_p, _i, _i64, _i64, _i32, _p, _p, _i64, _p]),
+    "glsdm_overlay_read": (_i, [_BANK, _p, _i, _p, _i64, _i64, _i32, _i32, _p, _p, _p, _p, _p, _p]),
     "glsdm_commit_static": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _p]),
     "glsdm_commit_static_max_entries": (_i64, []),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
@@ -409,6 +412,73 @@ def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_
     _check(lib.glsdm_commit(_ptr(flat), _ptr(out), _dtype_code(values), row_base, flat.shape[0], dim,
                             _ptr(addresses), _ptr(deltas), _ptr(keys), entries, key_bits, _ptr(work),
                             work.numel(), _ptr(status_word(values.device)), _stream(values.device)))
+    return out
+
+
+MAX_UNDO_LOGS = 8
+
+
+def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
+    """In-place commit that also records the touched rows' previous contents.
+
+    Returns (undo_addresses [entries] int64 sorted, undo_rows [entries, dim] in the bank dtype;
+    the first position of each run of equal addresses holds that address's old row)."""
+    require_cuda(values, addresses, deltas, keys)
+    dim = values.shape[-1]
+    flat = values.view(-1, dim)
+    if addresses.dtype != torch.int64 or (keys is not None and keys.dtype != torch.int64):
+        raise ValueError("addresses and sort keys must be int64")
+    if deltas.dtype != torch.float32:
+        raise ValueError("deltas must be float32")
+    entries = addresses.numel()
+    if deltas.numel() != entries * dim or (keys is not None and keys.numel() != entries):
+        raise ValueError("addresses, deltas and keys disagree on the number of entries")
+    undo_addresses = torch.empty(entries, dtype=torch.int64, device=values.device)
+    undo_rows = torch.empty((entries, dim), dtype=values.dtype, device=values.device)
+    lib = library()
+    work = _workspace(values.device, lib.glsdm_commit_workspace_bytes(entries, dim))
+    _check(lib.glsdm_commit_undo(_ptr(flat), _dtype_code(values), 0, flat.shape[0], dim, _ptr(addresses),
+                                 _ptr(deltas), _ptr(keys), entries, key_bits, _ptr(work), work.numel(),
+                                 _ptr(undo_addresses), _ptr(undo_rows), _ptr(status_word(values.device)),
+                                 _stream(values.device)))
+    return undo_addresses, undo_rows
+
+
+def undo_apply(values, undo_addresses, undo_rows):
+    """Write the logged old rows back into ``values`` (in place)."""
+    require_cuda(values, undo_addresses, undo_rows)
+    dim = values.shape[-1]
+    flat = values.view(-1, dim)
+    if undo_rows.dtype != values.dtype or undo_rows.shape[-1] != dim:
+        raise ValueError("the undo log does not match the bank")
+    _check(library().glsdm_undo_apply(_ptr(flat), _dtype_code(values), 0, flat.shape[0], dim, _ptr(undo_addresses),
+                                      _ptr(undo_rows), undo_addresses.numel(), _stream(values.device)))
+    return values
+
+
+def overlay_read(values, index, weights, rows_per_bank, logs):
+    """snapshot_read of an older version: ``logs`` = [(undo_addresses, undo_rows), ...] of the
+    commits applied to ``values`` since that version, oldest commit first."""
+    require_cuda(values, index, weights)
+    if index.dtype not in (torch.int64, torch.int32) or weights.dtype != torch.float32:
+        raise ValueError("routes are int32/int64 indices with float32 weights")
+    if len(logs) > MAX_UNDO_LOGS:
+        raise ValueError(f"at most {MAX_UNDO_LOGS} undo logs per read")
+    for a, r in logs:
+        require_cuda(a, r)
+        if a.dtype != torch.int64 or r.dtype != values.dtype or r.shape[-1] != values.shape[-1]:
+            raise ValueError("the undo log does not match the bank")
+    bank = bank_of(values)
+    width = index.shape[-1]
+    rows = index.numel() // width
+    n = len(logs)
+    addresses = (ctypes.c_void_p * max(n, 1))(*[a.data_ptr() for a, _ in logs])
+    log_rows = (ctypes.c_void_p * max(n, 1))(*[r.data_ptr() for _, r in logs])
+    entries = (ctypes.c_int64 * max(n, 1))(*[a.numel() for a, _ in logs])
+    out = torch.empty((*index.shape[:-1], values.shape[-1]), dtype=torch.float32, device=values.device)
+    _check(library().glsdm_overlay_read(ctypes.byref(bank), _ptr(index), int(index.dtype == torch.int64),
+                                        _ptr(weights), rows, rows_per_bank, width, n, addresses, log_rows, entries,
+                                        _ptr(out), _ptr(status_word(values.device)), _stream(values.device)))
     return out
 
 

@@ -4,7 +4,7 @@ Same fields, defaults and error text as the reference (gl_sdm/memory/state.py:7-
 extension: a view may hold bfloat16 values (the reference plans bf16 storage with fp32
 accumulation, OPTIMIZATION_PLAN.md:99-105); the learned parameter itself stays float32.
 """
-from dataclasses import dataclass, field
+from dataclasses import FrozenInstanceError, dataclass, field
 
 import torch
 from torch import nn
@@ -12,18 +12,75 @@ from torch import nn
 _VIEW_DTYPES = (torch.float32, torch.bfloat16)
 
 
-@dataclass(frozen=True)
-class MemoryView:
-    """An immutable bank version: values [requests, heads, slots, dim]."""
-    values: torch.Tensor
-    version: int = 0
-    lineage: object = field(default_factory=object)
+class UndoLog:
+    """Rows one copy-free commit overwrote: ``addresses`` [entries] int64 sorted (runs of equal
+    addresses), ``rows`` [entries, dim] with the old row at the first position of every run.
+    ``next`` is the log of the following copy-free commit on the same storage, ``broken`` is
+    set when the storage was later changed without a log (a donated commit)."""
+    __slots__ = ("addresses", "rows", "next", "broken")
 
-    def __post_init__(self):
-        v = self.values
-        bad_shape = v.ndim != 4 or min(v.shape) < 1
-        if bad_shape or v.dtype not in _VIEW_DTYPES or self.version < 0:
+    def __init__(self, addresses, rows):
+        self.addresses, self.rows, self.next, self.broken = addresses, rows, None, False
+
+    def chain(self):
+        """This log and every later one, oldest commit first."""
+        out, log = [], self
+        while log is not None:
+            if log.broken:
+                raise RuntimeError("this snapshot was invalidated by an in-place (donated) commit of a later version")
+            out.append(log)
+            log = log.next
+        return out
+
+
+class MemoryView:
+    """An immutable bank version: values [requests, heads, slots, dim].
+
+    Same fields, defaults and validation as the reference's frozen dataclass
+    (gl_sdm/memory/state.py:7-15). One addition: after a copy-free commit
+    (``commit(..., donate="overlay")``) the storage behind this view holds the NEWER version
+    and the view keeps the undo log that leads back to its own; ``values`` then rebuilds this
+    version on first use (one bank copy plus the touched rows), while
+    ``gl_sdm_b200.memory.overlay.read`` reads it without any copy.
+    """
+    __slots__ = ("_storage", "version", "lineage", "_undo", "_made_by")
+
+    def __init__(self, values, version=0, lineage=None):
+        bad_shape = values.ndim != 4 or min(values.shape) < 1
+        if bad_shape or values.dtype not in _VIEW_DTYPES or version < 0:
             raise ValueError("memory views require nonempty [batch, heads, slots, dim] FP32 values and a nonnegative version")
+        set_ = object.__setattr__
+        set_(self, "_storage", values)
+        set_(self, "version", version)
+        set_(self, "lineage", object() if lineage is None else lineage)
+        set_(self, "_undo", None)      # first log between this version and the storage's content
+        set_(self, "_made_by", None)   # the log of the copy-free commit that produced this view
+
+    def __setattr__(self, name, value):
+        raise FrozenInstanceError(f"cannot assign to field {name!r}")
+
+    def __delattr__(self, name):
+        raise FrozenInstanceError(f"cannot delete field {name!r}")
+
+    def __repr__(self):
+        return f"MemoryView(values={tuple(self._storage.shape)}, version={self.version}, stale={self._undo is not None})"
+
+    @property
+    def stale(self):
+        """True when the storage has moved on and this version lives in undo logs."""
+        return self._undo is not None
+
+    @property
+    def values(self):
+        if self._undo is None:
+            return self._storage
+        from .. import _native
+        rebuilt = self._storage.clone()
+        for log in reversed(self._undo.chain()):   # newest commit first, so the oldest row wins
+            _native.undo_apply(rebuilt, log.addresses, log.rows)
+        object.__setattr__(self, "_storage", rebuilt)
+        object.__setattr__(self, "_undo", None)
+        return rebuilt
 
 
 @dataclass(frozen=True)

@@ -84,10 +84,16 @@ def _concat(tensors):
 def commit(view, buffer, reference=False, backend="torch", donate=False, key_bits=0):
     """Apply a write buffer: stable sort by key, per-address fp32 sums, one write per row.
 
-    Returns a new view (version + 1, same lineage); the input view's tensor is left
-    bit-for-bit unchanged unless ``donate=True``, which updates it in place and hands the
-    same storage to the new view (extension for banks too large to copy per commit; the
-    old view must not be read afterwards). ``key_bits`` optionally bounds the sort keys.
+    Returns a new view (version + 1, same lineage). ``donate`` chooses what happens to the
+    input view's storage (extensions for banks too large to copy per commit):
+      False      the bank is copied, the input view's tensor stays bit-for-bit unchanged
+                 (the reference's behaviour, gl_sdm/memory/transactions.py:96);
+      True       update in place and hand the same storage to the new view; the old view must
+                 not be read afterwards;
+      "overlay"  update in place AND keep the old view valid: the commit records the rows it
+                 overwrites (an undo log of the touched rows only) and the old view reads
+                 through it (see ``MemoryView`` and ``memory.overlay``).
+    ``key_bits`` optionally bounds the sort keys.
     """
     _check_backend(backend)
     if buffer.base_version != view.version or buffer.lineage is not view.lineage:
@@ -97,6 +103,10 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
         raise ValueError("cannot mix keyed and unkeyed proposals")
     if reference:
         return oracle_hook.get("commit")(view, buffer)
+    if donate not in (False, True, "overlay"):
+        raise ValueError('donate must be False, True or "overlay"')
+    if donate and view.stale:
+        raise ValueError("an in-place commit needs the newest view of its storage")
     values = view.values
     _native.require_cuda(values)
     idx = _concat([p.addresses.reshape(-1) for p in buffer.proposals]).long().contiguous()
@@ -106,6 +116,17 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
         if donate:
             raise ValueError("a donated (in-place) commit cannot be differentiated")
         updated = autograd.Commit.apply(values, idx, delta, keys, key_bits)
-    else:
-        updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
+        return MemoryView(updated, view.version + 1, view.lineage)
+    if donate == "overlay":
+        from .state import UndoLog
+        log = UndoLog(*_native.commit_undo(values, idx, delta, keys, key_bits=key_bits))
+        newer = MemoryView(values, view.version + 1, view.lineage)
+        object.__setattr__(newer, "_made_by", log)
+        if view._made_by is not None:
+            view._made_by.next = log       # older snapshots continue through this commit
+        object.__setattr__(view, "_undo", log)
+        return newer
+    if donate and view._made_by is not None:
+        view._made_by.broken = True        # older overlay snapshots can no longer be rebuilt
+    updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
     return MemoryView(updated, view.version + 1, view.lineage)

@@ -212,6 +212,40 @@ int glsdm_commit(const void* values_in, void* values_out, int dtype, int64_t row
                  const int64_t* keys, int64_t entries, int32_t key_bits, void* workspace,
                  size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
 
+/* Copy-free versioned commit ("overlay" commit). The reference keeps an old snapshot valid by
+ * cloning the whole bank at every commit (gl_sdm/memory/transactions.py:96 index_copy,
+ * gl_sdm/memory/state.py:61-62) and plans touched-row overlays instead
+ * (OPTIMIZATION_PLAN.md, "Represent commits as compact overlays"). Here the bank is updated
+ * in place and the commit writes an UNDO LOG: for every touched address, the row it held
+ * before. An older version is then the current bank with the logs of all later commits
+ * played back, oldest log winning.
+ *   glsdm_commit_undo   as glsdm_commit in place, plus
+ *     undo_addresses [entries] int64   the entries' addresses in sorted order (runs of equal
+ *                                      addresses); valid after the call
+ *     undo_rows      [entries, dim]    bank dtype; position p holds the old row of
+ *                                      undo_addresses[p] iff p is the first of its run
+ *   glsdm_undo_apply    writes every logged old row back into the bank (materialises the
+ *                       previous version in `values`, e.g. in a copy of the bank)
+ *   glsdm_overlay_read  snapshot_read of an OLD version: each route's row is taken from the
+ *                       first of the n_logs logs (given oldest commit first) that holds its
+ *                       address, else from the bank. log_* are HOST arrays of n_logs device
+ *                       pointers / sizes; n_logs <= GLSDM_MAX_UNDO_LOGS. Unsharded banks only.
+ *                       With no logs it returns exactly what glsdm_snapshot_read returns. */
+#define GLSDM_MAX_UNDO_LOGS 8
+int glsdm_commit_undo(void* values, int dtype, int64_t row_base, int64_t bank_rows, int32_t dim,
+                      const int64_t* addresses, const float* deltas, const int64_t* keys,
+                      int64_t entries, int32_t key_bits, void* workspace, size_t workspace_bytes,
+                      int64_t* undo_addresses, void* undo_rows, uint32_t* device_status,
+                      glsdm_stream_t stream);
+int glsdm_undo_apply(void* values, int dtype, int64_t row_base, int64_t bank_rows, int32_t dim,
+                     const int64_t* undo_addresses, const void* undo_rows, int64_t entries,
+                     glsdm_stream_t stream);
+int glsdm_overlay_read(const glsdm_bank* bank, const void* index, int index_i64,
+                       const float* weights, int64_t rows, int64_t rows_per_bank, int32_t width,
+                       int32_t n_logs, const int64_t* const* log_addresses,
+                       const void* const* log_rows, const int64_t* log_entries, float* out_read,
+                       uint32_t* device_status, glsdm_stream_t stream);
+
 /* Commit for hosts that cannot provide a workspace. It has no counterpart in the reference
  * (whose commit allocates freely through PyTorch). Same arguments and result as glsdm_commit,
  * minus the workspace: the sort/reduce scratch is a 4 MiB array built into the library's

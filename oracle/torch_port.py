@@ -1,7 +1,9 @@
 """Multi-threaded CPU port (PyTorch tensor ops) of the GL-SDM memory operator.
 
 TEST INFRASTRUCTURE ONLY: the timed CPU baseline of bench.py (cpu_baseline and
-`--impl reference`) and a second checker in tests/. The reference's own CPU path for this
+`--impl reference`) and a second checker in tests/. The functions follow the device of
+their inputs, so bench.py can also time the same library-op sequence on CUDA tensors as a
+comparison (never as the product). The reference's own CPU path for this
 operator is PyTorch tensor code (projects/gl-sdm/src/gl_sdm/memory/routing.py:10-42,
 memory/transactions.py:69-97, runtime/dense.py:11-14), so its faithful CPU timing is the
 same sequence of library sorts, gathers and segmented sums run on all host threads. The
@@ -41,9 +43,9 @@ def flat_rows(memory, index):
     B, T, H, _ = index.shape
     S = memory.shape[2]
     if memory.shape[0] == 1 and B > 1:
-        part = torch.arange(H).view(1, 1, H, 1)
+        part = torch.arange(H, device=index.device).view(1, 1, H, 1)
     else:
-        part = torch.arange(B * H).view(B, 1, H, 1)
+        part = torch.arange(B * H, device=index.device).view(B, 1, H, 1)
     return part * S + index
 
 
@@ -67,9 +69,9 @@ def propose(memory, scores, width, target, beta, log_decay, mass, offset, layer_
     prediction, index, weights = routed_read(memory, scores, width)
     addresses = flat_rows(memory, index)
     rows = memory.flatten(0, 2)[addresses].float()
-    mass = torch.ones(B, T) if mass is None else mass
+    mass = torch.ones(B, T, device=scores.device) if mass is None else mass
     delta = delta_rows(rows, weights, prediction, target, beta.unsqueeze(-1), log_decay.unsqueeze(-1), mass)
-    position = torch.arange(offset, offset + T).view(1, T, 1, 1)
+    position = torch.arange(offset, offset + T, device=scores.device).view(1, T, 1, 1)
     keys = addresses * (chunk_size * num_layers) + position * num_layers + layer_index
     return addresses.flatten(), delta.flatten(0, 3), keys.flatten()
 
@@ -131,9 +133,10 @@ def dense_epoch(memory, keys, queries, write_queries, width, target, beta, log_d
     rows = flat[windex].float()
     prediction = (rows * wweights.unsqueeze(-1)).sum(-2)
     delta = delta_rows(rows.view(B, T, 1, width, -1), wweights.view(B, T, 1, width), prediction.view(B, T, 1, -1),
-                       target.view(B, T, 1, -1), beta.view(B, T, 1, 1), log_decay.view(B, T, 1, 1), torch.ones(B, T))
+                       target.view(B, T, 1, -1), beta.view(B, T, 1, 1), log_decay.view(B, T, 1, 1),
+                       torch.ones(B, T, device=queries.device))
     address = windex.view(B, T, 1, width)
-    position = torch.arange(T).view(1, T, 1, 1)
+    position = torch.arange(T, device=queries.device).view(1, T, 1, 1)
     key = address * chunk_size + position
     memory = commit(memory, address.flatten(), delta.flatten(0, 3), key.flatten(), in_place=in_place)
     return readings, memory

@@ -1,6 +1,7 @@
 """Host-side logic of the gl_sdm.memory mirror: value objects, validation, error text,
 no CPU fallback, and the module shim - the CPU-checkable parts of the reference's tests
 (projects/gl-sdm/tests/test_global_memory.py:27-54,57-66; test_native_memory.py:141-144)."""
+import dataclasses
 import sys
 
 import pytest
@@ -118,3 +119,60 @@ def test_install_shim_binds_reference_module_names():
     finally:
         install.uninstall(previous)
     assert sys.modules.get("gl_sdm.memory") is not memory
+
+
+def test_overlay_commit_bookkeeping(monkeypatch):
+    """Host side of the copy-free commit (kernels replaced by torch stand-ins): versions,
+    lineage, which views go stale, how logs chain, and when a snapshot is declared lost."""
+    from gl_sdm_b200 import _native
+    from gl_sdm_b200.memory import overlay
+
+    def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
+        flat = values.view(-1, values.shape[-1])
+        order = torch.sort(addresses if keys is None else keys, stable=True).indices
+        ordered = addresses[order]
+        old = flat[ordered].clone()
+        rows, counts = torch.unique_consecutive(ordered, return_counts=True)
+        flat[rows] = flat[rows] + torch.segment_reduce(deltas[order], "sum", lengths=counts)
+        return ordered, old
+
+    def undo_apply(values, addresses, rows):
+        flat = values.view(-1, values.shape[-1])
+        head = torch.ones_like(addresses, dtype=torch.bool)
+        head[1:] = addresses[1:] != addresses[:-1]
+        flat[addresses[head]] = rows[head]
+        return values
+
+    def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0):
+        out = values.clone() if out is None else out
+        commit_undo(out, addresses, deltas, keys)
+        return out
+
+    for name, fn in (("commit_undo", commit_undo), ("undo_apply", undo_apply), ("commit_rows", commit_rows),
+                     ("require_cuda", lambda *a: None)):
+        monkeypatch.setattr(_native, name, fn)
+
+    def proposal(view, seed):
+        g = torch.Generator().manual_seed(seed)
+        a = torch.randint(0, 16, (10,), generator=g)
+        return WriteProposal(view.version, a, torch.randn(10, 4, generator=g), view.lineage, a * 100 + torch.arange(10))
+
+    bank = torch.randn(1, 1, 16, 4)
+    v0 = MemoryView(bank.clone())
+    v1 = commit(v0, merge(v0, [proposal(v0, 1)]), donate="overlay")
+    assert (v1.version, v1.lineage is v0.lineage, v0.stale, v1.stale) == (1, True, True, False)
+    state1 = v1.values.clone()
+    v2 = commit(v1, merge(v1, [proposal(v1, 2)]), donate="overlay")
+    assert len(overlay.logs_of(v0)) == 2 and len(overlay.logs_of(v1)) == 1 and overlay.logs_of(v2) == []
+    with pytest.raises(ValueError, match="newest view"):
+        commit(v0, merge(v0, [proposal(v0, 3)]), donate=True)
+    assert torch.equal(v1.values, state1) and not v1.stale          # rebuilt into storage of its own
+    assert torch.equal(v0.values, bank)
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        v2.version = 9
+    # a donated commit of the newest view leaves no log: snapshots that still hang on it are lost
+    w0 = MemoryView(bank.clone())
+    w1 = commit(w0, merge(w0, [proposal(w0, 4)]), donate="overlay")
+    commit(w1, merge(w1, [proposal(w1, 5)]), donate=True)
+    with pytest.raises(RuntimeError, match="invalidated"):
+        w0.values
