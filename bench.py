@@ -238,7 +238,7 @@ def reference_arm(args, w, rank):
 class Runner:
     """Binds a workload to the operator for one routing mode: device inputs and one epoch call."""
 
-    def __init__(self, w, routing, dev, rank, world, dist):
+    def __init__(self, w, routing, dev, rank, world, dist, factored=True):
         from gl_sdm_b200 import workloads
         from gl_sdm_b200.operator import SharedBankOperator
         from gl_sdm_b200.sharded import ShardedBankOperator
@@ -247,14 +247,14 @@ class Runner:
         bank = workloads.make_bank(w, dev)
         if routing == "dense":
             keys = workloads.make_keys(w, dev)
-            self.op = ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk, keys=keys)
+            self.op = ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk, keys=keys, factored=factored)
             self.names = ("q", "kq", "target", "beta", "log_decay")
             self.epochs = [workloads.make_epoch_inputs_dense(w, dev, 1000 * (rank + 1) + e, seqs_local, keys=keys)
                            for e in range(w.epochs)]
             del keys
         else:
-            self.op = (ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk) if world > 1
-                       else SharedBankOperator(bank, w.width, w.width, chunk_size=w.chunk))
+            self.op = (ShardedBankOperator(bank, w.width, w.width, dist, chunk_size=w.chunk, factored=factored)
+                       if world > 1 else SharedBankOperator(bank, w.width, w.width, chunk_size=w.chunk, factored=factored))
             self.names = ("q_scores", "k_scores", "target", "beta", "log_decay")
             self.epochs = [workloads.make_epoch_inputs(w, dev, 1000 * (rank + 1) + e, seqs_local)
                            for e in range(w.epochs)]
@@ -309,16 +309,24 @@ def phase_times_pk(runner):
         ev[0].record()
         op.read(x["q_scores"])
         ev[1].record()
-        prop = op.propose(x["k_scores"], x["target"], x["beta"], x["log_decay"])
-        ev[2].record()
-        op.commit(*prop)
+        if op.factored:
+            prop = op.write_operands(x["k_scores"], x["target"], x["beta"], x["log_decay"])
+            ev[2].record()
+            op.commit_operands(*prop)
+        else:
+            prop = op.propose(x["k_scores"], x["target"], x["beta"], x["log_decay"])
+            ev[2].record()
+            op.commit(*prop)
         ev[3].record()
         marks.append(ev)
     torch.cuda.synchronize()
     for ev in marks:
         for i, name in enumerate(("read", "propose", "commit")):
             phase[name] += ev[i].elapsed_time(ev[i + 1])
-    unique = float(torch.unique(prop[0]).numel()) / max(1, prop[0].numel())
+    touched = prop[0].long().flatten() if op.factored else prop[0]   # one shared single-head-per-row address space
+    if op.factored and op.heads > 1:
+        touched = touched.view(-1, op.heads, prop[0].shape[-1]) + torch.arange(op.heads, device=touched.device).view(1, -1, 1) * op.slots
+    unique = float(torch.unique(touched).numel()) / max(1, touched.numel())
     return {k: v / len(marks) for k, v in phase.items()}, unique
 
 
@@ -338,6 +346,11 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
         "propose": tokens * (w.dim + 1) * 4 + entries * (w.dim * e + 4 * w.dim + 16) + tokens * w.width * 8,
         "commit": entries * (4 * w.dim + 16) + entries * 2 * w.dim * e,
     }
+    if getattr(runner.op, "factored", False):
+        # no delta rows: the proposal stage only forms the error vectors (prediction in, errors out);
+        # the commit reads a route per entry and an error vector per token, and updates each row once
+        hbm["propose"] = tokens * ((w.dim + 1) * 4 + w.dim * 4 + w.dim * e + 8)
+        hbm["commit"] = entries * 8 + tokens * (w.dim + 1) * 4 + entries * 2 * w.dim * e
     out = {"bound": "tensor", "kernel": "score_topk_kernel (tcgen05 + TMEM + TMA, fused top-k)", "achieved": achieved,
            "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
            "peak_kind": f"of {peak_kind} sustained cuBLAS bf16 (the kernel runs for >0.1 s inside a multi-second step)",
@@ -356,10 +369,12 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
     if world > 1:
         return pk_sharded_roofline(w, runner, world, peaks, peak_kind)
     phase, unique = phase_times_pk(runner)
-    algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1)
+    algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1, factored=runner.op.factored)
     dominant = max(phase, key=phase.get)
     achieved = algo[dominant] / (phase[dominant] / 1e3) / 1e9
-    names = {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"}
+    names = ({"read": "pk_select_read_kernel", "propose": "pk_select_read_kernel + write_error_kernel",
+              "commit": "factored commit (radix sort + reduce_factored_kernel)"} if runner.op.factored else
+             {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"})
     return {"bound": "hbm", "kernel": names[dominant], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}",
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": load_traffic(dominant, w),
@@ -383,6 +398,10 @@ def pk_sharded_roofline(w, runner, world, peaks, peak_kind):
         "propose": w.tokens_per_epoch * (w.dim + 1) * 4 + entries * (w.dim * e + 4 * w.dim + 16),
         "commit": entries * (4 * w.dim + 16) + entries * 2 * w.dim * e,
     }
+    if getattr(runner.op, "factored", False):
+        th = w.tokens_per_epoch * w.heads
+        algo["propose"] = th * ((w.dim + 1) * 4 + w.dim * 4 + w.dim * e + 8) // world
+        algo["commit"] = entries * 8 + th * (w.dim + 1) * 4 + entries * 2 * w.dim * e
     dominant = max((k for k in algo if k in phases), key=lambda k: phases[k])
     achieved = algo[dominant] / (phases[dominant] / 1e3) / 1e9
     return {"bound": "hbm", "kernel": {"route": "pk_select_kernel", "read": "snapshot_read_kernel (shard)",
@@ -467,7 +486,7 @@ def ours(args, w, rank, world, local, dist):
         raise SystemExit("c1/c2 hold one bank per request (replicas only); this benchmark covers the shared-bank "
                          "configurations c3-c5")
     peaks, peak_kind = measured_peaks()
-    runner = Runner(w, args.routing, dev, rank, world, dist)
+    runner = Runner(w, args.routing, dev, rank, world, dist, not args.delta_rows)
     for _ in range(args.warmup):
         runner.step()
     sampler = ClockSampler(local)
@@ -486,7 +505,7 @@ def ours(args, w, rank, world, local, dist):
     if args.routing == "dense" and world == 1 and not args.no_pk_block:
         del runner
         torch.cuda.empty_cache()
-        pk = Runner(w, "pk", dev, rank, world, dist)
+        pk = Runner(w, "pk", dev, rank, world, dist, not args.delta_rows)
         pk_ms = timed_steps(pk, args.steps, args.warmup, dist, dev)
         extra = {"note": "same workload with the reference's operator contract: factor scores [tokens, 2*half] fp32 in",
                  "value": w.tokens_per_step / (pk_ms / 1e3), "unit": "tokens/s", "ms_per_step": pk_ms,
@@ -534,6 +553,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input pass (profiling runs)")
+    ap.add_argument("--delta-rows", action="store_true",
+                    help="write the proposal's delta rows to memory and commit them (the two-step path) instead of the "
+                         "factored commit")
     ap.add_argument("--no-pk-block", action="store_true", help="skip the attached product-key-scores measurement")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]

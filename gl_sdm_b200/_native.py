@@ -57,6 +57,9 @@ SIGNATURES = {
     "glsdm_commit_undo": (_i, [_p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _sz, _p, _p, _p, _p]),
     "glsdm_undo_apply": (_i, [_p, _i, _i64, _i64, _i32, _p, _p, _i64, _p]),
     "glsdm_overlay_read": (_i, [_BANK, _p, _i, _p, _i64, _i64, _i32, _i32, _p, _p, _p, _p, _p, _p]),
+    "glsdm_commit_factored_workspace_bytes": (_sz, [_i64, _i32]),
+    "glsdm_commit_factored": (_i, [_BANK, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i64, _i64,
+                                   _i32, _i32, _i32, _p, _sz, _p, _p]),
     "glsdm_commit_static": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _p]),
     "glsdm_commit_static_max_entries": (_i64, []),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
@@ -368,6 +371,35 @@ def shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_str
                                          chunk_size, num_layers, layer_index, _ptr(addresses), _ptr(deltas),
                                          _ptr(keys), _stream(shard.device)))
     return addresses[:entries], deltas[:entries], keys[:entries]
+
+
+def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
+                    offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
+                    layer_index, key_bits=0):
+    """Commit the proposal of these write routes into ``shard`` in place without ever writing
+    its delta rows: the reducer rebuilds them from ``errors`` (the write_error buffer, laid out
+    as for shard_propose) and the bank rows it updates. ``offsets=None`` (unsharded bank):
+    every route is an entry and ``entries`` must be rows * width. ``routes`` is the int32
+    all-gather buffer addressed by index_at / weights_at, or a pair (index int32, weights)."""
+    if isinstance(routes, tuple):
+        index, weights = routes
+        require_cuda(index, weights)
+        if index.dtype != torch.int32 or weights.dtype != torch.float32:
+            raise ValueError("write routes are int32 indices with float32 weights")
+        index_ptr, weights_ptr = _ptr(index), _ptr(weights)
+    else:
+        require_cuda(routes)
+        index_ptr, weights_ptr = _at(routes, index_at), _at(routes, weights_at)
+    require_cuda(shard, errors, mass, offsets)
+    bank = bank_of(shard, slot_lo, None, slots)
+    dim = shard.shape[-1]
+    lib = library()
+    work = _workspace(shard.device, lib.glsdm_commit_factored_workspace_bytes(entries, dim))
+    _check(lib.glsdm_commit_factored(ctypes.byref(bank), index_ptr, weights_ptr,
+                                     _at(errors, 0), _ptr(mass), _ptr(offsets), entries, rows, block_rows,
+                                     route_stride, error_stride, tokens, width, chunk_offset, chunk_size, num_layers,
+                                     layer_index, key_bits, _ptr(work), work.numel(),
+                                     _ptr(status_word(shard.device)), _stream(shard.device)))
 
 
 _workspaces = threading.local()

@@ -1,0 +1,451 @@
+// Commit of a write proposal that is never written out as delta rows.
+//
+// A proposal entry is delta_k = mass * ((decay - 1) * row_k + w_k * err), with
+// err = beta * (target - decay * prediction) one vector per token
+// (gl_sdm/runtime/dense.py:11-14, built in gl_sdm/layers/global_layer.py:44-51 and summed per
+// address by gl_sdm/memory/transactions.py:90-96). row_k is the bank row the commit is about to
+// update, so the reducer already holds it: it needs only the token's error vector and three
+// scalars per entry to rebuild the delta in registers. The [entries, dim] fp32 delta array of
+// the materialised path (4*dim bytes written by the proposal and read back by the commit,
+// plus the proposal's second read of the bank rows) disappears; what crosses HBM per entry is
+// its 8-byte key, 8-byte address and a 16-byte descriptor, plus one read-modify-write per
+// touched bank row. Error vectors are shared by a token's K entries and stay in L2.
+//
+// The arithmetic is the materialised path's, operation for operation (same fp32 products,
+// sums and order), so both commits produce bit-identical banks.
+#include "commit.cuh"
+#include "route.cuh"
+
+namespace glsdm {
+namespace {
+
+// What the reducer needs to rebuild one entry's delta row.
+struct __align__(16) Descriptor {
+  uint32_t error_at;  // float offset of the token's error row in the error array
+  float weight;       // w_k
+  float gate;         // decay - 1
+  float mass;
+};
+
+struct FactoredScratch {
+  int64_t* keys;          // [entries] unsorted sort keys
+  int64_t* addresses;     // [entries] unsorted shard-local rows
+  Descriptor* described;  // [entries] unsorted
+  Descriptor* sorted;     // [entries] in key order
+};
+
+size_t carve_factored(Workspace* w, FactoredScratch* f, char* base, int64_t entries, int32_t dim) {
+  size_t at = carve(w, base, entries, dim);
+  auto take = [&](size_t bytes) {
+    char* p = base ? base + at : nullptr;
+    at += align_up(bytes, 256);
+    return p;
+  };
+  FactoredScratch local;
+  FactoredScratch* o = f ? f : &local;
+  o->keys = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
+  o->addresses = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
+  o->described = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
+  o->sorted = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
+  return at;
+}
+
+struct EntryArgs {
+  const int32_t* index;     // write routes, blocks of block_rows rows, route_stride apart
+  const float* weights;
+  const float* error;       // per block: [block_rows, dim] error rows then [block_rows] decay-1
+  const float* mass;        // per token or null
+  const uint32_t* offsets;  // first entry of every row, or null: entry = row * width + route
+  int64_t rows, block_rows, route_stride, error_stride, tokens;
+  int64_t chunk_offset, key_stride;
+  int width, num_layers, layer_index;
+};
+
+// One warp per routing row: address, sort key and descriptor of every route this shard owns
+// (addresses and keys as in gl_sdm/layers/global_layer.py:45,52-53).
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+factored_entries_kernel(BankView bank, EntryArgs a, FactoredScratch out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= a.rows) return;
+  const int64_t block = row / a.block_rows, inner = row % a.block_rows;
+  int64_t slot = -1;
+  float w = 0.f;
+  if (lane < a.width) {
+    slot = a.index[block * a.route_stride + inner * a.width + lane];
+    w = a.weights[block * a.route_stride + inner * a.width + lane];
+  }
+  const bool owned = slot >= bank.slot_lo && slot < bank.slot_hi;
+  const unsigned mask = __ballot_sync(kFullMask, owned);
+  const int64_t head = row % bank.heads;
+  const int64_t token = row / bank.heads;
+  Descriptor d;
+  d.error_at = static_cast<uint32_t>(block * a.error_stride + inner * bank.dim);
+  d.weight = w;
+  d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
+  d.mass = a.mass != nullptr ? a.mass[token] : 1.0f;
+  if (a.offsets != nullptr) {
+    if (!owned) return;
+    const int64_t at = static_cast<int64_t>(a.offsets[row]) + __popc(mask & ((1u << lane) - 1u));
+    const int64_t position = a.chunk_offset + token % a.tokens;
+    out.addresses[at] = head * bank.part_stride_rows + (slot - bank.slot_lo);
+    out.keys[at] = (head * bank.slots + slot) * a.key_stride + position * a.num_layers + a.layer_index;
+    out.described[at] = d;
+  } else if (lane < a.width) {
+    // Dense numbering: every route has an entry; a slot outside the bank takes the key one
+    // past the last address, sorts last, and is dropped (and reported) by the reducer through
+    // its out-of-range address.
+    const int64_t at = row * a.width + lane;
+    const int64_t position = a.chunk_offset + token % a.tokens;
+    out.addresses[at] = owned ? head * bank.part_stride_rows + (slot - bank.slot_lo) : -1;
+    out.keys[at] = owned ? (head * bank.slots + slot) * a.key_stride + position * a.num_layers + a.layer_index
+                         : static_cast<int64_t>(bank.heads) * bank.slots * a.key_stride;
+    out.described[at] = d;
+  }
+}
+
+__global__ void gather_factored_kernel(Workspace w, FactoredScratch f, int64_t entries) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= entries) return;
+  const uint32_t id = w.ids[w.plan->final_buffer][i];
+  w.sorted_address[i] = f.addresses[id];
+  f.sorted[i] = f.described[id];
+}
+
+__device__ __forceinline__ Descriptor shfl_descriptor(const Descriptor& d, int src) {
+  Descriptor o;
+  o.error_at = __shfl_sync(kFullMask, d.error_at, src);
+  o.weight = __shfl_sync(kFullMask, d.weight, src);
+  o.gate = __shfl_sync(kFullMask, d.gate, src);
+  o.mass = __shfl_sync(kFullMask, d.mass, src);
+  return o;
+}
+
+// delta = mass * (gate * old + weight * err), the products and the sum rounded one by one as
+// the materialised proposal kernels do.
+template <int V>
+__device__ __forceinline__ void rebuild(Slice<V>& delta, const Descriptor& d, const Slice<V>& err,
+                                        const Slice<V>& old) {
+#pragma unroll
+  for (int i = 0; i < V; ++i)
+    delta.v[i] = __fmul_rn(d.mass, __fadd_rn(__fmul_rn(d.gate, old.v[i]), __fmul_rn(d.weight, err.v[i])));
+}
+
+// Sum entries [start, start+count) of the sorted order, strictly left to right.
+template <int V>
+__device__ __forceinline__ void sum_factored(Slice<V>& acc, const Descriptor* __restrict__ sorted,
+                                             const float* __restrict__ error, const Slice<V>& old,
+                                             int64_t start, int64_t count, int lane) {
+  for (int64_t done = 0; done < count; done += 32) {
+    const int n = (count - done < 32) ? static_cast<int>(count - done) : 32;
+    Descriptor mine = {0u, 0.f, 0.f, 0.f};
+    if (lane < n) mine = sorted[start + done + lane];
+    constexpr int kAhead = V >= 8 ? 2 : 4;   // error rows requested before the first is used
+    int t = 0;
+    for (; t + kAhead <= n; t += kAhead) {
+      Slice<V> e[kAhead];
+      Descriptor d[kAhead];
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j) {
+        d[j] = shfl_descriptor(mine, t + j);
+        load_delta<V>(e[j], error + d[j].error_at, lane);
+      }
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j) {
+        Slice<V> x;
+        rebuild<V>(x, d[j], e[j], old);
+        add<V>(acc, x);
+      }
+    }
+    for (; t < n; ++t) {
+      const Descriptor d = shfl_descriptor(mine, t);
+      Slice<V> e, x;
+      load_delta<V>(e, error + d.error_at, lane);
+      rebuild<V>(x, d, e, old);
+      add<V>(acc, x);
+    }
+  }
+}
+
+// Any-width variant over the 8 column blocks [c0, c0+256): lanes stride the columns.
+template <typename T>
+__device__ __forceinline__ void sum_factored_generic(float (&acc)[8], const float (&old)[8],
+                                                     const Descriptor* __restrict__ sorted,
+                                                     const float* __restrict__ error, int dim, int c0,
+                                                     int64_t start, int64_t count, int lane) {
+  for (int64_t t = 0; t < count; ++t) {
+    const Descriptor d = sorted[start + t];
+    const float* __restrict__ erow = error + d.error_at;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j * 32 + lane;
+      if (c < dim) {
+        const float x = __fmul_rn(d.mass, __fadd_rn(__fmul_rn(d.gate, old[j]), __fmul_rn(d.weight, __ldg(erow + c))));
+        acc[j] = __fadd_rn(acc[j], x);
+      }
+    }
+  }
+}
+
+struct FactoredArgs {
+  void* values;           // shard rows [bank_rows, dim], updated in place
+  const float* error;
+  const Descriptor* sorted;
+  int64_t entries;
+  int64_t bank_rows;
+  int dim;
+  uint32_t* device_status;
+};
+
+constexpr int kFactoredBatch = 2;   // single-entry rows in flight per warp (as in the delta-row reducer)
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+reduce_factored_kernel(Workspace w, FactoredArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp) * 32;
+  if (first >= a.entries) return;
+  const int64_t* __restrict__ sorted = w.sorted_address;
+  const int64_t at = first + lane;
+  const int64_t mine = at < a.entries ? sorted[at] : -1;
+  const int64_t prev = (at > 0 && at < a.entries) ? sorted[at - 1] : -2;
+  const bool is_head = at < a.entries && (at == 0 || mine != prev);
+  const unsigned all_heads = __ballot_sync(kFullMask, is_head);
+  unsigned heads = all_heads;
+  T* __restrict__ values = static_cast<T*>(a.values);
+  if constexpr (V > 0) {
+    const int64_t next = (at + 1 < a.entries) ? sorted[at + 1] : -3;
+    Descriptor my_d = {0u, 0.f, 0.f, 0.f};
+    if (at < a.entries) my_d = a.sorted[at];
+    unsigned singles = __ballot_sync(kFullMask, is_head && mine != next && mine >= 0 && mine < a.bank_rows);
+    heads &= ~singles;
+    while (singles) {
+      int pick[kFactoredBatch];
+#pragma unroll
+      for (int j = 0; j < kFactoredBatch; ++j) {
+        pick[j] = singles ? __ffs(singles) - 1 : -1;
+        if (singles) singles &= singles - 1;
+      }
+      Slice<V> err[kFactoredBatch], old[kFactoredBatch];
+      Descriptor d[kFactoredBatch];
+      int64_t where[kFactoredBatch];
+#pragma unroll
+      for (int j = 0; j < kFactoredBatch; ++j) {
+        if (pick[j] < 0) continue;
+        d[j] = shfl_descriptor(my_d, pick[j]);
+        where[j] = __shfl_sync(kFullMask, mine, pick[j]);
+        load_delta<V>(err[j], a.error + d[j].error_at, lane);
+        load_bank<T, V>(values + where[j] * a.dim, old[j], lane);
+      }
+#pragma unroll
+      for (int j = 0; j < kFactoredBatch; ++j) {
+        if (pick[j] < 0) continue;
+        Slice<V> x;
+        rebuild<V>(x, d[j], err[j], old[j]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) old[j].v[i] = __fadd_rn(old[j].v[i], __fadd_rn(0.f, x.v[i]));
+        store_bank<T, V>(values + where[j] * a.dim, old[j], lane);
+      }
+    }
+  }
+  while (heads) {
+    const int h = __ffs(heads) - 1;
+    heads &= heads - 1;
+    const int64_t start = first + h;
+    const int64_t local = __shfl_sync(kFullMask, mine, h);
+    if (local < 0 || local >= a.bank_rows) {
+      if (lane == 0 && a.device_status) atomicOr(a.device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+      continue;
+    }
+    int64_t len;
+    const unsigned later = h == 31 ? 0u : (all_heads & (0xffffffffu << (h + 1)));
+    if (later) {
+      len = (__ffs(later) - 1) - h;
+    } else {
+      const int64_t tail = first + 32 < a.entries ? first + 32 : a.entries;
+      len = tail - start;
+      if (tail < a.entries) len = segment_length(sorted, tail - 1, a.entries, local, lane) + (tail - 1 - start);
+    }
+    if (len > kLongSegment) {
+      if (lane == 0) {
+        const uint32_t slot = atomicAdd(&w.plan->long_count, 1u);
+        w.long_list[slot] = make_uint2(static_cast<uint32_t>(start), static_cast<uint32_t>(len));
+      }
+      continue;
+    }
+    T* row = values + local * a.dim;
+    if constexpr (V > 0) {
+      Slice<V> old, acc;
+      load_bank<T, V>(row, old, lane);
+      zero<V>(acc);
+      sum_factored<V>(acc, a.sorted, a.error, old, start, len, lane);
+#pragma unroll
+      for (int i = 0; i < V; ++i) old.v[i] = __fadd_rn(old.v[i], acc.v[i]);
+      store_bank<T, V>(row, old, lane);
+    } else {
+      for (int c0 = 0; c0 < a.dim; c0 += 256) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float old[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          old[j] = c < a.dim ? load_value<T>(row + c) : 0.f;
+        }
+        sum_factored_generic<T>(acc, old, a.sorted, a.error, a.dim, c0, start, len, lane);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (c < a.dim) store_value<T>(row + c, __fadd_rn(old[j], acc[j]));
+        }
+      }
+    }
+  }
+}
+
+// One block per queued long segment: 256-entry chunks summed in order by warps (each warp
+// reads the old row itself), chunk sums added in chunk order, row updated once. The block
+// must finish reading the old row before anyone overwrites it: the update happens after the
+// barrier that ends the chunk loop.
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+long_factored_kernel(Workspace w, FactoredArgs a) {
+  __shared__ uint32_t partial_base;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t count = w.plan->long_count;
+  for (uint32_t s = blockIdx.x; s < count; s += gridDim.x) {
+    const uint2 seg = w.long_list[s];
+    const int64_t start = seg.x, len = seg.y;
+    const int chunks = static_cast<int>((len + kLongSegment - 1) / kLongSegment);
+    __syncthreads();
+    if (threadIdx.x == 0) partial_base = atomicAdd(&w.plan->chunk_cursor, static_cast<uint32_t>(chunks));
+    __syncthreads();
+    float* __restrict__ partial = w.partial + static_cast<int64_t>(partial_base) * a.dim;
+    T* row = static_cast<T*>(a.values) + w.sorted_address[start] * a.dim;
+    for (int c = warp; c < chunks; c += kWarpsPerBlock) {
+      const int64_t cs = start + static_cast<int64_t>(c) * kLongSegment;
+      const int64_t cn = (len - static_cast<int64_t>(c) * kLongSegment < kLongSegment)
+                             ? len - static_cast<int64_t>(c) * kLongSegment : kLongSegment;
+      float* prow = partial + static_cast<int64_t>(c) * a.dim;
+      if constexpr (V > 0) {
+        Slice<V> old, acc;
+        load_bank<T, V>(row, old, lane);
+        zero<V>(acc);
+        sum_factored<V>(acc, a.sorted, a.error, old, cs, cn, lane);
+#pragma unroll
+        for (int i = 0; i < V; ++i) prow[column_of<V>(lane, i)] = acc.v[i];
+      } else {
+        for (int c0 = 0; c0 < a.dim; c0 += 256) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          float old[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int col = c0 + j * 32 + lane;
+            old[j] = col < a.dim ? load_value<T>(row + col) : 0.f;
+          }
+          sum_factored_generic<T>(acc, old, a.sorted, a.error, a.dim, c0, cs, cn, lane);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int col = c0 + j * 32 + lane;
+            if (col < a.dim) prow[col] = acc[j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    for (int col = threadIdx.x; col < a.dim; col += blockDim.x) {
+      float total = 0.f;
+      for (int c = 0; c < chunks; ++c) total = __fadd_rn(total, partial[static_cast<int64_t>(c) * a.dim + col]);
+      store_value<T>(row + col, __fadd_rn(load_value<T>(row + col), total));
+    }
+  }
+}
+
+template <typename T>
+int launch_factored(const Workspace& w, const FactoredArgs& a, bool aligned, glsdm_stream_t stream) {
+  const int grid = blocks_for((a.entries + 31) / 32, kWarpsPerBlock);
+  const int long_grid = static_cast<int>(w.long_capacity < 1184 ? w.long_capacity : 1184);
+#define GLSDM_FACTORED(V)                                                                   \
+  do {                                                                                      \
+    reduce_factored_kernel<T, V><<<grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);           \
+    GLSDM_CUDA_OK(cudaGetLastError(), "factored reduce launch");                            \
+    long_factored_kernel<T, V><<<long_grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);        \
+    GLSDM_CUDA_OK(cudaGetLastError(), "factored long-segment launch");                      \
+    count_launches(2);                                                                      \
+  } while (0)
+  if (aligned && a.dim == 32) GLSDM_FACTORED(1);
+  else if (aligned && a.dim == 64) GLSDM_FACTORED(2);
+  else if (aligned && a.dim == 128) GLSDM_FACTORED(4);
+  else if (aligned && a.dim == 256) GLSDM_FACTORED(8);
+  else GLSDM_FACTORED(0);
+#undef GLSDM_FACTORED
+  return GLSDM_OK;
+}
+
+}  // namespace
+}  // namespace glsdm
+
+using namespace glsdm;
+
+extern "C" size_t glsdm_commit_factored_workspace_bytes(int64_t entries, int32_t dim) {
+  if (entries < 0 || dim < 1) return 0;
+  return carve_factored(nullptr, nullptr, nullptr, entries < 1 ? 1 : entries, dim);
+}
+
+extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                                     const float* error, const float* mass, const uint32_t* offsets,
+                                     int64_t entries, int64_t rows, int64_t block_rows,
+                                     int64_t route_stride, int64_t error_stride, int64_t tokens,
+                                     int32_t width, int64_t chunk_offset, int64_t chunk_size,
+                                     int32_t num_layers, int32_t layer_index, int32_t key_bits,
+                                     void* workspace, size_t workspace_bytes, uint32_t* device_status,
+                                     glsdm_stream_t stream) {
+  if (rows == 0 || entries == 0) return GLSDM_OK;
+  if (bank == nullptr || bank->values == nullptr) return GLSDM_ERR_ARGUMENT;
+  if (bank->dtype != GLSDM_F32 && bank->dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
+  if (index == nullptr || weights == nullptr || error == nullptr || workspace == nullptr) return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || entries < 0 || tokens < 1 || width < 1 || chunk_size < 1 || num_layers < 1 || layer_index < 0 ||
+      layer_index >= num_layers || chunk_offset < 0 || block_rows < 1 || route_stride < 0 || error_stride < 0)
+    return GLSDM_ERR_ARGUMENT;
+  if (key_bits < 0 || key_bits > 64) return GLSDM_ERR_ARGUMENT;
+  if (width > 32 || bank->banks != 1) return GLSDM_ERR_UNSUPPORTED;
+  if (entries > 0xfffffff0ll) return GLSDM_ERR_LIMIT;
+  if (offsets == nullptr && entries != rows * width) return GLSDM_ERR_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GLSDM_ERR_ARGUMENT;
+  const BankView v = make_view(*bank);
+  // Descriptors address error rows with 32 bits.
+  const int64_t blocks = (rows + block_rows - 1) / block_rows;
+  if ((blocks - 1) * error_stride + block_rows * static_cast<int64_t>(v.dim + 1) > 0xffffffffll) return GLSDM_ERR_LIMIT;
+  Workspace w;
+  FactoredScratch f;
+  const size_t need = carve_factored(&w, &f, static_cast<char*>(workspace), entries, v.dim);
+  if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
+
+  EntryArgs e;
+  e.index = index; e.weights = weights; e.error = error; e.mass = mass; e.offsets = offsets;
+  e.rows = rows; e.block_rows = block_rows; e.route_stride = route_stride; e.error_stride = error_stride;
+  e.tokens = tokens; e.chunk_offset = chunk_offset; e.key_stride = chunk_size * num_layers;
+  e.width = width; e.num_layers = num_layers; e.layer_index = layer_index;
+  factored_entries_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored entries launch");
+  // With dense numbering a slot outside the bank carries the key one past the largest valid one.
+  const int passes = sort_passes(offsets == nullptr && key_bits > 0 && key_bits < 64 ? key_bits + 1 : key_bits);
+  if (int s = run_sort(w, f.keys, entries, passes, stream)) return s;
+  gather_factored_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, f, entries);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored gather launch");
+  count_launches(2);
+
+  FactoredArgs a;
+  a.values = const_cast<void*>(bank->values);
+  a.error = error;
+  a.sorted = f.sorted;
+  a.entries = entries;
+  a.bank_rows = static_cast<int64_t>(v.heads) * v.part_stride_rows;
+  a.dim = v.dim;
+  a.device_status = device_status;
+  // 16-byte loads of error rows and bank rows need aligned bases and row offsets.
+  const bool aligned = (reinterpret_cast<uintptr_t>(error) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(bank->values) & 15u) == 0 &&
+                       (error_stride % 4 == 0 || block_rows >= rows) && v.dim % 4 == 0;
+  if (bank->dtype == GLSDM_F32) return launch_factored<float>(w, a, aligned, stream);
+  return launch_factored<__nv_bfloat16>(w, a, aligned, stream);
+}

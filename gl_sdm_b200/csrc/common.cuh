@@ -12,7 +12,10 @@ namespace glsdm {
 
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kWarpsPerBlock = 8;
-constexpr int kStageSlots = 64;  // staged candidates per warp (shared memory, 8 bytes each)
+constexpr int kStageKeys = 64;   // staged candidate keys per warp (shared memory, 8 bytes each)
+// Per-warp selection scratch in 8-byte units: the staged keys, then 256 16-bit lane slots of
+// the two-pass factor selection.
+constexpr int kStageSlots = kStageKeys + 64;
 
 // Thread-local record of the last CUDA failure, for glsdm_last_cuda_error().
 void note_cuda_error(cudaError_t err, const char* where);

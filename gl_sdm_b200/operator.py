@@ -21,7 +21,7 @@ class SharedBankOperator:
     commit then applies all deltas in (address, position, layer, arrival) order in place.
     """
 
-    def __init__(self, values, reads, writes, chunk_size=512, num_layers=1, layer_index=0):
+    def __init__(self, values, reads, writes, chunk_size=512, num_layers=1, layer_index=0, factored=True):
         if values.ndim != 4 or values.shape[0] != 1:
             raise ValueError("a shared bank is [1, heads, slots, dim]")
         _native.require_cuda(values)
@@ -35,6 +35,11 @@ class SharedBankOperator:
         self.version = 0
         self.key_bits = max(1, (self.heads * self.slots * chunk_size * num_layers - 1).bit_length())
         self._buffers = None
+        # factored: the epoch's commit rebuilds each delta row from the token's error vector and
+        # the bank row it updates instead of reading a materialised [entries, dim] delta array
+        # (bit-identical result, a third of the HBM traffic on the write side).
+        self.factored = factored
+        self._packed = None
 
     def _proposal_buffers(self, rows):
         k = _native.routes_out(self.writes, self.half)
@@ -64,8 +69,33 @@ class SharedBankOperator:
         _native.commit_rows(self.values, addresses, deltas, keys, out=self.values, key_bits=self.key_bits)
         self.version += 1
 
+    def write_operands(self, k_scores, target, beta, log_decay):
+        """Write side without delta rows, first half: write routes, prediction read and the
+        per-token error vector beta * (target - decay * prediction) with decay - 1
+        (reference layers/global_layer.py:41-51). -> (index int32, weights, packed errors)."""
+        tokens = k_scores.shape[1]
+        prediction, index, weights = _native.pk_select_read(self.values, k_scores, self.writes, tokens * self.heads,
+                                                            index_dtype=torch.int32)
+        rows = index.numel() // index.shape[-1]
+        if self._packed is None or self._packed.numel() != rows * (self.dim + 1):
+            self._packed = torch.empty(rows * (self.dim + 1), dtype=torch.float32, device=self.values.device)
+        return index, weights, _native.write_error(prediction, target, beta, log_decay, self._packed)
+
+    def commit_operands(self, index, weights, packed, offset=0):
+        """Second half: the factored commit (reference layers/global_layer.py:52-54 and
+        memory/transactions.py:90-96 in one pass; every route is an entry, no host sync)."""
+        tokens, width = index.shape[1], index.shape[-1]
+        rows = index.numel() // width
+        _native.commit_factored(self.values, 0, self.slots, (index, weights), 0, 0, 0, packed, 0, None, None,
+                                rows * width, rows, rows, tokens, width, offset, self.chunk_size, self.num_layers,
+                                self.layer_index, self.key_bits)
+        self.version += 1
+
     def epoch(self, q_scores, k_scores, target, beta, log_decay, offset=0):
         """One full commit epoch: read, propose, commit. Returns the readings."""
         readings = self.read(q_scores)
-        self.commit(*self.propose(k_scores, target, beta, log_decay, offset))
+        if self.factored:
+            self.commit_operands(*self.write_operands(k_scores, target, beta, log_decay), offset)
+        else:
+            self.commit(*self.propose(k_scores, target, beta, log_decay, offset))
         return readings

@@ -65,7 +65,7 @@ class ShardedBankOperator:
     `keys` [S, dk] (or this rank's [S/R, dk] slice with is_shard) enables dense-key routing."""
 
     def __init__(self, values, reads, writes, dist=None, chunk_size=512, num_layers=1, layer_index=0,
-                 group=None, is_shard=False, slots=None, kernels=_native, keys=None):
+                 group=None, is_shard=False, slots=None, kernels=_native, keys=None, factored=True):
         if reads != writes:
             raise ValueError("the sharded operator needs equal read and write widths")
         dist = SingleProcess if dist is None else dist
@@ -91,6 +91,10 @@ class ShardedBankOperator:
         self.chunk_size, self.num_layers, self.layer_index = chunk_size, num_layers, layer_index
         self.key_bits = max(1, (self.heads * self.slots * chunk_size * num_layers - 1).bit_length())
         self.version = 0
+        # factored: the commit rebuilds every delta row from its token's error vector and the
+        # bank row it updates (no [entries, dim] delta array); False keeps the two-step
+        # proposal + commit with materialised deltas. Both give bit-identical banks.
+        self.factored = factored
         self._buf = {}
         self.marks = None   # set to a list to collect (stage name, CUDA event) pairs for profiling
 
@@ -182,7 +186,12 @@ class ShardedBankOperator:
             errors = packed
         offsets = k.shard_offsets(routes, plan["write_index_at"], R * n, n, stride, K, self.slot_lo, self.slot_hi)
         entries = int(offsets[-1].item())
-        if entries:
+        if entries and self.factored:
+            self._mark("commit")
+            k.commit_factored(self.shard, self.slot_lo, self.slots, routes, plan["write_index_at"],
+                              plan["write_weights_at"], stride, errors, n * (D + 1), None, offsets, entries, R * n, n,
+                              tokens, K, offset, self.chunk_size, self.num_layers, self.layer_index, self.key_bits)
+        elif entries:
             out = (self._buffer("addresses", entries, torch.int64),
                    self._buffer("deltas", entries * D, torch.float32).view(entries, D),
                    self._buffer("keys", entries, torch.int64))

@@ -151,15 +151,23 @@ def make_epoch_inputs_dense(w, device, seed, sequences=None, tokens=None, keys=N
     return out
 
 
-def algorithmic_bytes(w, tokens, unique_fraction=1.0, layers=None):
+def algorithmic_bytes(w, tokens, unique_fraction=1.0, layers=None, factored=False):
     """Bytes each stage must move for `tokens` tokens (per-unit figures: see DESIGN.md):
     query read K*D*e + 4*D plus 8*half of factor scores; proposal K*D*e + 8*half + target +
-    K*(4*D+16) written; commit K*(4*D+16) read + u*K*2*D*e rows."""
+    K*(4*D+16) written; commit K*(4*D+16) read + u*K*2*D*e rows. With the factored commit no
+    delta rows exist: the proposal stage ends at the error vector (4*(D+1) written), the commit
+    reads 8 bytes of route per entry and the error vector once, and updates u*K rows."""
     e = 2 if w.bank_dtype == torch.bfloat16 else 4
     te = e
     L = layers or w.global_layers
     th = tokens * w.heads * L
     K, D, half = w.width, w.dim, w.half
+    if factored:
+        return {
+            "read": th * (8 * half + K * D * e + 4 * D),
+            "propose": th * (8 * half + K * D * e + D * te + 8 + 4 * (D + 1)),
+            "commit": th * (K * 8 + 4 * (D + 1) + unique_fraction * K * 2 * D * e),
+        }
     return {
         "read": th * (8 * half + K * D * e + 4 * D),
         "propose": th * (8 * half + K * D * e + D * te + 8 + K * (4 * D + 16)),

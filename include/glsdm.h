@@ -246,6 +246,31 @@ int glsdm_overlay_read(const glsdm_bank* bank, const void* index, int index_i64,
                        const void* const* log_rows, const int64_t* log_entries, float* out_read,
                        uint32_t* device_status, glsdm_stream_t stream);
 
+/* Commit of a proposal in factored form: the delta rows
+ *   delta_k = mass * ((decay - 1) * row_k + w_k * err),  err = beta * (target - decay * prediction)
+ * (gl_sdm/runtime/dense.py:11-14; entries and keys of gl_sdm/layers/global_layer.py:44-54) are
+ * never written out. The caller passes what they are made of — the write routes, the per-token
+ * error rows and decay-1 of glsdm_write_error — and the reducer rebuilds each delta in registers
+ * from the bank row it is updating. Same sums in the same order as glsdm_shard_propose /
+ * glsdm_pk_propose followed by glsdm_commit in place: the banks come out bit-identical.
+ *   bank          the shard to update in place ([1, heads, local slots, dim], slot range set)
+ *   index/weights write routes as for glsdm_shard_propose (blocks of block_rows rows,
+ *                 route_stride elements apart; one block: block_rows = rows)
+ *   error         per block: [block_rows, dim] error rows then [block_rows] decay-1 values,
+ *                 error_stride floats per block
+ *   offsets       glsdm_shard_offsets of the same routes, entries = its total; or NULL for an
+ *                 unsharded bank: every route is an entry, entries = rows * width (no host
+ *                 synchronisation needed)
+ *   workspace     glsdm_commit_factored_workspace_bytes(entries, dim), 256-byte aligned */
+size_t glsdm_commit_factored_workspace_bytes(int64_t entries, int32_t dim);
+int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                          const float* error, const float* mass, const uint32_t* offsets,
+                          int64_t entries, int64_t rows, int64_t block_rows, int64_t route_stride,
+                          int64_t error_stride, int64_t tokens, int32_t width, int64_t chunk_offset,
+                          int64_t chunk_size, int32_t num_layers, int32_t layer_index,
+                          int32_t key_bits, void* workspace, size_t workspace_bytes,
+                          uint32_t* device_status, glsdm_stream_t stream);
+
 /* Commit for hosts that cannot provide a workspace. It has no counterpart in the reference
  * (whose commit allocates freely through PyTorch). Same arguments and result as glsdm_commit,
  * minus the workspace: the sort/reduce scratch is a 4 MiB array built into the library's

@@ -83,3 +83,16 @@ def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_
     new = oracle.commit(values.float().numpy(), addresses.numpy(), deltas.numpy(), None if keys is None else keys.numpy())
     out.copy_(torch.from_numpy(new).to(out.dtype))
     return out
+
+
+def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
+                    offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
+                    layer_index, key_bits=0):
+    """The factored commit is defined as proposal expansion followed by the in-place commit."""
+    D = shard.shape[-1]
+    out = (torch.empty(entries, dtype=torch.int64), torch.empty(entries, D), torch.empty(entries, dtype=torch.int64))
+    a, d, s = shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride,
+                            mass, offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size,
+                            num_layers, layer_index, out)
+    flat = shard.view(-1, D)
+    commit_rows(flat, a, d, s, out=flat, key_bits=key_bits)

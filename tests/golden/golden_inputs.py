@@ -11,12 +11,13 @@ import torch
 import torch.nn.functional as F
 
 ROUTED_CASES = ("ties_zero", "colliding_tiny", "production_bank", "factor512", "signed_zero_ties",
-                "c2_like", "wide_k32", "width_gt_half", "odd_half", "bf16_ties")
+                "c2_like", "wide_k32", "width_gt_half", "odd_half", "bf16_ties", "nan_inf_scores")
 PROPOSE_CASES = ("c1_like", "two_layers", "hot_slots")
 
 
 def checksum(t):
-    return float(t.double().sum().item())
+    # NaN and infinities count as fixed finite values so that the sum still pins the draw
+    return float(torch.nan_to_num(t.double(), nan=7.0, posinf=11.0, neginf=-13.0).sum().item())
 
 
 def routed_case(name):
@@ -65,6 +66,17 @@ def routed_case(name):
         memory = torch.randn(2, 2, 1024, 16)
         scores = (torch.randn(2, 33, 2, 64) * 0.25).bfloat16().float()
         scores = (scores * 4).round() / 4  # coarse grid: many exact ties at every boundary
+        return memory, scores, 8
+    if name == "nan_inf_scores":  # torch ranks NaN above +inf; sums with NaN are NaN and rank first
+        torch.manual_seed(13)
+        memory = torch.randn(1, 2, 256 * 256, 4)
+        scores = torch.randn(1, 24, 2, 512)
+        mask = torch.rand(scores.shape)
+        scores[mask < 0.01] = float("nan")
+        scores[(mask > 0.01) & (mask < 0.02)] = float("inf")
+        scores[(mask > 0.02) & (mask < 0.03)] = float("-inf")
+        scores[0, 0, 0, :256] = float("nan")
+        scores[0, 1] = torch.randn(2, 512)          # a clean row among them
         return memory, scores, 8
     raise KeyError(name)
 

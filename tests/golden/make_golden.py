@@ -2,7 +2,7 @@
 
 Run where the reference checkout is present (it is not needed afterwards):
 
-    python tests/golden/make_golden.py /path/to/GL-SDM
+    python tests/golden/make_golden.py /path/to/GL-SDM [routed case names ...]
 
 It imports the reference's own gl_sdm.memory (CPU, torch path), replays the inputs of the
 reference's tests for this path (tests/test_chunk_memory.py, test_layer_stack.py,
@@ -21,7 +21,7 @@ sys.path.insert(0, HERE)
 import golden_inputs as gi  # noqa: E402
 
 
-def main(reference_root):
+def main(reference_root, only=None):
     sys.path.insert(0, os.path.join(reference_root, "projects", "gl-sdm", "src"))
     from gl_sdm.memory import MemoryView, WriteProposal, commit, merge, read, propose_write
     from gl_sdm.memory.routing import torch_routed_read, gather_rows, absolute_addresses
@@ -32,6 +32,8 @@ def main(reference_root):
 
     # -- routed reads -------------------------------------------------------------------
     for name in gi.ROUTED_CASES:
+        if only and name not in only:
+            continue
         memory, scores, width = gi.routed_case(name)
         readings, index, weights = torch_routed_read(memory, scores, width)
         rec = {"readings": readings.numpy(), "index": index.numpy().astype(np.int32), "weights": weights.numpy(),
@@ -40,6 +42,9 @@ def main(reference_root):
             rec["memory"], rec["scores"] = memory.numpy(), scores.numpy()
         np.savez_compressed(os.path.join(HERE, f"routed_{name}.npz"), **rec)
         out[f"routed_{name}"] = tuple(index.shape)
+    if only:
+        print("wrote", sorted(out))
+        return
 
     # -- write proposal (global_layer.py:41-54 from the scores on) + commit ---------------
     for name in gi.PROPOSE_CASES:
@@ -131,4 +136,5 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # python make_golden.py [reference root] [routed case names to (re)write; default: everything]
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", set(sys.argv[2:]) or None)
