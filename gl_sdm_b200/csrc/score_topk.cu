@@ -28,6 +28,7 @@
 // Tie rule (gl_sdm/memory/routing.py:21-24): equal scores prefer the larger slot. Slots are
 // scanned in ascending order, so a score equal to the current k-th one replaces it.
 #include "score_topk_pair.cuh"
+#include "score_topk_wide.cuh"
 
 namespace glsdm {
 namespace {
@@ -224,17 +225,27 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const float floor = *my_floor;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const float best = max_of_32(&r[c * 32]);
+            float group[11];
+            const float best = max_of_32(&r[c * 32], group);
             if (!__any_sync(kFullMask, best >= floor)) continue;
             // Rare path. Registers cannot be indexed by a run-time column, and handling every
-            // column inline would bloat the loop, so: one bit per passing column, then a short
+            // column inline would bloat the loop, so: one bit per passing column - looking only
+            // into the three-column groups whose maximum passes in some row - then a short
             // loop over the columns that passed in any row, re-reading that single column
             // from tensor memory (the buffer is released only after the tile's events).
             const int first = h * 64 + c * 32;
             uint32_t mine = 0;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              mine |= (__uint_as_float(r[c * 32 + i]) >= floor && first + i < live_cols) ? (1u << i) : 0u;
+            for (int j = 0; j < 11; ++j) {
+              if (!__any_sync(kFullMask, group[j] >= floor)) continue;
+#pragma unroll
+              for (int i = 3 * j; i < (j < 10 ? 3 * j + 3 : 32); ++i)
+                mine |= (__uint_as_float(r[c * 32 + i]) >= floor) ? (1u << i) : 0u;
+            }
+            if (live_cols < kTileCols) {        // the ragged last tile: columns past the end never count
+              const int valid = live_cols - first;
+              mine &= valid >= 32 ? 0xffffffffu : (valid <= 0 ? 0u : (1u << valid) - 1u);
+            }
             uint32_t cols = __reduce_or_sync(kFullMask, mine);
             const uint32_t slot0 = static_cast<uint32_t>(col0) + first;
             while (cols && ok) {
@@ -396,13 +407,13 @@ EncodeTiled encode_tiled() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows, dk] with a row pitch of `pitch` elements; boxes of [128 rows x 64].
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int dk, int64_t pitch) {
+// 2-D bf16 tensor [rows, dk] with a row pitch of `pitch` elements; boxes of [box_rows x 64].
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int dk, int64_t pitch, int box_rows = kBlockRows) {
   EncodeTiled enc = encode_tiled();
   if (enc == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(dk), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * 2};
-  const cuuint32_t box[2] = {kAtomK, kBlockRows};
+  const cuuint32_t box[2] = {kAtomK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -418,9 +429,9 @@ struct Plan {
 // roughly 220*k key-tile times per unit), so the model is
 //   time(s) = waves(s) * (tiles per split + 220*k),  waves = ceil(row pairs * s / SMs),
 // minimised over s with at least 1024 key tiles per split; ties prefer fewer splits.
-Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = kTileCols) {
+Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = kTileCols, int unit_rows = kUnitRows) {
   Plan pl;
-  pl.unit_pairs = static_cast<int>((rows + kUnitRows - 1) / kUnitRows);
+  pl.unit_pairs = static_cast<int>((rows + unit_rows - 1) / unit_rows);
   pl.tiles_total = static_cast<int>((slots + tile_cols - 1) / tile_cols);
   const int64_t restart = 220ll * width;
   int best = 1;
@@ -439,20 +450,7 @@ Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = 
   return pl;
 }
 
-// Which kernel runs: 0 = one CTA per unit (cta_group::1, the default: measured faster on
-// B200), 1 = a CTA pair per unit (cta_group::2). Set by glsdm_score_topk_variant() or by
-// GLSDM_SCORE_TOPK_PAIR=1 in the environment.
-int g_variant = -1;
-
-bool use_pair() {
-  if (g_variant < 0) {
-    const char* env = getenv("GLSDM_SCORE_TOPK_PAIR");
-    g_variant = (env != nullptr && env[0] == '1') ? 1 : 0;
-  }
-  return g_variant == 1;
-}
-
-int sm_count() {
+int sm_count_cached() {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -463,22 +461,46 @@ int sm_count() {
   return sms;
 }
 
+// Which kernel runs: 0 = one CTA per 256 rows, key tiles of 128 slots (128x128x16 MMAs);
+// 1 = a CTA pair per 256 rows (cta_group::2); 2 = one CTA per 128 rows, key tiles of 256
+// slots (128x256x16 MMAs). Set by glsdm_score_topk_variant() or GLSDM_SCORE_TOPK_VARIANT.
+constexpr int kDefaultVariant = 2;
+int g_variant = -1;
+
+int variant() {
+  if (g_variant < 0) {
+    const char* env = getenv("GLSDM_SCORE_TOPK_VARIANT");
+    g_variant = (env != nullptr && env[0] >= '0' && env[0] <= '2') ? env[0] - '0' : kDefaultVariant;
+  }
+  return g_variant;
+}
+
+bool use_pair() { return variant() == 1; }
+
+Plan plan_for(int64_t rows, int64_t slots, int width) {
+  switch (variant()) {
+    case 1: return make_plan(rows, slots, sm_count_cached() / 2, width, kPairTileCols);
+    case 2: return make_plan(rows, slots, sm_count_cached(), width, kWideTileCols, kBlockRows);
+    default: return make_plan(rows, slots, sm_count_cached(), width);
+  }
+}
+
+
 }  // namespace
 }  // namespace glsdm
 
 using namespace glsdm;
 
-extern "C" int glsdm_score_topk_variant(int pair) {
-  const int before = use_pair() ? 1 : 0;
-  if (pair == 0 || pair == 1) g_variant = pair;
+extern "C" int glsdm_score_topk_variant(int which) {
+  const int before = variant();
+  if (which >= 0 && which <= 2) g_variant = which;
   return before;
 }
 
 extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;
-  const Plan pl = use_pair() ? make_plan(rows, slots, sm_count() / 2, width, kPairTileCols)
-                             : make_plan(rows, slots, sm_count(), width);
+  const Plan pl = plan_for(rows, slots, width);
   if (pl.splits <= 1) return 256;
   return static_cast<size_t>(pl.splits) * rows * width * 8 + 512;
 }
@@ -502,9 +524,10 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   if (width > 32 || col_base + slots > 0x7fffffffll || slots > kMaxSlotsPerCall) return GLSDM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
-  const int sms = sm_count();
+  const int sms = sm_count_cached();
   const bool pair = use_pair();
-  const Plan pl = pair ? make_plan(rows, slots, sms / 2, width, kPairTileCols) : make_plan(rows, slots, sms, width);
+  const bool wide = variant() == 2;
+  const Plan pl = plan_for(rows, slots, width);
   Params p;
   p.rows = rows;
   p.slots = slots;
@@ -526,7 +549,8 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
     p.out_slot = out_slot;
   }
   CUtensorMap map_q, map_k;
-  if (!make_map(&map_q, queries, rows, dk, query_pitch) || !make_map(&map_k, keys, slots, dk, key_pitch)) {
+  if (!make_map(&map_q, queries, rows, dk, query_pitch) ||
+      !make_map(&map_k, keys, slots, dk, key_pitch, wide ? kWideTileCols : kBlockRows)) {
     note_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
     return GLSDM_ERR_CUDA;
   }
@@ -555,6 +579,18 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
       GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          PairLayout<1>::total()), "score_topk pair shared memory");
       GLSDM_CUDA_OK(cudaLaunchKernelEx(&config, score_topk_pair_kernel<1>, map_q, map_k, p), "score_topk pair launch");
+    }
+  } else if (wide) {
+    if (dk == 128) {
+      const int smem = WideLayout<2>::total();
+      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                    "score_topk shared memory");
+      score_topk_wide_kernel<2><<<grid, kWideThreads, smem, stream>>>(map_q, map_k, p);
+    } else {
+      const int smem = WideLayout<1>::total();
+      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                    "score_topk shared memory");
+      score_topk_wide_kernel<1><<<grid, kWideThreads, smem, stream>>>(map_q, map_k, p);
     }
   } else if (dk == 128) {
     const int smem = Layout<2>::total(width);

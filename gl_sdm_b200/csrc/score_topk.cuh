@@ -143,14 +143,20 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-__device__ __forceinline__ float max_of_32(const uint32_t* r) {
-  float m[10];
+// m[j] = largest of columns 3j..3j+2 for j < 10, m[10] = larger of columns 30 and 31; returns
+// the largest of all 32. The group maxima let the rare path look only at groups that matter.
+__device__ __forceinline__ float max_of_32(const uint32_t* r, float (&m)[11]) {
 #pragma unroll
   for (int j = 0; j < 10; ++j)
     m[j] = max3(__uint_as_float(r[3 * j]), __uint_as_float(r[3 * j + 1]), __uint_as_float(r[3 * j + 2]));
+  m[10] = fmaxf(__uint_as_float(r[30]), __uint_as_float(r[31]));
   const float a = max3(m[0], m[1], m[2]), b = max3(m[3], m[4], m[5]), c = max3(m[6], m[7], m[8]);
-  const float d = max3(m[9], __uint_as_float(r[30]), __uint_as_float(r[31]));
-  return fmaxf(max3(a, b, c), d);
+  return fmaxf(max3(a, b, c), fmaxf(m[9], m[10]));
+}
+
+__device__ __forceinline__ float max_of_32(const uint32_t* r) {
+  float groups[11];
+  return max_of_32(r, groups);
 }
 
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

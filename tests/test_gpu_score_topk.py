@@ -54,9 +54,10 @@ def _check(q, keys, width, got_score, got_slot, col_base=0):
     return near_tie_rows
 
 
-@pytest.fixture(params=[0, 1], ids=["one-cta", "cta-pair"])
+@pytest.fixture(params=[0, 1, 2], ids=["one-cta", "cta-pair", "wide-tile"])
 def variant(native, request):
-    """Run a test under both kernels behind glsdm_score_topk (cta_group::1 and cta_group::2)."""
+    """Run a test under every kernel behind glsdm_score_topk: 128x128x16 MMAs over 256 rows,
+    the cta_group::2 pair, and 128x256x16 MMAs over 128 rows."""
     lib = native.library()
     before = lib.glsdm_score_topk_variant(request.param)
     yield request.param
