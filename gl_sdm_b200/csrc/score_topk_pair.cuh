@@ -5,7 +5,7 @@
 // That halves the shared-memory operand traffic per MMA, which is what limits the single-CTA
 // kernel (128x128x16 MMAs stream 128 B/clk). Accumulators: 128 lanes x 256 columns x 2
 // buffers of each CTA's tensor memory. Scanning, queues and inserters are as in the
-// single-CTA kernel, per CTA, over 128 rows.
+// wide-tile kernel, per CTA, over 128 rows (8 scanner warps, 4 inserter warps).
 //
 // Cross-CTA signalling: both CTAs' TMA loads complete transactions on the LEADER's full
 // barriers; the leader's commits are multicast to the barrier at the same offset in both CTAs
@@ -21,7 +21,7 @@ namespace dense {
 constexpr int kPairTileCols = 256;               // slots per key tile of the pair (MMA N)
 constexpr int kPairStages = 4;
 constexpr int kPairScanWarps = 8;                // 4 lane quarters x 2 column halves
-constexpr int kPairInsertWarps = 2;              // 64 rows each
+constexpr int kPairInsertWarps = 4;              // one per lane quarter (32 rows), fed by its two scanner warps
 constexpr int kPairThreads = 32 * (2 + kPairScanWarps + kPairInsertWarps);
 constexpr uint32_t kPairInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kPairTileCols >> 3) << 17) |
                                     ((256 >> 4) << 24);
@@ -220,9 +220,9 @@ score_topk_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int quarter = warp & 3;               // tensor-memory lane quarter this warp may read
     const int col_half = (warp - 2) >> 2;       // which 128 of the tile's 256 columns
     const int row = quarter * 32 + lane;        // row of this CTA's 128
-    Queue* q = queues + (row >> 6);
+    Queue* q = queues + quarter;
     volatile float* my_floor = floors + row;
-    const uint32_t row_tag = static_cast<uint32_t>(row & 63) << 24;
+    const uint32_t row_tag = static_cast<uint32_t>(lane) << 24;
     const uint32_t leader_empty[2] = {map_to_cta(smem_u32(&bars->acc_empty[0]), 0),
                                       map_to_cta(smem_u32(&bars->acc_empty[1]), 0)};
     uint32_t acc_phase[2] = {0, 0};
@@ -284,16 +284,15 @@ score_topk_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else {
     // ---------------------------------------------------------------- inserters
-    const int iw = warp - 2 - kPairScanWarps;   // rows [64*iw, 64*iw + 64) of this CTA
+    const int iw = warp - 2 - kPairScanWarps;   // rows [32*iw, 32*iw + 32) of this CTA: lane quarter iw
     Queue* q = queues + iw;
-    uint64_t* lists = all_lists + static_cast<size_t>(iw) * 64 * 32;
-    float* floor_s = floors + iw * 64;
+    uint64_t* lists = all_lists + static_cast<size_t>(iw) * 32 * 32;
+    float* floor_s = floors + iw * 32;
     const int K = p.width;
     uint32_t head = 0, units_done = 0;
     bool ok = true;
-    for (int r = 0; r < 64; ++r) lists[r * 32 + lane] = 0;
+    for (int r = 0; r < 32; ++r) lists[r * 32 + lane] = 0;
     floor_s[lane] = -INFINITY;
-    floor_s[32 + lane] = -INFINITY;
     __syncwarp();
     for (int unit = cluster_id; unit < units && ok; unit += clusters) {
       const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
@@ -305,15 +304,15 @@ score_topk_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (count == 0) {
           const uint32_t finished = *reinterpret_cast<volatile uint32_t*>(&q->done);
           const uint32_t tail = *reinterpret_cast<volatile uint32_t*>(&q->tail);
-          // four scanner warps feed a queue: two lane quarters x two column halves
-          if (finished == 4u * (units_done + 1u) && tail == head) break;
+          // two scanner warps feed a queue: the two column halves of this lane quarter
+          if (finished == 2u * (units_done + 1u) && tail == head) break;
           if (++idle >= kSpinLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
           continue;
         }
         idle = 0;
         for (int j = 0; j < count; ++j) {
           const uint64_t entry = shfl_u64(e, j);
-          const int row = static_cast<int>(entry >> 24) & 63;
+          const int row = static_cast<int>(entry >> 24) & 31;
           const uint64_t key = (entry & 0xffffffff00000000ull) | (entry & 0xffffffull);
           uint64_t* row_list = lists + row * 32;
           const uint64_t cur = row_list[lane];
@@ -335,8 +334,8 @@ score_topk_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (!ok) break;
       __syncwarp();
-      for (int r = 0; r < 64; ++r) {
-        const int64_t row = static_cast<int64_t>(pair) * kUnitRows + static_cast<int64_t>(rank) * kBlockRows + iw * 64 + r;
+      for (int r = 0; r < 32; ++r) {
+        const int64_t row = static_cast<int64_t>(pair) * kUnitRows + static_cast<int64_t>(rank) * kBlockRows + iw * 32 + r;
         const uint64_t e = lists[r * 32 + lane];
         if (row < p.rows && lane < K) {
           const int64_t at = (static_cast<int64_t>(split) * p.rows + row) * K + lane;
@@ -346,7 +345,6 @@ score_topk_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         lists[r * 32 + lane] = 0;
       }
       floor_s[lane] = -INFINITY;
-      floor_s[32 + lane] = -INFINITY;
       __threadfence_block();
       __syncwarp();
       ++units_done;
