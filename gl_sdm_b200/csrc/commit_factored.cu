@@ -56,7 +56,7 @@ struct EntryArgs {
   const float* error;       // per block: [block_rows, dim] error rows then [block_rows] decay-1
   const float* mass;        // per token or null
   const uint32_t* offsets;  // first entry of every row, or null: entry = row * width + route
-  int64_t rows, block_rows, route_stride, error_stride, tokens;
+  int64_t rows, block_rows, route_stride, error_stride, tokens, sequences;
   int64_t chunk_offset, key_stride;
   int width, num_layers, layer_index;
 };
@@ -92,14 +92,16 @@ factored_entries_kernel(BankView bank, EntryArgs a, FactoredScratch out) {
     out.keys[at] = (head * bank.slots + slot) * a.key_stride + position * a.num_layers + a.layer_index;
     out.described[at] = d;
   } else if (lane < a.width) {
-    // Dense numbering: every route has an entry; a slot outside the bank takes the key one
-    // past the last address, sorts last, and is dropped (and reported) by the reducer through
-    // its out-of-range address.
-    const int64_t at = row * a.width + lane;
-    const int64_t position = a.chunk_offset + token % a.tokens;
+    // Dense numbering: every route has an entry. Entries are numbered token-major
+    // ((position, sequence, head), route): the canonical order inside an address is
+    // (position, layer, arrival = sequence), so a stable sort by the ADDRESS alone already
+    // yields it and the key needs no position bits (3 radix passes instead of 5 at 16M slots).
+    // A slot outside the bank takes the address one past the last, sorts last, and is dropped
+    // (and reported) by the reducer through its out-of-range row.
+    const int64_t sequence = token / a.tokens, position = token % a.tokens;
+    const int64_t at = (((position * a.sequences + sequence) * bank.heads + head) * a.width) + lane;
     out.addresses[at] = owned ? head * bank.part_stride_rows + (slot - bank.slot_lo) : -1;
-    out.keys[at] = owned ? (head * bank.slots + slot) * a.key_stride + position * a.num_layers + a.layer_index
-                         : static_cast<int64_t>(bank.heads) * bank.slots * a.key_stride;
+    out.keys[at] = owned ? head * bank.slots + slot : static_cast<int64_t>(bank.heads) * bank.slots;
     out.described[at] = d;
   }
 }
@@ -409,7 +411,8 @@ extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* inde
   if (key_bits < 0 || key_bits > 64) return GLSDM_ERR_ARGUMENT;
   if (width > 32 || bank->banks != 1) return GLSDM_ERR_UNSUPPORTED;
   if (entries > 0xfffffff0ll) return GLSDM_ERR_LIMIT;
-  if (offsets == nullptr && entries != rows * width) return GLSDM_ERR_ARGUMENT;
+  if (offsets == nullptr && (entries != rows * width || rows % (static_cast<int64_t>(bank->heads) * tokens) != 0))
+    return GLSDM_ERR_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GLSDM_ERR_ARGUMENT;
   const BankView v = make_view(*bank);
   // Descriptors address error rows with 32 bits.
@@ -423,12 +426,15 @@ extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* inde
   EntryArgs e;
   e.index = index; e.weights = weights; e.error = error; e.mass = mass; e.offsets = offsets;
   e.rows = rows; e.block_rows = block_rows; e.route_stride = route_stride; e.error_stride = error_stride;
-  e.tokens = tokens; e.chunk_offset = chunk_offset; e.key_stride = chunk_size * num_layers;
+  e.tokens = tokens; e.sequences = rows / (static_cast<int64_t>(v.heads) * tokens); e.chunk_offset = chunk_offset; e.key_stride = chunk_size * num_layers;
   e.width = width; e.num_layers = num_layers; e.layer_index = layer_index;
   factored_entries_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
   GLSDM_CUDA_OK(cudaGetLastError(), "factored entries launch");
-  // With dense numbering a slot outside the bank carries the key one past the largest valid one.
-  const int passes = sort_passes(offsets == nullptr && key_bits > 0 && key_bits < 64 ? key_bits + 1 : key_bits);
+  // Dense numbering sorts by address alone (one value past the last address marks a slot
+  // outside the bank).
+  int address_bits = 1;
+  while ((static_cast<int64_t>(v.heads) * v.slots) >> address_bits) ++address_bits;
+  const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
   if (int s = run_sort(w, f.keys, entries, passes, stream)) return s;
   gather_factored_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, f, entries);
   GLSDM_CUDA_OK(cudaGetLastError(), "factored gather launch");

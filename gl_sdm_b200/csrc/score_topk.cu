@@ -422,6 +422,8 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int dk, int64_t 
 
 struct Plan {
   int unit_pairs, tiles_total, splits, tiles_per_split;
+  int tail_blocks = 0, tail_splits = 0, tail_tiles_per_split = 0;   // see Params
+  int64_t tail_rows = 0;
 };
 
 // Pick the number of slot-range splits. Every split restarts its rows' lists from nothing and
@@ -447,6 +449,33 @@ Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = 
   pl.splits = best;
   pl.tiles_per_split = (pl.tiles_total + best - 1) / best;
   pl.splits = (pl.tiles_total + pl.tiles_per_split - 1) / pl.tiles_per_split;
+  return pl;
+}
+
+// The wide-tile kernel may also keep one split for the row blocks that fill whole waves of
+// CTAs and cut only the blocks of the last, partly filled wave (their lists are merged
+// afterwards): time = full waves * (tiles + restart) + (tiles / tail splits + restart).
+Plan make_plan_with_tail(int64_t rows, int64_t slots, int sms, int width, int tile_cols, int unit_rows) {
+  Plan pl = make_plan(rows, slots, sms, width, tile_cols, unit_rows);
+  const int blocks = pl.unit_pairs;
+  const int full = blocks / sms * sms, tail = blocks - full;
+  if (full == 0 || tail == 0) return pl;
+  const int64_t restart = 220ll * width;
+  int parts = sms / tail;
+  while (parts > 1 && (pl.tiles_total + parts - 1) / parts < 1024) --parts;
+  if (parts < 2) return pl;
+  const int64_t per = (pl.tiles_total + parts - 1) / parts;
+  const int64_t uniform_units = static_cast<int64_t>(blocks) * pl.splits;
+  const int64_t uniform_cost = (uniform_units + sms - 1) / sms * (pl.tiles_per_split + restart);
+  const int64_t tail_cost = static_cast<int64_t>(full / sms) * (pl.tiles_total + restart) + per + restart;
+  if (tail_cost * 100 >= uniform_cost * 98) return pl;
+  pl.unit_pairs = full;
+  pl.splits = 1;
+  pl.tiles_per_split = pl.tiles_total;
+  pl.tail_blocks = tail;
+  pl.tail_tiles_per_split = static_cast<int>(per);
+  pl.tail_splits = static_cast<int>((pl.tiles_total + per - 1) / per);
+  pl.tail_rows = rows - static_cast<int64_t>(full) * unit_rows;
   return pl;
 }
 
@@ -480,7 +509,7 @@ bool use_pair() { return variant() == 1; }
 Plan plan_for(int64_t rows, int64_t slots, int width) {
   switch (variant()) {
     case 1: return make_plan(rows, slots, sm_count_cached() / 2, width, kPairTileCols);
-    case 2: return make_plan(rows, slots, sm_count_cached(), width, kWideTileCols, kBlockRows);
+    case 2: return make_plan_with_tail(rows, slots, sm_count_cached(), width, kWideTileCols, kBlockRows);
     default: return make_plan(rows, slots, sm_count_cached(), width);
   }
 }
@@ -501,6 +530,7 @@ extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, 
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;
   const Plan pl = plan_for(rows, slots, width);
+  if (pl.tail_blocks > 0) return static_cast<size_t>(pl.tail_splits) * pl.tail_rows * width * 8 + 512;
   if (pl.splits <= 1) return 256;
   return static_cast<size_t>(pl.splits) * rows * width * 8 + 512;
 }
@@ -539,7 +569,19 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   p.tiles_total = pl.tiles_total;
   p.unit_pairs = pl.unit_pairs;
   p.device_status = device_status;
-  if (pl.splits > 1) {
+  p.tail_blocks = pl.tail_blocks;
+  p.tail_splits = pl.tail_splits;
+  p.tail_tiles_per_split = pl.tail_tiles_per_split;
+  p.tail_score = nullptr;
+  p.tail_slot = nullptr;
+  if (pl.tail_blocks > 0) {
+    const size_t cells = static_cast<size_t>(pl.tail_splits) * pl.tail_rows * width;
+    if (workspace == nullptr || workspace_bytes < cells * 8) return GLSDM_ERR_WORKSPACE;
+    p.tail_score = static_cast<float*>(workspace);
+    p.tail_slot = reinterpret_cast<int32_t*>(static_cast<float*>(workspace) + cells);
+    p.out_score = out_score;
+    p.out_slot = out_slot;
+  } else if (pl.splits > 1) {
     const size_t need = static_cast<size_t>(pl.splits) * rows * width * 8;
     if (workspace == nullptr || workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
     p.out_score = static_cast<float*>(workspace);
@@ -554,7 +596,7 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
     note_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
     return GLSDM_ERR_CUDA;
   }
-  const int units = pl.unit_pairs * pl.splits;
+  const int units = pl.unit_pairs * pl.splits + pl.tail_blocks * pl.tail_splits;
   const int grid = units < sms ? units : sms;
   if (pair) {
     const int clusters = units < sms / 2 ? units : sms / 2;
@@ -605,7 +647,14 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   }
   GLSDM_CUDA_OK(cudaGetLastError(), "score_topk launch");
   count_launches(1);
-  if (pl.splits > 1) {
+  if (pl.tail_blocks > 0) {
+    const int64_t first = rows - pl.tail_rows;
+    split_merge_kernel<<<blocks_for(pl.tail_rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+        p.tail_score, p.tail_slot, pl.tail_splits, pl.tail_rows, width, out_score + first * width,
+        out_slot + first * width);
+    GLSDM_CUDA_OK(cudaGetLastError(), "score_topk tail merge launch");
+    count_launches(1);
+  } else if (pl.splits > 1) {
     split_merge_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
         p.out_score, p.out_slot, pl.splits, rows, width, out_score, out_slot);
     GLSDM_CUDA_OK(cudaGetLastError(), "score_topk merge launch");

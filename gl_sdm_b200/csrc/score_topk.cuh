@@ -34,11 +34,51 @@ struct Params {
   int splits;
   int tiles_per_split;
   int tiles_total;
-  int unit_pairs;       // ceil(rows / 256)
+  int unit_pairs;       // row blocks that take the uniform splits (all of them unless there is a tail)
   float* out_score;     // [splits][rows][width] (or the final output when splits == 1)
   int32_t* out_slot;
   uint32_t* device_status;
+  // Tail (wide-tile kernel only): the row blocks left over after the last full wave of CTAs
+  // have their slot range cut in tail_splits parts, so the last wave is short instead of
+  // mostly idle. Their partial lists go to tail_score/tail_slot [part][tail row][width].
+  int tail_blocks;
+  int tail_splits;
+  int tail_tiles_per_split;
+  float* tail_score;
+  int32_t* tail_slot;
 };
+
+// One unit of work: a block of query rows against the key tiles [t0, t1); `part` numbers the
+// pieces of the block's slot range, `tail` says which output the piece belongs to.
+struct UnitSpan {
+  int block, part, t0, t1;
+  bool tail;
+};
+
+__device__ __forceinline__ int unit_count(const Params& p) {
+  return p.unit_pairs * p.splits + p.tail_blocks * p.tail_splits;
+}
+
+// Units are numbered part-major, so the CTAs that run at the same time stream the same keys.
+__device__ __forceinline__ UnitSpan unit_span(const Params& p, int unit) {
+  UnitSpan u;
+  const int uniform = p.unit_pairs * p.splits;
+  if (unit < uniform) {
+    u.tail = false;
+    u.part = unit / p.unit_pairs;
+    u.block = unit % p.unit_pairs;
+    u.t0 = u.part * p.tiles_per_split;
+    u.t1 = min(u.t0 + p.tiles_per_split, p.tiles_total);
+  } else {
+    const int j = unit - uniform;
+    u.tail = true;
+    u.part = j / p.tail_blocks;
+    u.block = p.unit_pairs + j % p.tail_blocks;
+    u.t0 = u.part * p.tail_tiles_per_split;
+    u.t1 = min(u.t0 + p.tail_tiles_per_split, p.tiles_total);
+  }
+  return u;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

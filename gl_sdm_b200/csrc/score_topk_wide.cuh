@@ -97,7 +97,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  const int units = p.unit_pairs * p.splits;
+  const int units = unit_count(p);
   const int first_unit = blockIdx.x, unit_stride = gridDim.x;
   constexpr uint32_t kQueryBytes = KB * kSubTileBytes;          // 128 query rows
   constexpr uint32_t kKeyBytes = KB * kWideSubTileBytes;        // 256 key rows
@@ -109,7 +109,8 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       uint32_t stage = 0, b_phase = 0, a_phase = 0;
       bool ok = true;
       for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
-        const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
+        const UnitSpan span = unit_span(p, unit);
+        const int pair = span.block;
         if (unit != first_unit) {
           ok = mbar_wait(&bars->a_empty, a_phase, abort_flag);
           a_phase ^= 1u;
@@ -118,8 +119,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_expect_tx(&bars->a_full, kQueryBytes);
         for (int kb = 0; kb < KB; ++kb)
           tma_load_2d(smem_a + kb * kSubTileBytes, &map_q, kb * kAtomK, pair * kBlockRows, &bars->a_full);
-        const int t0 = split * p.tiles_per_split;
-        const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+        const int t0 = span.t0, t1 = span.t1;
         for (int t = t0; t < t1; ++t) {
           ok = mbar_wait(&bars->b_empty[stage], b_phase ^ 1u, abort_flag);
           if (!ok) break;
@@ -141,12 +141,11 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool ok = true;
       int done = 0;
       for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
-        const int split = unit / p.unit_pairs;
+        const UnitSpan span = unit_span(p, unit);
         ok = mbar_wait(&bars->a_full, a_phase, abort_flag);
         a_phase ^= 1u;
         if (!ok) break;
-        const int t0 = split * p.tiles_per_split;
-        const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+        const int t0 = span.t0, t1 = span.t1;
         for (int t = t0; t < t1; ++t, ++tile_counter) {
           const uint32_t buf = tile_counter & 1u;
           ok = mbar_wait(&bars->b_full[stage], b_phase, abort_flag);
@@ -183,12 +182,11 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t tile_counter = 0, unit_local = 0;
     bool ok = true;
     for (int unit = first_unit; unit < units && ok; unit += unit_stride, ++unit_local) {
-      const int split = unit / p.unit_pairs;
+      const UnitSpan span = unit_span(p, unit);
       for (uint32_t spin = 0; *reinterpret_cast<volatile uint32_t*>(&q->epoch) < unit_local; ++spin)
         if (spin >= kSpinLimit || ((spin & 1023u) == 1023u && *abort_flag)) { *abort_flag = 1; ok = false; break; }
       if (!__all_sync(kFullMask, ok)) { ok = false; break; }
-      const int t0 = split * p.tiles_per_split;
-      const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+      const int t0 = span.t0, t1 = span.t1;
       for (int t = t0; t < t1 && ok; ++t, ++tile_counter) {
         const uint32_t buf = tile_counter & 1u;
         ok = mbar_wait(&bars->acc_full[buf], acc_phase[buf], abort_flag);
@@ -261,7 +259,8 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     floor_s[lane] = -INFINITY;
     __syncwarp();
     for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
-      const int split = unit / p.unit_pairs, pair = unit % p.unit_pairs;
+      const UnitSpan span = unit_span(p, unit);
+      const int pair = span.block;
       uint32_t idle = 0;
       for (;;) {
         const uint64_t e = *reinterpret_cast<volatile uint64_t*>(&q->slot[(head + lane) & (kQueueSlots - 1)]);
@@ -304,9 +303,19 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + r;
         const uint64_t e = lists[r * 32 + lane];
         if (row < p.rows && lane < K) {
-          const int64_t at = (static_cast<int64_t>(split) * p.rows + row) * K + lane;
-          p.out_score[at] = e ? from_orderable_bits(static_cast<uint32_t>(e >> 32)) : -INFINITY;
-          p.out_slot[at] = e ? static_cast<int32_t>(p.col_base + static_cast<int64_t>(e & 0xffffffull)) : -1;
+          const float score = e ? from_orderable_bits(static_cast<uint32_t>(e >> 32)) : -INFINITY;
+          const int32_t slot = e ? static_cast<int32_t>(p.col_base + static_cast<int64_t>(e & 0xffffffull)) : -1;
+          if (span.tail) {
+            const int64_t tail_rows = p.rows - static_cast<int64_t>(p.unit_pairs) * kBlockRows;
+            const int64_t at = (static_cast<int64_t>(span.part) * tail_rows +
+                                (row - static_cast<int64_t>(p.unit_pairs) * kBlockRows)) * K + lane;
+            p.tail_score[at] = score;
+            p.tail_slot[at] = slot;
+          } else {
+            const int64_t at = (static_cast<int64_t>(span.part) * p.rows + row) * K + lane;
+            p.out_score[at] = score;
+            p.out_slot[at] = slot;
+          }
         }
         lists[r * 32 + lane] = 0;
       }

@@ -41,28 +41,43 @@ __global__ void owned_count_kernel(const int32_t* __restrict__ index, int64_t ro
 }
 
 // In-place exclusive scan of counts[rows] by one block; total written to counts[rows].
+// 1024 counts per round, read and written coalesced: a shuffle scan inside each warp, one
+// more over the 32 warp totals, and a running carry from round to round.
 __global__ void __launch_bounds__(1024) offsets_scan_kernel(uint32_t* counts, int64_t rows) {
-  __shared__ uint32_t sums[1024];
-  const int64_t per = (rows + 1023) / 1024;
-  const int64_t lo = per * threadIdx.x;
-  const int64_t hi = lo + per < rows ? lo + per : rows;
-  uint32_t total = 0;
-  for (int64_t i = lo; i < hi; ++i) total += counts[i];
-  sums[threadIdx.x] = total;
+  __shared__ uint32_t warp_total[32];
+  __shared__ uint32_t carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {
-    const uint32_t add = threadIdx.x >= off ? sums[threadIdx.x - off] : 0u;
+  for (int64_t base = 0; base < rows; base += 1024) {
+    const int64_t i = base + threadIdx.x;
+    const uint32_t c = i < rows ? counts[i] : 0u;
+    uint32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(kFullMask, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_total[warp] = incl;
     __syncthreads();
-    sums[threadIdx.x] += add;
+    if (warp == 0) {
+      const uint32_t t = warp_total[lane];
+      uint32_t run = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t n = __shfl_up_sync(kFullMask, run, o);
+        if (lane >= o) run += n;
+      }
+      warp_total[lane] = run - t;          // exclusive offset of every warp within the round
+    }
+    __syncthreads();
+    const uint32_t before = carry + warp_total[warp] + incl - c;
+    if (i < rows) counts[i] = before;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = before + c;
     __syncthreads();
   }
-  uint32_t run = sums[threadIdx.x] - total;
-  for (int64_t i = lo; i < hi; ++i) {
-    const uint32_t c = counts[i];
-    counts[i] = run;
-    run += c;
-  }
-  if (threadIdx.x == 1023) counts[rows] = sums[1023];
+  if (threadIdx.x == 0) counts[rows] = carry;
 }
 
 // One warp per routing row: expand the owned routes into delta rows at the row's offset.

@@ -184,8 +184,13 @@ class ShardedBankOperator:
             dist.all_gather_into_tensor(errors, packed, group=self.group)
         else:
             errors = packed
-        offsets = k.shard_offsets(routes, plan["write_index_at"], R * n, n, stride, K, self.slot_lo, self.slot_hi)
-        entries = int(offsets[-1].item())
+        if R == 1 and self.factored:
+            # one shard owns every route: entries are numbered row * K + route, nothing to count,
+            # no host synchronisation in the epoch
+            offsets, entries = None, n * K
+        else:
+            offsets = k.shard_offsets(routes, plan["write_index_at"], R * n, n, stride, K, self.slot_lo, self.slot_hi)
+            entries = int(offsets[-1].item())
         if entries and self.factored:
             self._mark("commit")
             k.commit_factored(self.shard, self.slot_lo, self.slots, routes, plan["write_index_at"],

@@ -260,7 +260,8 @@ int glsdm_overlay_read(const glsdm_bank* bank, const void* index, int index_i64,
  *                 error_stride floats per block
  *   offsets       glsdm_shard_offsets of the same routes, entries = its total; or NULL for an
  *                 unsharded bank: every route is an entry, entries = rows * width (no host
- *                 synchronisation needed)
+ *                 synchronisation needed); rows must then be whole sequences of `tokens`
+ *                 tokens x heads (rows laid out [sequence, token, head])
  *   workspace     glsdm_commit_factored_workspace_bytes(entries, dim), 256-byte aligned */
 size_t glsdm_commit_factored_workspace_bytes(int64_t entries, int32_t dim);
 int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* index, const float* weights,

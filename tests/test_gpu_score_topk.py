@@ -137,3 +137,27 @@ def test_pk_gemm_select_matches_the_product_key_oracle(native, rows, half, width
         boundary = np.sort((left[r][:, None] + right[r][None, :]).ravel())[-width]
         for s in set(got[r]) ^ set(want_index[r]):
             assert abs(left[r, s // half] + right[r, s % half] - boundary) <= 2 * EPS
+
+
+def test_tail_split_units_agree_with_the_uniform_plan(native):
+    """More row blocks than SMs and a long slot range: the wide-tile kernel keeps one split for
+    the blocks that fill whole waves and cuts only the last wave's blocks in parts. Its routes
+    must be those of the 128x128 kernel (pinned to the oracle above), row for row."""
+    lib = native.library()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows, slots, width = (sms + 20) * 128 - 37, 1 << 20, 32
+    g = torch.Generator(device=DEV).manual_seed(77)
+    q = torch.randn(rows, 128, generator=g, device=DEV).bfloat16()
+    k = torch.randn(slots, 128, generator=g, device=DEV)
+    k = (k / k.norm(dim=1, keepdim=True)).bfloat16()
+    before = lib.glsdm_score_topk_variant(0)
+    try:
+        want_score, want_slot = native.score_topk(q, k, width, col_base=5)
+        lib.glsdm_score_topk_variant(2)
+        got_score, got_slot = native.score_topk(q, k, width, col_base=5)
+    finally:
+        lib.glsdm_score_topk_variant(before)
+    native.raise_on_device_status(DEV)
+    order_w, order_g = torch.sort(want_slot, dim=-1), torch.sort(got_slot, dim=-1)
+    assert torch.equal(order_w.values, order_g.values)
+    assert torch.equal(torch.gather(want_score, -1, order_w.indices), torch.gather(got_score, -1, order_g.indices))
