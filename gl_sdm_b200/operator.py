@@ -104,10 +104,13 @@ class SharedBankOperator:
 class GraphedEpoch:
     """One epoch of an unsharded operator, captured once as a CUDA graph and replayed.
 
-    Small epochs (a few thousand tokens) finish on the GPU faster than the host can issue
-    their ~25 kernel launches; replaying a captured graph removes that cost. Shapes are fixed
-    at construction; every call copies its inputs into the captured buffers and returns the
-    captured output tensor (valid until the next call). Works for operators whose epoch makes
+    For callers that are bound by the cost of issuing an epoch's ~25 kernel launches from the
+    host (a serving loop doing other Python work between epochs). Shapes are fixed at
+    construction; every call copies its inputs into the captured buffers and returns the
+    captured output tensor (valid until the next call). Measured on B200 with the benchmark's
+    back-to-back epochs the replay is NOT faster than eager launches (c5: 173 against 162 us
+    per 2,048-token epoch; the input copies cost more than the launches), so the benchmark
+    does not use it. Works for operators whose epoch makes
     no host synchronisation: ``SharedBankOperator`` and a single-rank ``ShardedBankOperator``
     with the factored commit.
     """
@@ -124,11 +127,16 @@ class GraphedEpoch:
         bank.copy_(saved)
         del saved
         self.graph = torch.cuda.CUDAGraph()
+        counter = _native.library().glsdm_kernel_launches
+        before = counter()
         with torch.cuda.graph(self.graph):
             self.output = epoch_fn(*self.inputs)
+        self.launches_per_replay = int(counter() - before)   # kernels of this library inside the graph
+        self.replays = 0
 
     def __call__(self, *inputs):
         for mine, given in zip(self.inputs, inputs):
             mine.copy_(given)
         self.graph.replay()
+        self.replays += 1
         return self.output
