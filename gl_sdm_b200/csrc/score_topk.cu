@@ -431,11 +431,12 @@ struct Plan {
 // roughly 220*k key-tile times per unit), so the model is
 //   time(s) = waves(s) * (tiles per split + 220*k),  waves = ceil(row pairs * s / SMs),
 // minimised over s with at least 1024 key tiles per split; ties prefer fewer splits.
-Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = kTileCols, int unit_rows = kUnitRows) {
+Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = kTileCols, int unit_rows = kUnitRows,
+               int restart_per_width = 220) {
   Plan pl;
   pl.unit_pairs = static_cast<int>((rows + unit_rows - 1) / unit_rows);
   pl.tiles_total = static_cast<int>((slots + tile_cols - 1) / tile_cols);
-  const int64_t restart = 220ll * width;
+  const int64_t restart = static_cast<int64_t>(restart_per_width) * width;
   int best = 1;
   int64_t best_cost = -1;
   for (int s = 1; s <= 64; ++s) {
@@ -452,15 +453,19 @@ Plan make_plan(int64_t rows, int64_t slots, int sms, int width, int tile_cols = 
   return pl;
 }
 
+// Start-up of a unit of the wide-tile kernel in key-tile times per route kept (one wave of
+// 128-row units over 512..16384 tiles of 256 slots, top-32: time = 1.05 us x tiles + start-up).
+constexpr int kWideRestartPerWidth = 47;
+
 // The wide-tile kernel may also keep one split for the row blocks that fill whole waves of
 // CTAs and cut only the blocks of the last, partly filled wave (their lists are merged
 // afterwards): time = full waves * (tiles + restart) + (tiles / tail splits + restart).
 Plan make_plan_with_tail(int64_t rows, int64_t slots, int sms, int width, int tile_cols, int unit_rows) {
-  Plan pl = make_plan(rows, slots, sms, width, tile_cols, unit_rows);
+  Plan pl = make_plan(rows, slots, sms, width, tile_cols, unit_rows, kWideRestartPerWidth);
   const int blocks = pl.unit_pairs;
   const int full = blocks / sms * sms, tail = blocks - full;
   if (full == 0 || tail == 0) return pl;
-  const int64_t restart = 220ll * width;
+  const int64_t restart = static_cast<int64_t>(kWideRestartPerWidth) * width;
   int parts = sms / tail;
   while (parts > 1 && (pl.tiles_total + parts - 1) / parts < 1024) --parts;
   if (parts < 2) return pl;

@@ -275,8 +275,9 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           continue;
         }
         idle = 0;
-        for (int j = 0; j < count; ++j) {
-          const uint64_t entry = shfl_u64(e, j);
+        // One insertion: the warp holds the row's list (lane j = entry j, best first), finds the
+        // key's place with a ballot and shifts the tail down by one lane.
+        auto insert_one = [&](uint64_t entry) {
           const int row = static_cast<int>(entry >> 24) & 31;
           const uint64_t key = (entry & 0xffffffff00000000ull) | (entry & 0xffffffull);
           uint64_t* row_list = lists + row * 32;
@@ -290,7 +291,48 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               *reinterpret_cast<volatile float*>(&floor_s[row]) =
                   ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
           }
+        };
+        // Entries of four different rows are independent: their list loads, ballots and
+        // stores are issued together, which hides the shared-memory and vote latencies that a
+        // single insertion spends waiting (the start of a unit is nothing but insertions).
+        int j = 0;
+        for (; j + 4 <= count; j += 4) {
+          uint64_t entry[4];
+          int row[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            entry[i] = shfl_u64(e, j + i);
+            row[i] = static_cast<int>(entry[i] >> 24) & 31;
+          }
+          const bool distinct = row[0] != row[1] && row[0] != row[2] && row[0] != row[3] && row[1] != row[2] &&
+                                row[1] != row[3] && row[2] != row[3];
+          if (!distinct) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) insert_one(entry[i]);
+            continue;
+          }
+          uint64_t key[4], cur[4];
+          int pos[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            key[i] = (entry[i] & 0xffffffff00000000ull) | (entry[i] & 0xffffffull);
+            cur[i] = lists[row[i] * 32 + lane];
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) pos[i] = __popc(__ballot_sync(kFullMask, cur[i] > key[i]));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint64_t up = __shfl_up_sync(kFullMask, cur[i], 1);
+            if (pos[i] < K) {
+              const uint64_t ne = lane < pos[i] ? cur[i] : (lane == pos[i] ? key[i] : up);
+              lists[row[i] * 32 + lane] = ne;
+              if (lane == K - 1)
+                *reinterpret_cast<volatile float*>(&floor_s[row[i]]) =
+                    ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+            }
+          }
         }
+        for (; j < count; ++j) insert_one(shfl_u64(e, j));
         if (lane < count) *reinterpret_cast<volatile uint64_t*>(&q->slot[(head + lane) & (kQueueSlots - 1)]) = 0;
         __threadfence_block();
         __syncwarp();
