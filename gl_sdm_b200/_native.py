@@ -68,6 +68,7 @@ SIGNATURES = {
     "glsdm_score_topk_pitched": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_pk_combine": (_i, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),
+    "glsdm_topk_merge_strided": (_i, [_p, _p, _i32, _i64, _i64, _i32, _p, _i, _p, _p]),
 }
 
 
@@ -533,6 +534,21 @@ def topk_merge(cand_score, cand_slot, index_dtype=torch.int64, out=None):
     _check(library().glsdm_topk_merge(_ptr(cand_score), _ptr(cand_slot), parts, rows, width, _ptr(index),
                                       int(index_dtype == torch.int64), _ptr(weights),
                                       _stream(cand_score.device)))
+    return index, weights
+
+
+def topk_merge_packed(packed, parts, rows, width, out):
+    """Merge candidates that arrive as one int32 buffer of `parts` blocks, each holding a
+    shard's scores [rows, width] (float32 bits) followed by its slots [rows, width]: the
+    receive buffer of a single all-gather. ``out`` = (index int32/int64, weights)."""
+    index, weights = out
+    require_cuda(packed, index, weights)
+    region = rows * width
+    if packed.numel() != parts * 2 * region or packed.dtype != torch.int32:
+        raise ValueError("packed candidates are parts x (scores, slots) x rows x width int32 words")
+    _check(library().glsdm_topk_merge_strided(_at(packed, 0), _at(packed, region), parts, 2 * region, rows, width,
+                                              _ptr(index), int(index.dtype == torch.int64), _ptr(weights),
+                                              _stream(packed.device)))
     return index, weights
 
 

@@ -139,22 +139,20 @@ class ShardedBankOperator:
         everyone = self._buffer("queries_all", R * 2 * n * dk, torch.bfloat16)
         self.dist.all_gather_into_tensor(everyone, send.view(-1), group=self.group)
         rows = R * 2 * n
-        mine = (self._buffer("cand_score", rows * K, torch.float32).view(rows, K),
-                self._buffer("cand_slot", rows * K, torch.int32).view(rows, K))
+        # this rank's candidates: scores then slots in one buffer, so that one all-gather moves both
+        mine = self._buffer("cand", 2 * rows * K, torch.int32)
         self._mark("score_topk")
-        k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo, out=mine)
+        k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo,
+                     out=(mine[:rows * K].view(torch.float32).view(rows, K), mine[rows * K:].view(rows, K)))
         self._mark("merge")
         if R > 1:
-            scores = self._buffer("cand_score_all", R * rows * K, torch.float32)
-            slots = self._buffer("cand_slot_all", R * rows * K, torch.int32)
-            self.dist.all_gather_into_tensor(scores, mine[0].view(-1), group=self.group)
-            self.dist.all_gather_into_tensor(slots, mine[1].view(-1), group=self.group)
-            scores, slots = scores.view(R, rows, K), slots.view(R, rows, K)
+            gathered = self._buffer("cand_all", R * 2 * rows * K, torch.int32)
+            self.dist.all_gather_into_tensor(gathered, mine, group=self.group)
         else:
-            scores, slots = mine[0].view(1, rows, K), mine[1].view(1, rows, K)
+            gathered = mine
         routes = self._buffer("routes_all", 2 * rows * K, torch.int32)
-        k.topk_merge(scores, slots, out=(routes[:rows * K].view(rows, K),
-                                         routes[rows * K:].view(torch.float32).view(rows, K)))
+        k.topk_merge_packed(gathered, R, rows, K, out=(routes[:rows * K].view(rows, K),
+                                                       routes[rows * K:].view(torch.float32).view(rows, K)))
         region = n * K
         return dict(routes=routes, stride=2 * region, read_weights_at=rows * K, write_index_at=region,
                     write_weights_at=rows * K + region)

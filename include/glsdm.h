@@ -334,6 +334,11 @@ int glsdm_pk_combine(const float* left_score, const int32_t* left_index, const f
 int glsdm_topk_merge(const float* cand_score, const int32_t* cand_slot, int32_t parts,
                      int64_t rows, int32_t width, void* out_index, int index_i64,
                      float* out_weights, glsdm_stream_t stream);
+/* The same with the parts' lists part_stride elements apart in both arrays (>= rows*width),
+ * e.g. the receive buffer of one all-gather that carries a rank's scores and slots together. */
+int glsdm_topk_merge_strided(const float* cand_score, const int32_t* cand_slot, int32_t parts,
+                             int64_t part_stride, int64_t rows, int32_t width, void* out_index,
+                             int index_i64, float* out_weights, glsdm_stream_t stream);
 
 #ifdef __cplusplus
 }
