@@ -169,11 +169,6 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-// One column, no wait: the caller issues several and then waits once (tmem_wait_loads).
-__device__ __forceinline__ void tmem_load1_async(uint32_t taddr, uint32_t& r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr));
-}
-
 __device__ __forceinline__ uint32_t tmem_load1(uint32_t taddr) {
   uint32_t r;
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr));

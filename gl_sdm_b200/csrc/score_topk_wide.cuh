@@ -229,26 +229,12 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t cols = __reduce_or_sync(kFullMask, mine);
             const uint32_t slot0 = static_cast<uint32_t>(col0) + first;
             while (cols && ok) {
-              // up to four columns are fetched from tensor memory behind one wait
-              int col[4];
-              uint32_t raw[4];
-#pragma unroll
-              for (int c4 = 0; c4 < 4; ++c4) {
-                col[c4] = cols ? __ffs(cols) - 1 : -1;
-                if (cols) cols &= cols - 1;
-                raw[c4] = 0;
-                if (col[c4] >= 0) tmem_load1_async(taddr + first + col[c4], raw[c4]);
-              }
-              tmem_wait_loads();
-#pragma unroll
-              for (int c4 = 0; c4 < 4; ++c4) {
-                if (col[c4] < 0 || !ok) continue;
-                const bool pass = (mine >> col[c4]) & 1u;
-                const unsigned m = __ballot_sync(kFullMask, pass);
-                ok = queue_push(q, m, pass,
-                                pack_key(orderable_bits(__uint_as_float(raw[c4])), row_tag | (slot0 + col[c4])), lane,
-                                abort_flag);
-              }
+              const int i = __ffs(cols) - 1;
+              cols &= cols - 1;
+              const float v = __uint_as_float(tmem_load1(taddr + first + i));
+              const bool pass = (mine >> i) & 1u;
+              const unsigned m = __ballot_sync(kFullMask, pass);
+              ok = queue_push(q, m, pass, pack_key(orderable_bits(v), row_tag | (slot0 + i)), lane, abort_flag);
             }
           }
         }
