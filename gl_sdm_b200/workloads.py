@@ -152,7 +152,7 @@ def make_epoch_inputs_dense(w, device, seed, sequences=None, tokens=None, keys=N
 
 
 def algorithmic_bytes(w, tokens, unique_fraction=1.0, layers=None, factored=False):
-    """Bytes each stage must move for `tokens` tokens (per-unit figures: see DESIGN.md):
+    """Bytes each stage must move for `tokens` tokens (per routing row: K routes, D value width, e bank element bytes, u unique-row fraction):
     query read K*D*e + 4*D plus 8*half of factor scores; proposal K*D*e + 8*half + target +
     K*(4*D+16) written; commit K*(4*D+16) read + u*K*2*D*e rows. With the factored commit no
     delta rows exist: the proposal stage ends at the error vector (4*(D+1) written), the commit

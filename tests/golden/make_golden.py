@@ -137,4 +137,4 @@ def main(reference_root, only=None):
 
 if __name__ == "__main__":
     # python make_golden.py [reference root] [routed case names to (re)write; default: everything]
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", set(sys.argv[2:]) or None)
+    main(sys.argv[1], set(sys.argv[2:]) or None)
