@@ -60,6 +60,8 @@ SIGNATURES = {
     "glsdm_commit_factored_workspace_bytes": (_sz, [_i64, _i32]),
     "glsdm_commit_factored": (_i, [_BANK, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i64, _i64,
                                    _i32, _i32, _i32, _p, _sz, _p, _p]),
+    "glsdm_commit_factored_phased": (_i, [_BANK, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i64,
+                                          _i64, _i32, _i32, _i32, _i32, _p, _sz, _p, _p]),
     "glsdm_commit_static": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _p]),
     "glsdm_commit_static_max_entries": (_i64, []),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
@@ -374,14 +376,19 @@ def shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_str
     return addresses[:entries], deltas[:entries], keys[:entries]
 
 
+COMMIT_ORDER, COMMIT_APPLY = 1, 2
+
+
 def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
                     offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
-                    layer_index, key_bits=0):
+                    layer_index, key_bits=0, phases=COMMIT_ORDER | COMMIT_APPLY):
     """Commit the proposal of these write routes into ``shard`` in place without ever writing
     its delta rows: the reducer rebuilds them from ``errors`` (the write_error buffer, laid out
     as for shard_propose) and the bank rows it updates. ``offsets=None`` (unsharded bank):
     every route is an entry and ``entries`` must be rows * width. ``routes`` is the int32
-    all-gather buffer addressed by index_at / weights_at, or a pair (index int32, weights)."""
+    all-gather buffer addressed by index_at / weights_at, or a pair (index int32, weights).
+    ``phases`` = COMMIT_ORDER (entries + sort into the workspace; leaves the bank alone, so it may
+    run beside kernels that still read the bank), COMMIT_APPLY (sums + row updates), or both."""
     if isinstance(routes, tuple):
         index, weights = routes
         require_cuda(index, weights)
@@ -396,11 +403,11 @@ def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_s
     dim = shard.shape[-1]
     lib = library()
     work = _workspace(shard.device, lib.glsdm_commit_factored_workspace_bytes(entries, dim))
-    _check(lib.glsdm_commit_factored(ctypes.byref(bank), index_ptr, weights_ptr,
-                                     _at(errors, 0), _ptr(mass), _ptr(offsets), entries, rows, block_rows,
-                                     route_stride, error_stride, tokens, width, chunk_offset, chunk_size, num_layers,
-                                     layer_index, key_bits, _ptr(work), work.numel(),
-                                     _ptr(status_word(shard.device)), _stream(shard.device)))
+    _check(lib.glsdm_commit_factored_phased(ctypes.byref(bank), index_ptr, weights_ptr,
+                                            _at(errors, 0), _ptr(mass), _ptr(offsets), entries, rows, block_rows,
+                                            route_stride, error_stride, tokens, width, chunk_offset, chunk_size,
+                                            num_layers, layer_index, key_bits, phases, _ptr(work), work.numel(),
+                                            _ptr(status_word(shard.device)), _stream(shard.device)))
 
 
 _workspaces = threading.local()

@@ -401,6 +401,21 @@ extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* inde
                                      int32_t num_layers, int32_t layer_index, int32_t key_bits,
                                      void* workspace, size_t workspace_bytes, uint32_t* device_status,
                                      glsdm_stream_t stream) {
+  return glsdm_commit_factored_phased(bank, index, weights, error, mass, offsets, entries, rows, block_rows,
+                                      route_stride, error_stride, tokens, width, chunk_offset, chunk_size,
+                                      num_layers, layer_index, key_bits, GLSDM_COMMIT_ORDER | GLSDM_COMMIT_APPLY,
+                                      workspace, workspace_bytes, device_status, stream);
+}
+
+extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                                            const float* error, const float* mass, const uint32_t* offsets,
+                                            int64_t entries, int64_t rows, int64_t block_rows,
+                                            int64_t route_stride, int64_t error_stride, int64_t tokens,
+                                            int32_t width, int64_t chunk_offset, int64_t chunk_size,
+                                            int32_t num_layers, int32_t layer_index, int32_t key_bits,
+                                            int32_t phases, void* workspace, size_t workspace_bytes,
+                                            uint32_t* device_status, glsdm_stream_t stream) {
+  if ((phases & ~(GLSDM_COMMIT_ORDER | GLSDM_COMMIT_APPLY)) != 0 || phases == 0) return GLSDM_ERR_ARGUMENT;
   if (rows == 0 || entries == 0) return GLSDM_OK;
   if (bank == nullptr || bank->values == nullptr) return GLSDM_ERR_ARGUMENT;
   if (bank->dtype != GLSDM_F32 && bank->dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
@@ -423,6 +438,7 @@ extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* inde
   const size_t need = carve_factored(&w, &f, static_cast<char*>(workspace), entries, v.dim);
   if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
 
+  if (phases & GLSDM_COMMIT_ORDER) {
   EntryArgs e;
   e.index = index; e.weights = weights; e.error = error; e.mass = mass; e.offsets = offsets;
   e.rows = rows; e.block_rows = block_rows; e.route_stride = route_stride; e.error_stride = error_stride;
@@ -439,6 +455,8 @@ extern "C" int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* inde
   gather_factored_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, f, entries);
   GLSDM_CUDA_OK(cudaGetLastError(), "factored gather launch");
   count_launches(2);
+  }
+  if (!(phases & GLSDM_COMMIT_APPLY)) return GLSDM_OK;
 
   FactoredArgs a;
   a.values = const_cast<void*>(bank->values);

@@ -40,6 +40,7 @@ class SharedBankOperator:
         # (bit-identical result, a third of the HBM traffic on the write side).
         self.factored = factored
         self._packed = None
+        self._side = None
 
     def _proposal_buffers(self, rows):
         k = _native.routes_out(self.writes, self.half)
@@ -81,23 +82,43 @@ class SharedBankOperator:
             self._packed = torch.empty(rows * (self.dim + 1), dtype=torch.float32, device=self.values.device)
         return index, weights, _native.write_error(prediction, target, beta, log_decay, self._packed)
 
-    def commit_operands(self, index, weights, packed, offset=0):
+    def commit_operands(self, index, weights, packed, offset=0, phases=_native.COMMIT_ORDER | _native.COMMIT_APPLY):
         """Second half: the factored commit (reference layers/global_layer.py:52-54 and
-        memory/transactions.py:90-96 in one pass; every route is an entry, no host sync)."""
+        memory/transactions.py:90-96 in one pass; every route is an entry, no host sync).
+        ``phases`` selects its two steps: ordering the entries (leaves the bank alone) and
+        applying them."""
         tokens, width = index.shape[1], index.shape[-1]
         rows = index.numel() // width
         _native.commit_factored(self.values, 0, self.slots, (index, weights), 0, 0, 0, packed, 0, None, None,
                                 rows * width, rows, rows, tokens, width, offset, self.chunk_size, self.num_layers,
-                                self.layer_index, self.key_bits)
-        self.version += 1
+                                self.layer_index, self.key_bits, phases=phases)
+        if phases & _native.COMMIT_APPLY:
+            self.version += 1
 
     def epoch(self, q_scores, k_scores, target, beta, log_decay, offset=0):
         """One full commit epoch: read, propose, commit. Returns the readings."""
-        readings = self.read(q_scores)
-        if self.factored:
-            self.commit_operands(*self.write_operands(k_scores, target, beta, log_decay), offset)
-        else:
+        if not self.factored:
+            readings = self.read(q_scores)
             self.commit(*self.propose(k_scores, target, beta, log_decay, offset))
+            return readings
+        # Write side first; ordering its entries (a chain of small sort kernels that only fills
+        # the commit's workspace) then runs on a second stream beside the query-side read, and
+        # the rows are updated once both are done. Reads and proposal see the same snapshot.
+        device = self.values.device
+        if self._side is None:
+            self._side = torch.cuda.Stream(device)
+        main = torch.cuda.current_stream(device)
+        operands = self.write_operands(k_scores, target, beta, log_decay)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(ready)
+            self.commit_operands(*operands, offset, phases=_native.COMMIT_ORDER)
+            ordered = torch.cuda.Event()
+            ordered.record(self._side)
+        readings = self.read(q_scores)
+        main.wait_event(ordered)
+        self.commit_operands(*operands, offset, phases=_native.COMMIT_APPLY)
         return readings
 
 

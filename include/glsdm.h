@@ -271,6 +271,21 @@ int glsdm_commit_factored(const glsdm_bank* bank, const int32_t* index, const fl
                           int64_t chunk_size, int32_t num_layers, int32_t layer_index,
                           int32_t key_bits, void* workspace, size_t workspace_bytes,
                           uint32_t* device_status, glsdm_stream_t stream);
+/* The same in two steps, so that the first can overlap other work that still reads the bank:
+ *   GLSDM_COMMIT_ORDER  entries, sort and gather into the workspace (reads routes and errors,
+ *                       touches neither the bank nor anything the caller owns)
+ *   GLSDM_COMMIT_APPLY  segmented sums and the row updates, from the workspace as ORDER left it
+ * Pass both bits for the one-call behaviour. Between the two calls the workspace, routes and
+ * error array must stay as they were; the caller orders the streams (ORDER before APPLY). */
+#define GLSDM_COMMIT_ORDER 1
+#define GLSDM_COMMIT_APPLY 2
+int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_t* index, const float* weights,
+                                 const float* error, const float* mass, const uint32_t* offsets,
+                                 int64_t entries, int64_t rows, int64_t block_rows, int64_t route_stride,
+                                 int64_t error_stride, int64_t tokens, int32_t width, int64_t chunk_offset,
+                                 int64_t chunk_size, int32_t num_layers, int32_t layer_index,
+                                 int32_t key_bits, int32_t phases, void* workspace, size_t workspace_bytes,
+                                 uint32_t* device_status, glsdm_stream_t stream);
 
 /* Commit for hosts that cannot provide a workspace. It has no counterpart in the reference
  * (whose commit allocates freely through PyTorch). Same arguments and result as glsdm_commit,
