@@ -351,7 +351,8 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
         # the commit reads a route per entry and an error vector per token, and updates each row once
         hbm["propose"] = tokens * ((w.dim + 1) * 4 + w.dim * 4 + w.dim * e + 8)
         hbm["commit"] = entries * 8 + tokens * (w.dim + 1) * 4 + entries * 2 * w.dim * e
-    out = {"bound": "tensor", "kernel": "score_topk_kernel (tcgen05 + TMEM + TMA, fused top-k)", "achieved": achieved,
+    two_step_commit = entries * (4 * w.dim + 16) + entries * 2 * w.dim * e
+    out = {"bound": "tensor", "kernel": "score_topk_wide_kernel (tcgen05 128x256x16 + TMEM + TMA, fused top-k)", "achieved": achieved,
            "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
            "peak_kind": f"of {peak_kind} sustained cuBLAS bf16 (the kernel runs for >0.1 s inside a multi-second step)",
            "frac_of_burst_peak": achieved / peaks["bf16_tflops"], "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
@@ -361,6 +362,11 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
         if name in phases and phases[name] > 0:
             gbs = nbytes / (phases[name] / 1e3) / 1e9
             out["phases"][name].update({"algorithmic_GBs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]})
+    if getattr(runner.op, "factored", False) and phases.get("commit", 0) > 0:
+        # the same milliseconds against the bytes of a commit that reads materialised delta rows
+        gbs = two_step_commit / (phases["commit"] / 1e3) / 1e9
+        out["phases"]["commit"].update({"delta_row_commit_equivalent_GBs": gbs,
+                                        "delta_row_commit_equivalent_frac": gbs / peaks["hbm_gbs"]})
     return out
 
 
@@ -372,6 +378,11 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
     algo = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1, factored=runner.op.factored)
     dominant = max(phase, key=phase.get)
     achieved = algo[dominant] / (phase[dominant] / 1e3) / 1e9
+    extra = {}
+    if runner.op.factored:
+        plain = workloads.algorithmic_bytes(w, w.tokens_per_epoch // world, unique, layers=1, factored=False)
+        gbs = plain["commit"] / (phase["commit"] / 1e3) / 1e9
+        extra = {"delta_row_commit_equivalent_GBs": gbs, "delta_row_commit_equivalent_frac": gbs / peaks["hbm_gbs"]}
     names = ({"read": "pk_select_read_kernel", "propose": "pk_select_read_kernel + write_error_kernel",
               "commit": "factored commit (radix sort + reduce_factored_kernel)"} if runner.op.factored else
              {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"})
@@ -380,7 +391,8 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": load_traffic(dominant, w),
             "algorithmic_bytes_per_launch": algo[dominant], "ms_per_launch": phase[dominant],
             "phases": {k: {"ms_per_epoch": phase[k], "algorithmic_GBs": algo[k] / (phase[k] / 1e3) / 1e9,
-                           "frac_of_hbm_peak": algo[k] / (phase[k] / 1e3) / 1e9 / peaks["hbm_gbs"]} for k in phase},
+                           "frac_of_hbm_peak": algo[k] / (phase[k] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                           **(extra if k == "commit" else {})} for k in phase},
             "unique_row_fraction": unique}
 
 
