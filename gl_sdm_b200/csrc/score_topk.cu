@@ -531,6 +531,23 @@ extern "C" int glsdm_score_topk_variant(int which) {
   return before;
 }
 
+extern "C" int glsdm_score_topk_plan(int64_t rows, int64_t slots, int32_t width, int32_t which, int32_t sms,
+                                     int32_t* out) {
+  if (rows < 1 || slots < 1 || width < 1 || sms < 1 || out == nullptr || which < 0 || which > 2) return GLSDM_ERR_ARGUMENT;
+  const Plan pl = which == 1   ? make_plan(rows, slots, sms / 2 > 0 ? sms / 2 : 1, width, kPairTileCols)
+                  : which == 2 ? make_plan_with_tail(rows, slots, sms, width, kWideTileCols, kBlockRows)
+                               : make_plan(rows, slots, sms, width);
+  out[0] = pl.unit_pairs;
+  out[1] = pl.splits;
+  out[2] = pl.tiles_per_split;
+  out[3] = pl.tiles_total;
+  out[4] = pl.tail_blocks;
+  out[5] = pl.tail_splits;
+  out[6] = pl.tail_tiles_per_split;
+  out[7] = which == 2 ? kBlockRows : kUnitRows;
+  return GLSDM_OK;
+}
+
 extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;

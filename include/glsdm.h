@@ -321,10 +321,17 @@ int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_
                      int32_t* out_slot, void* workspace, size_t workspace_bytes,
                      uint32_t* device_status, glsdm_stream_t stream);
 
-/* Choose the kernel behind glsdm_score_topk: 0 = one CTA per unit (tcgen05 cta_group::1,
- * default), 1 = a CTA pair per unit (cta_group::2, each CTA loads half of every key tile).
- * Any other value only queries. Returns the previous setting. Same results either way. */
-int glsdm_score_topk_variant(int pair);
+/* Choose the kernel behind glsdm_score_topk: 2 = one CTA per 128 rows, key tiles of 256 slots,
+ * 128x256x16 MMAs (default); 0 = one CTA per 256 rows, key tiles of 128 slots, 128x128x16 MMAs;
+ * 1 = a CTA pair per 256 rows (cta_group::2, each CTA loads half of every key tile). Any other
+ * value only queries. Returns the previous setting. Same results whichever runs. */
+int glsdm_score_topk_variant(int which);
+/* The work decomposition glsdm_score_topk would use (host arithmetic only, no GPU needed):
+ * out[8] = row blocks with uniform parts, parts, key tiles per part, key tiles in all, row
+ * blocks of the last wave that are cut further, their parts, key tiles per such part, rows per
+ * block. Every (row block, key tile) pair belongs to exactly one unit. */
+int glsdm_score_topk_plan(int64_t rows, int64_t slots, int32_t width, int32_t which, int32_t sms,
+                          int32_t* out);
 
 /* The same with row pitches (in elements, multiples of 8): a query matrix whose rows hold
  * several sub-queries, e.g. the two halves of a product-key query. */

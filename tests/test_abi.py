@@ -50,3 +50,27 @@ def test_argument_errors_need_no_device(native):
     assert lib.glsdm_commit(fake, fake, 0, 0, 16, 8, fake, fake, null, 10, 0, ctypes.c_void_p(256), 16, null, null) == 3
     assert lib.glsdm_topk_merge(fake, fake, 2, 0, 8, fake, 1, fake, null) == 0
     assert lib.glsdm_topk_merge(fake, fake, 2, 4, 40, fake, 1, fake, null) == 2
+
+
+def test_score_topk_plans_cover_every_block_and_tile_once():
+    """Host-side work decomposition of the dense-key routing kernels (no GPU involved): the
+    uniform parts and the extra cuts of the last wave's row blocks tile rows x key tiles exactly."""
+    import ctypes
+    from gl_sdm_b200 import _native
+    lib = _native.library()
+    out = (ctypes.c_int32 * 8)()
+    for which in (0, 1, 2):
+        for sms in (148, 132, 8):
+            for rows in (1, 127, 128, 129, 5000, 19000, 65536, 70001):
+                for slots in (1, 255, 4096, 70000, 1 << 20, (1 << 24) - 3):
+                    assert lib.glsdm_score_topk_plan(rows, slots, 32, which, sms, out) == 0
+                    blocks_u, parts, per, tiles, tail_blocks, tail_parts, tail_per, block_rows = list(out)
+                    tile_cols = 128 if which == 0 else 256
+                    assert tiles == -(-slots // tile_cols)
+                    assert (blocks_u + tail_blocks) * block_rows >= rows > (blocks_u + tail_blocks - 1) * block_rows
+                    assert parts >= 1 and (parts - 1) * per < tiles <= parts * per
+                    if tail_blocks:
+                        assert which == 2 and parts == 1 and blocks_u % sms == 0
+                        assert tail_parts >= 2 and (tail_parts - 1) * tail_per < tiles <= tail_parts * tail_per
+                        assert tail_blocks * tail_parts <= sms
+    assert lib.glsdm_score_topk_plan(0, 10, 32, 2, 148, out) != 0
