@@ -294,7 +294,8 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const uint32_t finished = *reinterpret_cast<volatile uint32_t*>(&q->done);
           const uint32_t tail = *reinterpret_cast<volatile uint32_t*>(&q->tail);
           if (finished == 2u * (units_done + 1u) && tail == head) break;    // unit complete, queue empty
-          if (++idle >= kSpinLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
+          if (++idle >= kIdleLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
+          __nanosleep(kIdleNanoseconds);   // an idle poll loop costs issue slots and, under the power cap, clock
           continue;
         }
         idle = 0;

@@ -24,6 +24,8 @@ constexpr int kQueueSlots = 32;                  // entries per inserter queue (
 constexpr int64_t kMaxSlotsPerCall = 1 << 24;    // a queue entry carries a 24-bit slot
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr unsigned kIdleNanoseconds = 1000;      // an idle inserter sleeps this long between looks at its queue
+constexpr uint32_t kIdleLimit = 1u << 22;        // idle looks before an inserter gives up (about four seconds)
 
 struct Params {
   int64_t rows;
