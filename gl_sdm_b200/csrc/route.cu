@@ -3,6 +3,13 @@
 // glsdm_pk_propose.
 #include "route.cuh"
 
+// Resident blocks per SM the selection kernels are compiled for: with 4 (a 64-register budget)
+// the fused route + read measured 336 us at 32,768 rows of 2 x 4096 scores against 355 us
+// without a bound, 353 us with 6 and 400 us with 8 (spills).
+#ifndef GLSDM_SELECT_MIN_BLOCKS
+#define GLSDM_SELECT_MIN_BLOCKS 4
+#endif
+
 namespace glsdm {
 namespace {
 
@@ -21,7 +28,7 @@ __device__ __forceinline__ void store_routes(void* out_index, bool i64, float* o
   if (out_weights != nullptr) out_weights[at] = weight;
 }
 
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, GLSDM_SELECT_MIN_BLOCKS)
 pk_select_kernel(const float* __restrict__ scores, int64_t rows, int half, int kf, int kout,
                  void* out_index, int i64, float* out_weights) {
   __shared__ uint64_t stage[kWarpsPerBlock][kStageSlots];
@@ -35,7 +42,7 @@ pk_select_kernel(const float* __restrict__ scores, int64_t rows, int half, int k
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, GLSDM_SELECT_MIN_BLOCKS)
 pk_select_read_kernel(BankView bank, const float* __restrict__ scores, int64_t rows,
                       int64_t rows_per_bank, int half, int kf, int kout, bool vec,
                       float* __restrict__ out_read, void* out_index, int i64,
