@@ -218,6 +218,16 @@ def cpu_sample_text(w, routing, n, sec):
 def reference_arm(args, w, rank):
     if rank != 0:
         return
+    if w.per_request_banks:
+        cpu = per_request_cpu_port(w, seconds=10.0)
+        ms = cpu.pop("ms_per_step")
+        print(json.dumps({
+            "impl": "reference", "metric": "memory-op tokens/s", "value": cpu["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": per_request_config(w), "cpu_baseline": cpu,
+            "e2e": {"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
     threads = os.cpu_count() or 1
     tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
     value, n, sec = run_cpu_port(w, args.routing, args.steps, args.warmup, tokens, threads)
@@ -229,6 +239,177 @@ def reference_arm(args, w, rank):
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": cpu_sample_text(w, args.routing, n, sec)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- per-request banks (c1 / c2) through the reference-shaped API ------------------------------------
+
+def api_inputs(w, device, seed):
+    """Factor scores and write operands of every (epoch, global layer) of one step; the same
+    distributions as make_epoch_inputs, one bank per request."""
+    from gl_sdm_b200 import workloads
+    return [[workloads.make_epoch_inputs(w, device, seed + 100 * e + layer) for layer in range(w.global_layers)]
+            for e in range(w.epochs)]
+
+
+def api_step(w, values, inputs, memory):
+    """One step the way the reference's stack drives the operator (gl_sdm/layers/stack.py:41-70,
+    global_layer.py:22-54): per 512-token chunk every global layer reads, proposes against the
+    chunk-start snapshot (delta formula of gl_sdm/runtime/dense.py:11-14, written here with
+    tensor ops as the caller does), then one functional commit of all proposals."""
+    view = memory.MemoryView(values)
+    L, C = w.global_layers, w.chunk
+    readings = None
+    for layers in inputs:
+        proposals = []
+        for layer, x in enumerate(layers):
+            readings, _, _ = memory.routing.torch_routed_read(view.values, x["q_scores"], w.width)
+            prediction, index, weights = memory.routing.torch_routed_read(view.values, x["k_scores"], w.width)
+            rows = memory.routing.gather_rows(view.values, index)
+            addresses = memory.routing.absolute_addresses(view.values, index)
+            decay = x["log_decay"].exp().unsqueeze(-1)
+            error = x["beta"].unsqueeze(-1) * (x["target"].float() - decay * prediction)
+            delta = (decay.unsqueeze(-1) - 1) * rows + weights.unsqueeze(-1) * error.unsqueeze(-2)
+            position = torch.arange(index.shape[1], device=index.device).view(1, -1, 1, 1)
+            keys = addresses * (C * L) + position * L + layer
+            proposals.append(memory.WriteProposal(view.version, addresses.flatten(), delta.flatten(0, 3), view.lineage,
+                                                  keys.flatten()))
+        view = memory.commit(view, memory.merge(view, proposals))
+    return readings, view
+
+
+class PortMemory:
+    """The CPU port behind the same five names, so api_step can time it unchanged."""
+
+    def __init__(self):
+        from oracle import torch_port as port
+        self.port = port
+        self.routing = self
+
+    class View:
+        def __init__(self, values, version=0):
+            self.values, self.version, self.lineage = values, version, None
+
+    def MemoryView(self, values):
+        return PortMemory.View(values)
+
+    def WriteProposal(self, version, addresses, deltas, lineage, keys):
+        return (addresses, deltas, keys)
+
+    def torch_routed_read(self, values, scores, width):
+        return self.port.routed_read(values, scores, width)
+
+    def gather_rows(self, values, index):
+        return values.flatten(0, 2)[self.port.flat_rows(values, index)]
+
+    def absolute_addresses(self, values, index):
+        return self.port.flat_rows(values, index)
+
+    def merge(self, view, proposals):
+        return proposals
+
+    def commit(self, view, proposals):
+        a, d, k = (torch.cat([p[i] for p in proposals]) for i in range(3))
+        return PortMemory.View(self.port.commit(view.values, a, d, k), view.version + 1)
+
+
+def per_request_config(w):
+    bank_mb = w.sequences * w.heads * w.slots * w.dim * 4 >> 20
+    return {"workload": f"{w.name}: {w.description}",
+            "routing": "product-key factor scores through the memory API (routed_read, gather_rows, merge, functional "
+                       "commit), one bank per request: replicas only",
+            "slots": w.slots, "d_v": w.dim, "top_k": w.width, "tokens_per_step": w.tokens_per_step,
+            "global_layers": w.global_layers, "commit_epochs": w.epochs,
+            "l2": f"banks of {bank_mb} MB: " + ("L2-resident, so the HBM fraction understates nothing and bounds nothing; "
+                                                  "the step is launch-bound" if bank_mb < 100 else
+                                                  "larger than L2; every commit copies them (functional commit)")}
+
+
+def per_request_cpu_port(w, seconds=5.0):
+    """The CPU port through api_step on all host cores: c1 whole, c2 one request x one chunk
+    (8 layers); repeated until `seconds` have passed, median step. Returns the cpu_baseline."""
+    from gl_sdm_b200 import workloads
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    sample = w if w.name == "c1" else w.scaled(sequences=1, seq_len=w.chunk)
+    values = workloads.make_bank(sample, "cpu")
+    inputs = api_inputs(sample, "cpu", 1000)
+    port = PortMemory()
+    api_step(sample, values, inputs, port)
+    times, begun = [], time.perf_counter()
+    while not times or (time.perf_counter() - begun < seconds and len(times) < 50):
+        t = time.perf_counter()
+        api_step(sample, values, inputs, port)
+        times.append(time.perf_counter() - t)
+    sec = statistics.median(times)
+    return {"value": sample.tokens_per_step / sec, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{sample.sequences} x {sample.seq_len} tokens, {sample.global_layers} global layer(s), through the same "
+                      f"call sequence (functional commit), median of {len(times)} steps of {sec:.2f} s; PyTorch CPU port of "
+                      "the reference path",
+            "ms_per_step": sec * 1e3}
+
+
+def per_request_arm(args, w, rank):
+    """c1 / c2: one fp32 bank per request, no sharding (replicas only): rank 0 measures one GPU."""
+    if rank != 0:
+        return
+    import gl_sdm_b200.memory as memory
+    from gl_sdm_b200 import _native, workloads
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _native.library()
+    peaks, peak_kind = measured_peaks()
+    values = workloads.make_bank(w, dev)
+    inputs = api_inputs(w, dev, 1000)
+    for _ in range(args.warmup):
+        api_step(w, values, inputs, memory)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = lib.glsdm_kernel_launches()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    start.record()
+    for _ in range(args.steps):
+        api_step(w, values, inputs, memory)
+    stop.record()
+    torch.cuda.synchronize(dev)
+    ms = start.elapsed_time(stop) / args.steps
+    launches = lib.glsdm_kernel_launches() - launches0
+    clocks = sampler.stop()
+    _native.raise_on_device_status(dev)
+    # host inputs: every chunk's scores and write operands come from pinned memory, the last readings go back
+    host = [[{k: v.cpu().pin_memory() for k, v in x.items()} for x in layers] for layers in inputs]
+    h2d = sum(v.numel() * v.element_size() for layers in host for x in layers for v in x.values())
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    t0.record()
+    moved = [[{k: v.to(dev, non_blocking=True) for k, v in x.items()} for x in layers] for layers in host]
+    readings, _ = api_step(w, values, moved, memory)
+    back = readings.cpu()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = t0.elapsed_time(t1)
+    algo = workloads.algorithmic_bytes(w, w.tokens_per_step, 1.0)
+    # the functional commit writes a new bank per epoch: one read and one write of every bank
+    algo["bank_copy"] = w.epochs * 2 * values.numel() * values.element_size()
+    total = sum(algo.values())
+    gbs = total / (ms / 1e3) / 1e9
+    cpu = None if args.no_cpu_baseline else per_request_cpu_port(w)
+    line = {
+        "metric": "memory-op tokens/s", "value": w.tokens_per_step / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": per_request_config(w),
+        "roofline": {"bound": "hbm", "kernel": "whole step (pk_select_read, gather_rows, commit sort + reduce; delta by tensor ops)",
+                     "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "algorithmic_bytes_per_step": total,
+                     "algorithmic_bytes_by_stage": {k: int(v) for k, v in algo.items()}},
+        "cpu_baseline": cpu,
+        "e2e": {"value": w.tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": 1,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": back.numel() * 4},
+        "gpu_launches": int(launches), "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
 
@@ -494,9 +675,6 @@ def ours(args, w, rank, world, local, dist):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     lib = _native.library()
-    if w.per_request_banks:
-        raise SystemExit("c1/c2 hold one bank per request (replicas only); this benchmark covers the shared-bank "
-                         "configurations c3-c5")
     peaks, peak_kind = measured_peaks()
     runner = Runner(w, args.routing, dev, rank, world, dist, not args.delta_rows)
     for _ in range(args.warmup):
@@ -576,6 +754,11 @@ def main():
     rank, world, local, dist = dist_setup(args)
     if args.impl == "reference":
         reference_arm(args, w, rank)
+        return
+    if w.per_request_banks:
+        per_request_arm(args, w, rank)
+        if dist is not None:
+            dist.destroy_process_group()
         return
     if w.sequences % world:
         raise SystemExit("sequences per step must divide over the ranks")
