@@ -83,5 +83,51 @@ class Commit(torch.autograd.Function):
         return incoming if ctx.needs_input_grad[0] else None, None, grad_deltas, None, None
 
 
+class TokenRead(torch.autograd.Function):
+    """Token-clock weighted read of supplied routes [A, H, K] -> [A, H, D].
+
+    The forward is the same kernel the forward-only call runs. Like the reference's wrapper
+    (gl_sdm/memory/backends/token.py:134-168) it keeps the selected rows, not the bank, for
+    the backward; unlike it the bank gradient is scattered deterministically.
+    """
+
+    @staticmethod
+    def forward(ctx, values, requests, indices, weights, addresses):
+        heads = values.shape[1]
+        weights = weights.detach().float().contiguous()
+        out = _native.snapshot_read(values.detach(), indices, weights, rows_per_bank=heads, requests=requests)
+        rows = _native.gather_rows(values.detach().flatten(0, 2), addresses) if ctx.needs_input_grad[3] else None
+        ctx.save_for_backward(addresses, weights, rows)
+        ctx.bank = (values.shape, values.device, values.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, incoming):
+        addresses, weights, rows = ctx.saved_tensors
+        shape, device, dtype = ctx.bank
+        incoming = incoming.float()
+        grad_values = grad_weights = None
+        if ctx.needs_input_grad[0]:
+            grad_values = _dense_bank_gradient(shape, device, addresses,
+                                               weights.unsqueeze(-1) * incoming.unsqueeze(-2)).to(dtype)
+        if ctx.needs_input_grad[3]:
+            grad_weights = (rows.float() * incoming.unsqueeze(-2)).sum(-1)
+        return grad_values, None, None, grad_weights, None
+
+
+def token_proposal_deltas(values, addresses, weights, targets, beta, log_decay, mass):
+    """Differentiable token-clock write proposal: the row gather runs on the kernels (its
+    backward is the deterministic scatter), the delta itself is the reference's expression
+    (gl_sdm/memory/transactions.py:52-58) in tensor ops so autograd covers every operand."""
+    rows = GatherRows.apply(values, addresses).float()
+    decay = log_decay.float().exp().unsqueeze(-1)
+    decayed = rows * decay
+    w = weights.float().unsqueeze(-1)
+    retrieved = (decayed * w).sum(-2)
+    error = beta.float() * (targets.float() - retrieved)
+    delta = decayed - rows + w * error.unsqueeze(-2)
+    return delta * mass.float()[:, None, None, None]
+
+
 def needs_grad(*tensors):
     return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)

@@ -20,12 +20,6 @@ def _check_backend(backend):
         raise ValueError("memory backend must be torch or urm")
 
 
-def _forward_only(*tensors):
-    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
-        raise NotImplementedError(
-            "the B200 memory operator is forward-only: run under torch.no_grad() / inference_mode()")
-
-
 def addresses(view, requests, indices):
     """Flat bank row of every selected slot: (request*heads + head)*slots + slot."""
     heads, slots = view.values.shape[1:3]
@@ -46,7 +40,10 @@ def read(view, requests, indices, weights, reference=False, backend="torch"):
     _check_backend(backend)
     if reference:
         return oracle_hook.get("read")(view, requests, indices, weights)
-    _forward_only(view.values, weights)
+    _native.require_cuda(view.values)
+    if autograd.needs_grad(view.values, weights):
+        return autograd.TokenRead.apply(view.values, requests.long().contiguous(), indices.contiguous(), weights,
+                                        addresses(view, requests, indices).contiguous())
     heads = view.values.shape[1]
     return _native.snapshot_read(view.values, indices.contiguous(), weights.float().contiguous(),
                                  rows_per_bank=heads, requests=requests.long().contiguous())
@@ -61,7 +58,11 @@ def propose_write(view, requests, indices, weights, targets, beta, log_decay,
     _check_backend(backend)
     if reference:
         return oracle_hook.get("propose_write")(view, requests, indices, weights, targets, beta, log_decay, mass)
-    _forward_only(view.values, weights, targets, beta, log_decay, mass)
+    _native.require_cuda(view.values)
+    if autograd.needs_grad(view.values, weights, targets, beta, log_decay, mass):
+        flat = addresses(view, requests, indices).contiguous()
+        deltas = autograd.token_proposal_deltas(view.values, flat, weights, targets, beta, log_decay, mass)
+        return WriteProposal(view.version, flat.flatten(), deltas.flatten(0, 2), view.lineage)
     flat_addresses, deltas = _native.token_propose(
         view.values, requests.long().contiguous(), indices.contiguous(), weights.float().contiguous(),
         targets.float().contiguous(), beta.float().contiguous(), log_decay.float().contiguous(),

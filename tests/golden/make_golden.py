@@ -42,6 +42,9 @@ def main(reference_root, only=None):
             rec["memory"], rec["scores"] = memory.numpy(), scores.numpy()
         np.savez_compressed(os.path.join(HERE, f"routed_{name}.npz"), **rec)
         out[f"routed_{name}"] = tuple(index.shape)
+    if only and "token_gradients" in only:
+        write_token_gradients(MemoryView, read, propose_write)
+        out["token_gradients"] = ()
     if only:
         print("wrote", sorted(out))
         return
@@ -132,7 +135,28 @@ def main(reference_root, only=None):
     updated = commit(view, merge(view, [p, p2]))
     np.savez_compressed(os.path.join(HERE, "token_api.npz"), read=retrieved.numpy(), addresses=p.addresses.numpy(),
                         deltas=p.deltas.numpy(), deltas2=p2.deltas.numpy(), updated=updated.values.numpy())
-    print("wrote", sorted(out), "commit_cases token_api")
+    write_token_gradients(MemoryView, read, propose_write)
+    print("wrote", sorted(out), "commit_cases token_api token_gradients")
+
+
+def write_token_gradients(MemoryView, read, propose_write):
+    """Reference autograd through the token-clock read and write proposal (torch path; the
+    native path's hand-written backward is gl_sdm/memory/backends/token.py:134-168)."""
+    t = gi.token_case()
+    names = ("memory", "weights", "targets", "beta", "log_decay", "mass")
+    leaves = {k: t[k].clone().requires_grad_() for k in names}
+    view = MemoryView(leaves["memory"])
+    retrieved = read(view, t["requests"], t["indices"], leaves["weights"])
+    p = propose_write(view, t["requests"], t["indices"], leaves["weights"], leaves["targets"], leaves["beta"],
+                      leaves["log_decay"], leaves["mass"])
+    cot_read, cot_delta = gi.cotangents("token", retrieved.shape, p.deltas.shape)
+    rec = {}
+    grads = torch.autograd.grad((retrieved * cot_read).sum(), (leaves["memory"], leaves["weights"]), retain_graph=True)
+    rec["read_grad_memory"], rec["read_grad_weights"] = (g.numpy() for g in grads)
+    grads = torch.autograd.grad((p.deltas * cot_delta).sum(), [leaves[k] for k in names])
+    for k, g in zip(names, grads):
+        rec[f"propose_grad_{k}"] = g.numpy()
+    np.savez_compressed(os.path.join(HERE, "token_gradients.npz"), **rec)
 
 
 if __name__ == "__main__":

@@ -59,3 +59,33 @@ def test_write_chain_gradients_match_reference_autograd(native):
     with pytest.raises(ValueError, match="donated"):
         commit(view, merge(view, [WriteProposal(0, addresses.flatten(), delta.flatten(0, 3), view.lineage, keys.flatten())]),
                donate=True)
+
+
+def test_token_clock_gradients_match_reference_autograd(native):
+    """Token-clock read and write proposal (gl_sdm/memory/transactions.py:28-59) with every
+    operand requiring grad, against the reference's autograd on the same inputs; the forward
+    results under grad mode still match the forward-only golden vectors."""
+    from gl_sdm_b200.memory import MemoryView, propose_write, read
+    gold, forward = load_golden("token_gradients"), load_golden("token_api")
+    t = {k: v.to(DEV) for k, v in gi.token_case().items()}
+    names = ("memory", "weights", "targets", "beta", "log_decay", "mass")
+    leaves = {k: t[k].clone().requires_grad_() for k in names}
+    view = MemoryView(leaves["memory"])
+    retrieved = read(view, t["requests"], t["indices"], leaves["weights"])
+    p = propose_write(view, t["requests"], t["indices"], leaves["weights"], leaves["targets"], leaves["beta"],
+                      leaves["log_decay"], leaves["mass"])
+    assert retrieved.requires_grad and p.deltas.requires_grad
+    np.testing.assert_allclose(retrieved.detach().cpu().numpy(), forward["read"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(p.deltas.detach().cpu().numpy(), forward["deltas"], rtol=1e-5, atol=1e-5)
+    assert np.array_equal(p.addresses.cpu().numpy(), forward["addresses"])
+    cot_read, cot_delta = gi.cotangents("token", retrieved.shape, p.deltas.shape)
+    grads = torch.autograd.grad((retrieved * cot_read.to(DEV)).sum(), (leaves["memory"], leaves["weights"]), retain_graph=True)
+    np.testing.assert_allclose(grads[0].cpu().numpy(), gold["read_grad_memory"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(grads[1].cpu().numpy(), gold["read_grad_weights"], rtol=1e-5, atol=1e-5)
+    grads = torch.autograd.grad((p.deltas * cot_delta.to(DEV)).sum(), [leaves[k] for k in names])
+    for k, g in zip(names, grads):
+        np.testing.assert_allclose(g.cpu().numpy(), gold[f"propose_grad_{k}"], rtol=1e-4, atol=1e-5, err_msg=k)
+    # only the bank requires grad: the weight gradient (and its saved rows) is skipped
+    only_bank = read(view, t["requests"], t["indices"], t["weights"])
+    (g,) = torch.autograd.grad((only_bank * cot_read.to(DEV)).sum(), (leaves["memory"],))
+    np.testing.assert_allclose(g.cpu().numpy(), gold["read_grad_memory"], rtol=1e-5, atol=1e-5)
