@@ -67,6 +67,7 @@ SIGNATURES = {
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
     "glsdm_score_topk": (_i, [_p, _p, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_score_topk_variant": (_i, [_i]),
+    "glsdm_commit_factored_mode": (_i, [_i]),
     "glsdm_score_topk_plan": (_i, [_i64, _i64, _i32, _i32, _i32, _p]),
     "glsdm_score_topk_pitched": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_pk_combine": (_i, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _i, _p, _p]),

@@ -44,7 +44,14 @@ struct Workspace {
   int64_t partial_rows;
   int64_t long_capacity;
   int tiles;
+  // When set, the number of live entries is read on the device (a list whose length the
+  // host does not know): grids stay sized for the capacity, blocks past the end do nothing.
+  const uint32_t* live;
 };
+
+__device__ __forceinline__ int64_t live_entries(const uint32_t* live, int64_t capacity) {
+  return live != nullptr ? static_cast<int64_t>(*live) : capacity;
+}
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -61,6 +68,7 @@ size_t carve(Workspace* w, char* base, int64_t entries, int32_t dim) {
   Workspace local;
   Workspace* o = w ? w : &local;
   o->tiles = tiles;
+  o->live = nullptr;
   o->long_capacity = long_capacity;
   o->partial_rows = partial_rows;
   o->keys[0] = reinterpret_cast<uint64_t*>(take(sizeof(uint64_t) * entries));
@@ -81,10 +89,12 @@ __device__ __forceinline__ uint32_t digit_of(uint64_t key, int pass) {
 }
 
 __global__ void __launch_bounds__(kSortThreads)
-prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes,
+prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, const uint32_t* live, int passes,
                uint64_t* __restrict__ out_keys, uint32_t* __restrict__ out_ids,
                uint32_t* __restrict__ histogram) {
   __shared__ uint32_t local[kDigits][kRadix];
+  entries = live_entries(live, entries);
+  if (static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
   for (int i = threadIdx.x; i < kDigits * kRadix; i += kSortThreads) (&local[0][0])[i] = 0;
   __syncthreads();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
@@ -104,9 +114,10 @@ prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes,
   }
 }
 
-__global__ void plan_kernel(const uint32_t* __restrict__ histogram, int64_t entries, int passes,
-                            Plan* plan) {
+__global__ void plan_kernel(const uint32_t* __restrict__ histogram, int64_t entries, const uint32_t* live,
+                            int passes, Plan* plan) {
   __shared__ uint32_t uniform[kDigits];
+  entries = live_entries(live, entries);
   if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
@@ -130,6 +141,9 @@ __global__ void __launch_bounds__(kSortThreads)
 count_kernel(Workspace w, int64_t entries, int pass) {
   if (w.plan->skip[pass]) return;
   __shared__ uint32_t local[kRadix];
+  entries = live_entries(w.live, entries);
+  // With a device-side count the scan reads only the tiles that hold live entries.
+  if (w.live != nullptr && static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
   local[threadIdx.x] = 0;
   __syncthreads();
   const uint64_t* __restrict__ keys = w.keys[w.plan->source[pass]];
@@ -161,9 +175,14 @@ scan_kernel(Workspace w, int pass) {
   if (threadIdx.x == 0) carry = part[0];
   __syncthreads();
   uint32_t* __restrict__ row = w.tile_count + static_cast<size_t>(d) * w.tiles;
-  for (int t0 = 0; t0 < w.tiles; t0 += kSortThreads) {
+  int tiles = w.tiles;   // only the tiles that hold live entries need their bases
+  if (w.live != nullptr) {
+    const int64_t used = (static_cast<int64_t>(*w.live) + kTile - 1) / kTile;
+    if (used < tiles) tiles = static_cast<int>(used);
+  }
+  for (int t0 = 0; t0 < tiles; t0 += kSortThreads) {
     const int t = t0 + threadIdx.x;
-    const uint32_t c = t < w.tiles ? row[t] : 0u;
+    const uint32_t c = t < tiles ? row[t] : 0u;
     part[threadIdx.x] = c;
     __syncthreads();
     for (int off = 1; off < kSortThreads; off <<= 1) {
@@ -173,7 +192,7 @@ scan_kernel(Workspace w, int pass) {
       __syncthreads();
     }
     const uint32_t base = carry;
-    if (t < w.tiles) row[t] = base + part[threadIdx.x] - c;
+    if (t < tiles) row[t] = base + part[threadIdx.x] - c;
     __syncthreads();
     if (threadIdx.x == kSortThreads - 1) carry = base + part[threadIdx.x];
     __syncthreads();
@@ -185,6 +204,8 @@ scan_kernel(Workspace w, int pass) {
 __global__ void __launch_bounds__(kSortThreads)
 scatter_kernel(Workspace w, int64_t entries, int pass) {
   if (w.plan->skip[pass]) return;
+  entries = live_entries(w.live, entries);
+  if (static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
   constexpr int kWarps = kSortThreads / 32;
   __shared__ uint32_t warp_count[kWarps][kRadix];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -240,7 +261,7 @@ scatter_kernel(Workspace w, int64_t entries, int pass) {
 __global__ void gather_address_kernel(Workspace w, const int64_t* __restrict__ addresses,
                                       int64_t entries) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= entries) return;
+  if (i >= live_entries(w.live, entries)) return;
   const uint32_t* __restrict__ ids = w.ids[w.plan->final_buffer];
   w.sorted_address[i] = addresses[ids[i]];
 }
@@ -420,10 +441,10 @@ inline int run_sort(const Workspace& w, const int64_t* keys, int64_t entries, in
                     glsdm_stream_t stream) {
   GLSDM_CUDA_OK(cudaMemsetAsync(w.histogram, 0, sizeof(uint32_t) * kDigits * kRadix, stream),
                 "commit histogram clear");
-  prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, passes, w.keys[0], w.ids[0],
+  prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, w.live, passes, w.keys[0], w.ids[0],
                                                        w.histogram);
   GLSDM_CUDA_OK(cudaGetLastError(), "commit prepare launch");
-  plan_kernel<<<1, 256, 0, stream>>>(w.histogram, entries, passes, w.plan);
+  plan_kernel<<<1, 256, 0, stream>>>(w.histogram, entries, w.live, passes, w.plan);
   GLSDM_CUDA_OK(cudaGetLastError(), "commit plan launch");
   for (int p = 0; p < passes; ++p) {
     count_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);

@@ -13,6 +13,9 @@
 //
 // The arithmetic is the materialised path's, operation for operation (same fp32 products,
 // sums and order), so both commits produce bit-identical banks.
+#include <atomic>
+#include <cstdlib>
+
 #include "commit.cuh"
 #include "route.cuh"
 
@@ -32,7 +35,21 @@ struct FactoredScratch {
   int64_t* addresses;     // [entries] unsorted shard-local rows
   Descriptor* described;  // [entries] unsorted
   Descriptor* sorted;     // [entries] in key order
+  // Dense numbering only: which addresses are written more than once.
+  uint32_t* seen;         // [bits / 32] an entry has this address (modulo bits)
+  uint32_t* twice;        // [bits / 32] a second entry had it too
+  uint32_t* block_shared; // [entries / 8 + 2] entries per block of rows that need the sort, then its exclusive scan
+  uint32_t* live;         // [1] how many entries need the sort
+  uint32_t bit_mask;      // bits - 1
 };
+
+// Bits of each address map: a power of two >= 16 per entry. A bank with more rows than bits
+// folds several addresses onto one bit; they then all take the sorted path, which is always correct.
+int64_t address_bits_for(int64_t entries) {
+  int64_t bits = 1 << 16;
+  while (bits < 16 * entries && bits < (int64_t{1} << 31)) bits <<= 1;
+  return bits;
+}
 
 size_t carve_factored(Workspace* w, FactoredScratch* f, char* base, int64_t entries, int32_t dim) {
   size_t at = carve(w, base, entries, dim);
@@ -47,6 +64,12 @@ size_t carve_factored(Workspace* w, FactoredScratch* f, char* base, int64_t entr
   o->addresses = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
   o->described = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
   o->sorted = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
+  const int64_t bits = address_bits_for(entries);
+  o->bit_mask = static_cast<uint32_t>(bits - 1);
+  o->seen = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(bits / 8) * 2));   // seen and twice, one clear
+  o->twice = o->seen != nullptr ? o->seen + bits / 32 : nullptr;
+  o->block_shared = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * (entries / kWarpsPerBlock + 2)));
+  o->live = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t)));
   return at;
 }
 
@@ -108,7 +131,7 @@ factored_entries_kernel(BankView bank, EntryArgs a, FactoredScratch out) {
 
 __global__ void gather_factored_kernel(Workspace w, FactoredScratch f, int64_t entries) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= entries) return;
+  if (i >= live_entries(w.live, entries)) return;
   const uint32_t id = w.ids[w.plan->final_buffer][i];
   w.sorted_address[i] = f.addresses[id];
   f.sorted[i] = f.described[id];
@@ -206,19 +229,20 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
 reduce_factored_kernel(Workspace w, FactoredArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp) * 32;
-  if (first >= a.entries) return;
+  const int64_t entries = live_entries(w.live, a.entries);
+  if (first >= entries) return;
   const int64_t* __restrict__ sorted = w.sorted_address;
   const int64_t at = first + lane;
-  const int64_t mine = at < a.entries ? sorted[at] : -1;
-  const int64_t prev = (at > 0 && at < a.entries) ? sorted[at - 1] : -2;
-  const bool is_head = at < a.entries && (at == 0 || mine != prev);
+  const int64_t mine = at < entries ? sorted[at] : -1;
+  const int64_t prev = (at > 0 && at < entries) ? sorted[at - 1] : -2;
+  const bool is_head = at < entries && (at == 0 || mine != prev);
   const unsigned all_heads = __ballot_sync(kFullMask, is_head);
   unsigned heads = all_heads;
   T* __restrict__ values = static_cast<T*>(a.values);
   if constexpr (V > 0) {
-    const int64_t next = (at + 1 < a.entries) ? sorted[at + 1] : -3;
+    const int64_t next = (at + 1 < entries) ? sorted[at + 1] : -3;
     Descriptor my_d = {0u, 0.f, 0.f, 0.f};
-    if (at < a.entries) my_d = a.sorted[at];
+    if (at < entries) my_d = a.sorted[at];
     unsigned singles = __ballot_sync(kFullMask, is_head && mine != next && mine >= 0 && mine < a.bank_rows);
     heads &= ~singles;
     while (singles) {
@@ -264,9 +288,9 @@ reduce_factored_kernel(Workspace w, FactoredArgs a) {
     if (later) {
       len = (__ffs(later) - 1) - h;
     } else {
-      const int64_t tail = first + 32 < a.entries ? first + 32 : a.entries;
+      const int64_t tail = first + 32 < entries ? first + 32 : entries;
       len = tail - start;
-      if (tail < a.entries) len = segment_length(sorted, tail - 1, a.entries, local, lane) + (tail - 1 - start);
+      if (tail < entries) len = segment_length(sorted, tail - 1, entries, local, lane) + (tail - 1 - start);
     }
     if (len > kLongSegment) {
       if (lane == 0) {
@@ -362,6 +386,236 @@ long_factored_kernel(Workspace w, FactoredArgs a) {
   }
 }
 
+// ---- dense numbering: rows written once skip the sort ------------------------------------------
+//
+// Most addresses of a commit epoch are written by exactly one entry (a 16M-slot bank and 1M
+// entries: ~97 %). Such an entry has nothing to be ordered against: its row can be updated
+// straight from the routes, in whatever order the entries come. Two bit maps over the
+// addresses find them (first writer sets `seen`, any later one sets `twice`); only the entries
+// of addresses marked `twice` are compacted, in entry order, into the list that is sorted and
+// reduced as before. The list's length stays on the device.
+
+struct DenseLane {
+  int64_t address;   // shard-local row, or -1 when the slot is outside the bank
+  int64_t slot;
+  float weight;
+  bool valid;        // lane holds a route
+};
+
+// Row `major` of the token-major numbering ((position, sequence, head)) in the caller's
+// [sequence, token, head] layout.
+__device__ __forceinline__ int64_t caller_row(const BankView& bank, const EntryArgs& a, int64_t major) {
+  const int64_t head = major % bank.heads, ps = major / bank.heads;
+  const int64_t sequence = ps % a.sequences, position = ps / a.sequences;
+  return (sequence * a.tokens + position) * bank.heads + head;
+}
+
+__device__ __forceinline__ DenseLane dense_lane(const BankView& bank, const EntryArgs& a, int64_t row, int lane) {
+  DenseLane l;
+  l.valid = lane < a.width;
+  l.address = -1;
+  l.slot = -1;
+  l.weight = 0.f;
+  if (l.valid) {
+    const int64_t block = row / a.block_rows, inner = row % a.block_rows;
+    const int64_t at = block * a.route_stride + inner * a.width + lane;
+    l.slot = a.index[at];
+    l.weight = a.weights[at];
+    if (l.slot >= bank.slot_lo && l.slot < bank.slot_hi)
+      l.address = (row % bank.heads) * bank.part_stride_rows + (l.slot - bank.slot_lo);
+  }
+  return l;
+}
+
+__device__ __forceinline__ bool written_twice(const FactoredScratch& f, int64_t address) {
+  const uint32_t h = static_cast<uint32_t>(address) & f.bit_mask;
+  return (f.twice[h >> 5] >> (h & 31)) & 1u;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+mark_addresses_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= a.rows) return;
+  const DenseLane l = dense_lane(bank, a, row, lane);
+  if (l.address < 0) return;
+  const uint32_t h = static_cast<uint32_t>(l.address) & f.bit_mask;
+  const uint32_t bit = 1u << (h & 31);
+  if (atomicOr(&f.seen[h >> 5], bit) & bit) atomicOr(&f.twice[h >> 5], bit);
+}
+
+// Entries of this block's rows (token-major) that need the sort.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+count_shared_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
+  __shared__ uint32_t per_warp[kWarpsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  uint32_t c = 0;
+  if (major < a.rows) {
+    const DenseLane l = dense_lane(bank, a, caller_row(bank, a, major), lane);
+    c = __popc(__ballot_sync(kFullMask, l.address >= 0 && written_twice(f, l.address)));
+  }
+  if (lane == 0) per_warp[warp] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t total = 0;
+#pragma unroll
+    for (int q = 0; q < kWarpsPerBlock; ++q) total += per_warp[q];
+    f.block_shared[blockIdx.x] = total;
+  }
+}
+
+// In-place exclusive scan of counts[0, n); the total goes to *total.
+__global__ void __launch_bounds__(1024)
+scan_shared_kernel(uint32_t* __restrict__ counts, int64_t n, uint32_t* __restrict__ total) {
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t carry;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < n; base += 1024) {
+    const int64_t i = base + threadIdx.x;
+    const uint32_t c = i < n ? counts[i] : 0u;
+    uint32_t inclusive = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(kFullMask, inclusive, o);
+      if (lane >= o) inclusive += t;
+    }
+    if (lane == 31) warp_sum[warp] = inclusive;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t mine = warp_sum[lane];
+      uint32_t running = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(kFullMask, running, o);
+        if (lane >= o) running += t;
+      }
+      warp_sum[lane] = running - mine;
+    }
+    __syncthreads();
+    const uint32_t before = carry + warp_sum[warp] + inclusive - c;
+    if (i < n) counts[i] = before;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = before + c;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *total = carry;
+}
+
+// Address, key and descriptor of every entry that needs the sort, in entry order.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+compact_shared_kernel(BankView bank, EntryArgs a, FactoredScratch f, uint32_t* device_status) {
+  __shared__ uint32_t per_warp[kWarpsPerBlock];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  DenseLane l;
+  l.address = -1; l.slot = -1; l.weight = 0.f; l.valid = false;
+  int64_t row = 0;
+  unsigned mask = 0;
+  if (major < a.rows) {
+    row = caller_row(bank, a, major);
+    l = dense_lane(bank, a, row, lane);
+    mask = __ballot_sync(kFullMask, l.address >= 0 && written_twice(f, l.address));
+    if (l.valid && l.address < 0 && device_status != nullptr) atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+  }
+  if (lane == 0) per_warp[warp] = __popc(mask);
+  __syncthreads();
+  if (!((mask >> lane) & 1u)) return;
+  uint32_t at = f.block_shared[blockIdx.x] + __popc(mask & ((1u << lane) - 1u));
+  for (int q = 0; q < warp; ++q) at += per_warp[q];
+  const int64_t block = row / a.block_rows, inner = row % a.block_rows;
+  Descriptor d;
+  d.error_at = static_cast<uint32_t>(block * a.error_stride + inner * bank.dim);
+  d.weight = l.weight;
+  d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
+  d.mass = a.mass != nullptr ? a.mass[row / bank.heads] : 1.0f;
+  f.addresses[at] = l.address;
+  f.keys[at] = (row % bank.heads) * bank.slots + l.slot;
+  f.described[at] = d;
+}
+
+
+// Rows written by one entry only, updated straight from the routes: the token's error row is
+// read once per warp, the arithmetic is the single-entry case of the reducer.
+constexpr int kOnceBatch = 4;   // bank rows in flight per warp (2 measures the same, 8 is 40 % slower)
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+apply_once_kernel(BankView bank, EntryArgs a, FactoredScratch f, void* bank_values) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (major >= a.rows) return;
+  const int64_t row = caller_row(bank, a, major);
+  const DenseLane l = dense_lane(bank, a, row, lane);
+  unsigned once = __ballot_sync(kFullMask, l.address >= 0 && !written_twice(f, l.address));
+  if (once == 0) return;
+  const int64_t block = row / a.block_rows, inner = row % a.block_rows;
+  Descriptor d;
+  d.error_at = 0;
+  d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
+  d.mass = a.mass != nullptr ? a.mass[row / bank.heads] : 1.0f;
+  Slice<V> err;
+  load_delta<V>(err, a.error + block * a.error_stride + inner * bank.dim, lane);
+  T* __restrict__ values = static_cast<T*>(bank_values);
+  while (once) {
+    int pick[kOnceBatch];
+#pragma unroll
+    for (int j = 0; j < kOnceBatch; ++j) {
+      pick[j] = once ? __ffs(once) - 1 : -1;
+      if (once) once &= once - 1;
+    }
+    Slice<V> old[kOnceBatch];
+    int64_t where[kOnceBatch];
+    float weight[kOnceBatch];
+#pragma unroll
+    for (int j = 0; j < kOnceBatch; ++j) {
+      if (pick[j] < 0) continue;
+      where[j] = __shfl_sync(kFullMask, l.address, pick[j]);
+      weight[j] = __shfl_sync(kFullMask, l.weight, pick[j]);
+      load_bank<T, V>(values + where[j] * bank.dim, old[j], lane);
+    }
+#pragma unroll
+    for (int j = 0; j < kOnceBatch; ++j) {
+      if (pick[j] < 0) continue;
+      d.weight = weight[j];
+      Slice<V> x;
+      rebuild<V>(x, d, err, old[j]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) old[j].v[i] = __fadd_rn(old[j].v[i], __fadd_rn(0.f, x.v[i]));
+      store_bank<T, V>(values + where[j] * bank.dim, old[j], lane);
+    }
+  }
+}
+
+template <typename T, int V>
+int launch_once(const BankView& v, const EntryArgs& e, const FactoredScratch& f, void* values,
+                glsdm_stream_t stream) {
+  apply_once_kernel<T, V><<<blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f, values);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored single-writer launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+// -1 = decide from the sizes, 0 = sort every entry, 1 = single-writer rows skip the sort.
+// GLSDM_FACTORED_ONCE in the environment sets the initial value.
+std::atomic<int>& once_mode() {
+  static std::atomic<int> mode = [] {
+    const char* v = std::getenv("GLSDM_FACTORED_ONCE");
+    return (v == nullptr || v[0] == '\0') ? -1 : (v[0] == '0' ? 0 : 1);
+  }();
+  return mode;
+}
+
+// The bit maps, the compaction and the second reducer cost ~10 launches: they pay once the
+// sort they avoid is large (entries) and most rows have one writer (bank rows per entry).
+bool once_path_pays(int64_t entries, int64_t bank_rows) {
+  const int mode = once_mode().load();
+  if (mode >= 0) return mode == 1;
+  return entries >= (int64_t{1} << 19) && bank_rows >= 8 * entries;
+}
+
 template <typename T>
 int launch_factored(const Workspace& w, const FactoredArgs& a, bool aligned, glsdm_stream_t stream) {
   const int grid = blocks_for((a.entries + 31) / 32, kWarpsPerBlock);
@@ -387,6 +641,12 @@ int launch_factored(const Workspace& w, const FactoredArgs& a, bool aligned, gls
 }  // namespace glsdm
 
 using namespace glsdm;
+
+extern "C" int glsdm_commit_factored_mode(int mode) {
+  const int before = once_mode().load();
+  if (mode >= -1 && mode <= 1) once_mode().store(mode);
+  return before;
+}
 
 extern "C" size_t glsdm_commit_factored_workspace_bytes(int64_t entries, int32_t dim) {
   if (entries < 0 || dim < 1) return 0;
@@ -438,18 +698,42 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   const size_t need = carve_factored(&w, &f, static_cast<char*>(workspace), entries, v.dim);
   if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
 
-  if (phases & GLSDM_COMMIT_ORDER) {
+  // 16-byte loads of error rows and bank rows need aligned bases and row offsets.
+  const bool aligned = (reinterpret_cast<uintptr_t>(error) & 15u) == 0 &&
+                       (reinterpret_cast<uintptr_t>(bank->values) & 15u) == 0 &&
+                       (error_stride % 4 == 0 || block_rows >= rows) && v.dim % 4 == 0;
+  const bool once = offsets == nullptr && aligned &&
+                    once_path_pays(entries, static_cast<int64_t>(v.heads) * v.part_stride_rows) &&
+                    (v.dim == 32 || v.dim == 64 || v.dim == 128 || v.dim == 256);
+  if (once) w.live = f.live;
   EntryArgs e;
+  {
   e.index = index; e.weights = weights; e.error = error; e.mass = mass; e.offsets = offsets;
   e.rows = rows; e.block_rows = block_rows; e.route_stride = route_stride; e.error_stride = error_stride;
   e.tokens = tokens; e.sequences = rows / (static_cast<int64_t>(v.heads) * tokens); e.chunk_offset = chunk_offset; e.key_stride = chunk_size * num_layers;
   e.width = width; e.num_layers = num_layers; e.layer_index = layer_index;
+  }
+  if (phases & GLSDM_COMMIT_ORDER) {
+  if (once) {
+    const int row_blocks = blocks_for(rows, kWarpsPerBlock);
+    GLSDM_CUDA_OK(cudaMemsetAsync(f.seen, 0, (static_cast<size_t>(f.bit_mask) + 1) / 8 * 2, stream),
+                  "factored address map clear");
+    mark_addresses_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
+    count_shared_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
+    scan_shared_kernel<<<1, 1024, 0, stream>>>(f.block_shared, row_blocks, f.live);
+    compact_shared_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f, device_status);
+    GLSDM_CUDA_OK(cudaGetLastError(), "factored address map launches");
+    count_launches(3);
+  } else {
   factored_entries_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
   GLSDM_CUDA_OK(cudaGetLastError(), "factored entries launch");
+  }
   // Dense numbering sorts by address alone (one value past the last address marks a slot
   // outside the bank).
+  // The compacted list of the single-writer path holds no such slot: one value fewer.
+  const int64_t largest_key = static_cast<int64_t>(v.heads) * v.slots - (once ? 1 : 0);
   int address_bits = 1;
-  while ((static_cast<int64_t>(v.heads) * v.slots) >> address_bits) ++address_bits;
+  while (largest_key >> address_bits) ++address_bits;
   const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
   if (int s = run_sort(w, f.keys, entries, passes, stream)) return s;
   gather_factored_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, f, entries);
@@ -466,10 +750,17 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   a.bank_rows = static_cast<int64_t>(v.heads) * v.part_stride_rows;
   a.dim = v.dim;
   a.device_status = device_status;
-  // 16-byte loads of error rows and bank rows need aligned bases and row offsets.
-  const bool aligned = (reinterpret_cast<uintptr_t>(error) & 15u) == 0 &&
-                       (reinterpret_cast<uintptr_t>(bank->values) & 15u) == 0 &&
-                       (error_stride % 4 == 0 || block_rows >= rows) && v.dim % 4 == 0;
+  if (once) {
+    int s = GLSDM_OK;
+    const bool f32 = bank->dtype == GLSDM_F32;
+    switch (v.dim) {
+      case 32: s = f32 ? launch_once<float, 1>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 1>(v, e, f, a.values, stream); break;
+      case 64: s = f32 ? launch_once<float, 2>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 2>(v, e, f, a.values, stream); break;
+      case 128: s = f32 ? launch_once<float, 4>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 4>(v, e, f, a.values, stream); break;
+      default: s = f32 ? launch_once<float, 8>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 8>(v, e, f, a.values, stream); break;
+    }
+    if (s != GLSDM_OK) return s;
+  }
   if (bank->dtype == GLSDM_F32) return launch_factored<float>(w, a, aligned, stream);
   return launch_factored<__nv_bfloat16>(w, a, aligned, stream);
 }

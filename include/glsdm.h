@@ -287,6 +287,14 @@ int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_t* index, c
                                  int32_t key_bits, int32_t phases, void* workspace, size_t workspace_bytes,
                                  uint32_t* device_status, glsdm_stream_t stream);
 
+/* How glsdm_commit_factored treats rows that a single entry writes (dense numbering only):
+ * 1 = such rows are found with two bit maps over the addresses and updated straight from the
+ * routes, only the entries of shared addresses are sorted; 0 = every entry is sorted;
+ * -1 (default) = 1 when the commit is large and sparse enough for it to pay (at least 2^19
+ * entries, eight bank rows per entry), else 0. Any other value only queries. Returns the
+ * previous setting. The committed bank is bit-identical whichever runs. */
+int glsdm_commit_factored_mode(int mode);
+
 /* Commit for hosts that cannot provide a workspace. It has no counterpart in the reference
  * (whose commit allocates freely through PyTorch). Same arguments and result as glsdm_commit,
  * minus the workspace: the sort/reduce scratch is a 4 MiB array built into the library's
