@@ -565,7 +565,7 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
         gbs = plain["commit"] / (phase["commit"] / 1e3) / 1e9
         extra = {"delta_row_commit_equivalent_GBs": gbs, "delta_row_commit_equivalent_frac": gbs / peaks["hbm_gbs"]}
     names = ({"read": "pk_select_read_kernel", "propose": "pk_select_read_kernel + write_error_kernel",
-              "commit": "factored commit (apply_once_kernel for single-writer rows; radix sort + reduce_factored_kernel for the rest)"} if runner.op.factored else
+              "commit": "factored commit (apply_split_kernel: single-writer rows straight from the routes, shared addresses from a sorted list)"} if runner.op.factored else
              {"read": "pk_select_read_kernel", "propose": "pk_propose_kernel", "commit": "commit (radix sort + reduce_kernel)"})
     return {"bound": "hbm", "kernel": names[dominant], "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind}",

@@ -225,10 +225,9 @@ struct FactoredArgs {
 constexpr int kFactoredBatch = 2;   // single-entry rows in flight per warp (as in the delta-row reducer)
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
-reduce_factored_kernel(Workspace w, FactoredArgs a) {
+__device__ __forceinline__ void reduce_factored_block(const Workspace& w, const FactoredArgs& a, int64_t block) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp) * 32;
+  const int64_t first = (block * kWarpsPerBlock + warp) * 32;
   const int64_t entries = live_entries(w.live, a.entries);
   if (first >= entries) return;
   const int64_t* __restrict__ sorted = w.sorted_address;
@@ -326,6 +325,12 @@ reduce_factored_kernel(Workspace w, FactoredArgs a) {
       }
     }
   }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+reduce_factored_kernel(Workspace w, FactoredArgs a) {
+  reduce_factored_block<T, V>(w, a, blockIdx.x);
 }
 
 // One block per queued long segment: 256-entry chunks summed in order by warps (each warp
@@ -542,10 +547,10 @@ compact_shared_kernel(BankView bank, EntryArgs a, FactoredScratch f, uint32_t* d
 constexpr int kOnceBatch = 4;   // bank rows in flight per warp (2 measures the same, 8 is 40 % slower)
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
-apply_once_kernel(BankView bank, EntryArgs a, FactoredScratch f, void* bank_values) {
+__device__ __forceinline__ void apply_once_block(const BankView& bank, const EntryArgs& a, const FactoredScratch& f,
+                                                 void* bank_values, int64_t block_index) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  const int64_t major = block_index * kWarpsPerBlock + warp;
   if (major >= a.rows) return;
   const int64_t row = caller_row(bank, a, major);
   const DenseLane l = dense_lane(bank, a, row, lane);
@@ -589,12 +594,28 @@ apply_once_kernel(BankView bank, EntryArgs a, FactoredScratch f, void* bank_valu
   }
 }
 
+// Both kinds of rows in one launch: the first `shared_blocks` blocks reduce the sorted list of
+// the shared addresses (few entries, but each segment is summed in sequence: started first,
+// they finish under the bulk), the others update the single-writer rows. The two sets of rows
+// are disjoint.
 template <typename T, int V>
-int launch_once(const BankView& v, const EntryArgs& e, const FactoredScratch& f, void* values,
-                glsdm_stream_t stream) {
-  apply_once_kernel<T, V><<<blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f, values);
-  GLSDM_CUDA_OK(cudaGetLastError(), "factored single-writer launch");
-  count_launches(1);
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+apply_split_kernel(Workspace w, FactoredArgs a, BankView bank, EntryArgs e, FactoredScratch f, int shared_blocks) {
+  if (static_cast<int>(blockIdx.x) < shared_blocks) reduce_factored_block<T, V>(w, a, blockIdx.x);
+  else apply_once_block<T, V>(bank, e, f, a.values, static_cast<int64_t>(blockIdx.x) - shared_blocks);
+}
+
+template <typename T, int V>
+int launch_split(const Workspace& w, const FactoredArgs& a, const BankView& v, const EntryArgs& e,
+                 const FactoredScratch& f, glsdm_stream_t stream) {
+  const int shared_blocks = blocks_for((a.entries + 31) / 32, kWarpsPerBlock);
+  const int long_grid = static_cast<int>(w.long_capacity < 1184 ? w.long_capacity : 1184);
+  apply_split_kernel<T, V><<<shared_blocks + blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(
+      w, a, v, e, f, shared_blocks);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored split apply launch");
+  long_factored_kernel<T, V><<<long_grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored long-segment launch");
+  count_launches(2);
   return GLSDM_OK;
 }
 
@@ -751,15 +772,13 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   a.dim = v.dim;
   a.device_status = device_status;
   if (once) {
-    int s = GLSDM_OK;
     const bool f32 = bank->dtype == GLSDM_F32;
     switch (v.dim) {
-      case 32: s = f32 ? launch_once<float, 1>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 1>(v, e, f, a.values, stream); break;
-      case 64: s = f32 ? launch_once<float, 2>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 2>(v, e, f, a.values, stream); break;
-      case 128: s = f32 ? launch_once<float, 4>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 4>(v, e, f, a.values, stream); break;
-      default: s = f32 ? launch_once<float, 8>(v, e, f, a.values, stream) : launch_once<__nv_bfloat16, 8>(v, e, f, a.values, stream); break;
+      case 32: return f32 ? launch_split<float, 1>(w, a, v, e, f, stream) : launch_split<__nv_bfloat16, 1>(w, a, v, e, f, stream);
+      case 64: return f32 ? launch_split<float, 2>(w, a, v, e, f, stream) : launch_split<__nv_bfloat16, 2>(w, a, v, e, f, stream);
+      case 128: return f32 ? launch_split<float, 4>(w, a, v, e, f, stream) : launch_split<__nv_bfloat16, 4>(w, a, v, e, f, stream);
+      default: return f32 ? launch_split<float, 8>(w, a, v, e, f, stream) : launch_split<__nv_bfloat16, 8>(w, a, v, e, f, stream);
     }
-    if (s != GLSDM_OK) return s;
   }
   if (bank->dtype == GLSDM_F32) return launch_factored<float>(w, a, aligned, stream);
   return launch_factored<__nv_bfloat16>(w, a, aligned, stream);
