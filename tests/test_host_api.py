@@ -176,3 +176,43 @@ def test_overlay_commit_bookkeeping(monkeypatch):
     commit(w1, merge(w1, [proposal(w1, 5)]), donate=True)
     with pytest.raises(RuntimeError, match="invalidated"):
         w0.values
+
+
+def test_token_clock_backward_wiring_against_reference_gradients(monkeypatch):
+    """The host side of the differentiable token-clock read / write proposal (what is saved,
+    which cotangent goes where) checked on the CPU: the three kernel entry points it calls are
+    replaced by tensor expressions of what they compute, the gradients must then be the
+    reference's autograd (tests/golden/token_gradients.npz). The kernels themselves are
+    checked against the same file in tests/test_gpu_backward.py."""
+    import numpy as np
+    import golden_inputs as gi
+    from conftest import load_golden
+    from gl_sdm_b200 import _native
+
+    def snapshot_read(values, index, weights, rows_per_bank, requests=None, **_):
+        heads, slots = values.shape[1:3]
+        flat = (requests.view(-1, 1, 1) * heads + torch.arange(heads).view(1, heads, 1)) * slots + index
+        return (values.flatten(0, 2)[flat].float() * weights.unsqueeze(-1)).sum(-2)
+
+    def commit_rows(values, idx, delta, keys, out=None, key_bits=0):
+        return out.index_add_(0, idx, delta)
+
+    monkeypatch.setattr(_native, "require_cuda", lambda *a: None)
+    monkeypatch.setattr(_native, "snapshot_read", snapshot_read)
+    monkeypatch.setattr(_native, "gather_rows", lambda flat, addresses: flat[addresses])
+    monkeypatch.setattr(_native, "commit_rows", commit_rows)
+    gold = load_golden("token_gradients")
+    t = gi.token_case()
+    names = ("memory", "weights", "targets", "beta", "log_decay", "mass")
+    leaves = {k: t[k].clone().requires_grad_() for k in names}
+    view = MemoryView(leaves["memory"])
+    retrieved = read(view, t["requests"], t["indices"], leaves["weights"])
+    p = propose_write(view, t["requests"], t["indices"], leaves["weights"], leaves["targets"], leaves["beta"],
+                      leaves["log_decay"], leaves["mass"])
+    cot_read, cot_delta = gi.cotangents("token", retrieved.shape, p.deltas.shape)
+    grads = torch.autograd.grad((retrieved * cot_read).sum(), (leaves["memory"], leaves["weights"]))
+    np.testing.assert_allclose(grads[0].numpy(), gold["read_grad_memory"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(grads[1].numpy(), gold["read_grad_weights"], rtol=1e-5, atol=1e-5)
+    grads = torch.autograd.grad((p.deltas * cot_delta).sum(), [leaves[k] for k in names])
+    for k, g in zip(names, grads):
+        np.testing.assert_allclose(g.numpy(), gold[f"propose_grad_{k}"], rtol=1e-4, atol=1e-5, err_msg=k)
