@@ -629,12 +629,14 @@ std::atomic<int>& once_mode() {
   return mode;
 }
 
-// The bit maps, the compaction and the second reducer cost ~10 launches: they pay once the
+// The bit maps and the compaction cost ~6 launches more than they save: they pay once the
 // sort they avoid is large (entries) and most rows have one writer (bank rows per entry).
+// Measured with 512-byte rows: even at 524,288 entries, 4-8 % faster at 1,048,576 entries with
+// 4 to 16 bank rows per entry, 3-20 % slower at 262,144 entries and below.
 bool once_path_pays(int64_t entries, int64_t bank_rows) {
   const int mode = once_mode().load();
   if (mode >= 0) return mode == 1;
-  return entries >= (int64_t{1} << 19) && bank_rows >= 8 * entries;
+  return entries >= 3 * (int64_t{1} << 18) && bank_rows >= 4 * entries;
 }
 
 template <typename T>

@@ -290,8 +290,8 @@ int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_t* index, c
 /* How glsdm_commit_factored treats rows that a single entry writes (dense numbering only):
  * 1 = such rows are found with two bit maps over the addresses and updated straight from the
  * routes, only the entries of shared addresses are sorted; 0 = every entry is sorted;
- * -1 (default) = 1 when the commit is large and sparse enough for it to pay (at least 2^19
- * entries, eight bank rows per entry), else 0. Any other value only queries. Returns the
+ * -1 (default) = 1 when the commit is large and sparse enough for it to pay (at least
+ * 786,432 entries, four bank rows per entry), else 0. Any other value only queries. Returns the
  * previous setting. The committed bank is bit-identical whichever runs. */
 int glsdm_commit_factored_mode(int mode);
 

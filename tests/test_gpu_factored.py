@@ -104,11 +104,11 @@ def test_slot_outside_the_bank_is_reported_and_dropped(native, commit_mode):
 
 
 def test_large_sparse_commit_defaults_to_the_single_writer_path(native):
-    """524,288 entries on 4,194,304 slots: the size from which the default leaves single-writer
-    rows unsorted. Same bank, bit for bit, as with every entry sorted."""
+    """1,048,576 entries on 4,194,304 slots: large and sparse enough for the default to leave
+    single-writer rows unsorted. Same bank, bit for bit, as with every entry sorted."""
     from gl_sdm_b200.operator import SharedBankOperator
     lib = native.library()
-    seqs, T, half, D, K = 32, 512, 2048, 32, 32
+    seqs, T, half, D, K = 64, 512, 2048, 32, 32
     g = torch.Generator(device=DEV).manual_seed(3)
     bank = (torch.randn(1, 1, half * half, D, generator=g, device=DEV) * 0.05).to(torch.bfloat16)
     k = torch.randn(seqs, T, 1, 2 * half, generator=g, device=DEV)
