@@ -174,3 +174,40 @@ def chain_case():
                 target=torch.randn(B, T, H, D, generator=g), beta=torch.rand(B, T, H, generator=g),
                 log_decay=-torch.rand(B, T, H, generator=g) * 0.3, width=K,
                 cotangent=torch.randn(B, H, half * half, D, generator=g))
+
+
+def c1_step_case():
+    """Bank and per-(epoch, layer) inputs of the smallest benchmark configuration, drawn on
+    the CPU so that every machine rebuilds the same tensors."""
+    from gl_sdm_b200 import workloads
+    w = workloads.WORKLOADS["c1"]
+    values = workloads.make_bank(w, "cpu")
+    inputs = [[workloads.make_epoch_inputs(w, "cpu", 1000 + 100 * e + layer) for layer in range(w.global_layers)]
+              for e in range(w.epochs)]
+    return w, values, inputs
+
+
+def c1_step_digest(bank, readings):
+    """What the fixture keeps of a step's results: float64 sums per (request, head) and 256
+    sampled rows of the banks, the same for the readings."""
+    g = torch.Generator().manual_seed(5)
+    bank, readings = bank.detach().cpu(), readings.detach().cpu()
+    flat = bank.flatten(0, 2)
+    rows_at = torch.randint(0, flat.shape[0], (256,), generator=g)
+    read_flat = readings.flatten(0, 2)
+    read_at = torch.randint(0, read_flat.shape[0], (256,), generator=g)
+    return dict(bank_sum=bank.double().sum((2, 3)).numpy(), bank_abs=bank.double().abs().sum((2, 3)).numpy(),
+                rows_at=rows_at.numpy(), rows=flat[rows_at].numpy(),
+                readings_sum=readings.double().sum((1, 3)).numpy(), read_at=read_at.numpy(),
+                read_rows=read_flat[read_at].numpy())
+
+
+def assert_c1_step(bank, readings, gold, rtol):
+    """Compare a step's results with the stored digest of the reference's."""
+    import numpy as np
+    digest = c1_step_digest(bank, readings)
+    assert np.array_equal(digest["rows_at"], gold["rows_at"]) and np.array_equal(digest["read_at"], gold["read_at"])
+    np.testing.assert_allclose(digest["rows"], gold["rows"], rtol=rtol, atol=1e-6)
+    np.testing.assert_allclose(digest["read_rows"], gold["read_rows"], rtol=rtol, atol=1e-6)
+    for k in ("bank_sum", "bank_abs", "readings_sum"):
+        np.testing.assert_allclose(digest[k], gold[k], rtol=1e-6, atol=1e-4, err_msg=k)

@@ -367,3 +367,21 @@ def test_long_factor_selection_is_exact_on_awkward_rows(native, half, width):
     np.testing.assert_array_equal(cpu(index), want_index)
     finite = np.isfinite(want_weights).all(axis=-1)
     np.testing.assert_allclose(cpu(weights)[finite], want_weights[finite], rtol=1e-5, atol=1e-6)
+
+
+def test_c1_step_through_the_memory_api_matches_the_reference(native):
+    """The smallest benchmark configuration, one whole step (two commit epochs) through
+    gl_sdm_b200.memory with the call sequence bench.py times, against the same step driven
+    through the reference's gl_sdm.memory (tests/golden/c1_step.npz)."""
+    import bench
+    import gl_sdm_b200.memory as memory
+    gold = load_golden("c1_step")
+    w, values, inputs = gi.c1_step_case()
+    moved = [[{k: v.to(DEV) for k, v in x.items()} for x in layers] for layers in inputs]
+    before = values.clone()
+    on_device = values.to(DEV)
+    readings, view = bench.api_step(w, on_device, moved, memory)
+    assert view.version == w.epochs
+    assert torch.equal(on_device.cpu(), before)        # functional commits: the input bank is untouched
+    gi.assert_c1_step(view.values, readings, gold, rtol=1e-5)
+    native.raise_on_device_status(DEV)

@@ -149,3 +149,16 @@ def test_oracle_backward_matches_reference_autograd(name):
     untouched = np.ones(flat.shape[0], bool)
     untouched[gold[f"{name}_touched"]] = False
     assert not flat[untouched].any()
+
+
+def test_cpu_port_runs_the_c1_step_like_the_reference():
+    """The timed CPU baseline of the per-request configurations (bench.PortMemory behind
+    bench.api_step) against the same step driven through the reference's gl_sdm.memory."""
+    import bench
+    gold = load_golden("c1_step")
+    w, values, inputs = gi.c1_step_case()
+    drawn = [gi.checksum(values)] + [gi.checksum(x[k]) for layers in inputs for x in layers for k in sorted(x)]
+    np.testing.assert_allclose(drawn, gold["checksum"], rtol=1e-12)
+    readings, view = bench.api_step(w, values.clone(), inputs, bench.PortMemory())
+    assert view.version == w.epochs
+    gi.assert_c1_step(view.values, readings, gold, rtol=1e-5)
