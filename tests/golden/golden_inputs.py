@@ -176,11 +176,16 @@ def chain_case():
                 cotangent=torch.randn(B, H, half * half, D, generator=g))
 
 
-def c1_step_case():
-    """Bank and per-(epoch, layer) inputs of the smallest benchmark configuration, drawn on
-    the CPU so that every machine rebuilds the same tensors."""
+STEP_CASES = ("c1_step", "c2_chunk_step")
+
+
+def c1_step_case(name="c1_step"):
+    """Bank and per-(epoch, layer) inputs of a benchmark configuration with per-request banks,
+    drawn on the CPU so that every machine rebuilds the same tensors: "c1_step" is all of c1
+    (2 x 1024 tokens, one layer), "c2_chunk_step" one request and one 512-token chunk of c2
+    (eight global layers writing into one commit)."""
     from gl_sdm_b200 import workloads
-    w = workloads.WORKLOADS["c1"]
+    w = workloads.WORKLOADS["c1"] if name == "c1_step" else workloads.WORKLOADS["c2"].scaled(sequences=1, seq_len=512)
     values = workloads.make_bank(w, "cpu")
     inputs = [[workloads.make_epoch_inputs(w, "cpu", 1000 + 100 * e + layer) for layer in range(w.global_layers)]
               for e in range(w.epochs)]

@@ -42,9 +42,10 @@ def main(reference_root, only=None):
             rec["memory"], rec["scores"] = memory.numpy(), scores.numpy()
         np.savez_compressed(os.path.join(HERE, f"routed_{name}.npz"), **rec)
         out[f"routed_{name}"] = tuple(index.shape)
-    if only and "c1_step" in only:
-        write_c1_step(reference_root)
-        out["c1_step"] = ()
+    for name in gi.STEP_CASES:
+        if only and name in only:
+            write_c1_step(reference_root, name)
+            out[name] = ()
     if only and "token_gradients" in only:
         write_token_gradients(MemoryView, read, propose_write)
         out["token_gradients"] = ()
@@ -139,13 +140,14 @@ def main(reference_root, only=None):
     np.savez_compressed(os.path.join(HERE, "token_api.npz"), read=retrieved.numpy(), addresses=p.addresses.numpy(),
                         deltas=p.deltas.numpy(), deltas2=p2.deltas.numpy(), updated=updated.values.numpy())
     write_token_gradients(MemoryView, read, propose_write)
-    write_c1_step(reference_root)
-    print("wrote", sorted(out), "commit_cases token_api token_gradients c1_step")
+    for name in gi.STEP_CASES:
+        write_c1_step(reference_root, name)
+    print("wrote", sorted(out), "commit_cases token_api token_gradients", *gi.STEP_CASES)
 
 
-def write_c1_step(reference_root):
-    """One whole step of the smallest benchmark configuration (2 x 1024 tokens, two commit
-    epochs) driven through the reference's own gl_sdm.memory with the call sequence the
+def write_c1_step(reference_root, name):
+    """One whole step of a per-request-bank benchmark configuration (golden_inputs.STEP_CASES)
+    driven through the reference's own gl_sdm.memory with the call sequence the
     benchmark times (bench.api_step). Stored: float64 sums per (request, head) and sampled
     rows of the final banks and of the last chunk's readings."""
     sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
@@ -153,12 +155,12 @@ def write_c1_step(reference_root):
     import bench
     import gl_sdm.memory as reference_memory
     from gl_sdm.memory import routing as reference_routing
-    w, values, inputs = gi.c1_step_case()
+    w, values, inputs = gi.c1_step_case(name)
     memory = types.SimpleNamespace(MemoryView=reference_memory.MemoryView, WriteProposal=reference_memory.WriteProposal,
                                    merge=reference_memory.merge, commit=reference_memory.commit, routing=reference_routing)
     readings, view = bench.api_step(w, values.clone(), inputs, memory)
     assert view.version == w.epochs
-    np.savez_compressed(os.path.join(HERE, "c1_step.npz"), **gi.c1_step_digest(view.values, readings),
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **gi.c1_step_digest(view.values, readings),
                         checksum=np.array([gi.checksum(values)] + [gi.checksum(x[k]) for layers in inputs for x in layers
                                                                    for k in sorted(x)]))
 

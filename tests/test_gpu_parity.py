@@ -369,14 +369,16 @@ def test_long_factor_selection_is_exact_on_awkward_rows(native, half, width):
     np.testing.assert_allclose(cpu(weights)[finite], want_weights[finite], rtol=1e-5, atol=1e-6)
 
 
-def test_c1_step_through_the_memory_api_matches_the_reference(native):
-    """The smallest benchmark configuration, one whole step (two commit epochs) through
+@pytest.mark.parametrize("name", gi.STEP_CASES)
+def test_c1_step_through_the_memory_api_matches_the_reference(native, name):
+    """The per-request-bank benchmark configurations (all of c1: two commit epochs; one request
+    and chunk of c2: eight layers writing into one commit), one whole step through
     gl_sdm_b200.memory with the call sequence bench.py times, against the same step driven
-    through the reference's gl_sdm.memory (tests/golden/c1_step.npz)."""
+    through the reference's gl_sdm.memory (tests/golden/c1_step.npz, c2_chunk_step.npz)."""
     import bench
     import gl_sdm_b200.memory as memory
-    gold = load_golden("c1_step")
-    w, values, inputs = gi.c1_step_case()
+    gold = load_golden(name)
+    w, values, inputs = gi.c1_step_case(name)
     moved = [[{k: v.to(DEV) for k, v in x.items()} for x in layers] for layers in inputs]
     before = values.clone()
     on_device = values.to(DEV)

@@ -151,12 +151,13 @@ def test_oracle_backward_matches_reference_autograd(name):
     assert not flat[untouched].any()
 
 
-def test_cpu_port_runs_the_c1_step_like_the_reference():
+@pytest.mark.parametrize("name", gi.STEP_CASES)
+def test_cpu_port_runs_the_c1_step_like_the_reference(name):
     """The timed CPU baseline of the per-request configurations (bench.PortMemory behind
     bench.api_step) against the same step driven through the reference's gl_sdm.memory."""
     import bench
-    gold = load_golden("c1_step")
-    w, values, inputs = gi.c1_step_case()
+    gold = load_golden(name)
+    w, values, inputs = gi.c1_step_case(name)
     drawn = [gi.checksum(values)] + [gi.checksum(x[k]) for layers in inputs for x in layers for k in sorted(x)]
     np.testing.assert_allclose(drawn, gold["checksum"], rtol=1e-12)
     readings, view = bench.api_step(w, values.clone(), inputs, bench.PortMemory())
