@@ -114,6 +114,13 @@ def require_cuda(*tensors):
             raise ValueError("GL-SDM native kernels require contiguous CUDA tensors")
 
 
+def require_device(*tensors):
+    """Operands that the wrappers make contiguous themselves still have to live on a GPU."""
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("GL-SDM native kernels require contiguous CUDA tensors")
+
+
 def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 

@@ -157,6 +157,7 @@ extern "C" int glsdm_overlay_read(const glsdm_bank* bank, const void* index, int
   if (index == nullptr || weights == nullptr || out_read == nullptr || rows < 0 || rows_per_bank < 1)
     return GLSDM_ERR_ARGUMENT;
   if (width < 1 || n_logs < 0) return GLSDM_ERR_ARGUMENT;
+  if (bank->banks < 1 || (bank->banks > 1 && rows > bank->banks * rows_per_bank)) return GLSDM_ERR_ARGUMENT;
   if (width > 32) return GLSDM_ERR_UNSUPPORTED;
   if (n_logs > kMaxLogs) return GLSDM_ERR_LIMIT;
   if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;

@@ -407,6 +407,9 @@ extern "C" int glsdm_snapshot_read(const glsdm_bank* bank, const void* index, in
   if (int s = check_bank(bank)) return s;
   if (index == nullptr || weights == nullptr || out_read == nullptr || rows < 0) return GLSDM_ERR_ARGUMENT;
   if (width < 1 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (requests == nullptr) {
+    if (int s = check_rows(bank, rows, rows_per_bank)) return s;
+  }
   if (width > 32) return GLSDM_ERR_UNSUPPORTED;
   if (rows == 0) return GLSDM_OK;
   const BankView v = make_view(*bank);
@@ -461,6 +464,7 @@ extern "C" int glsdm_pk_select_read(const glsdm_bank* bank, const float* scores,
   int kf, kout;
   if (int s = route_shape(half, width, &kf, &kout)) return s;
   if (scores == nullptr || out_read == nullptr || rows < 0 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (int s = check_rows(bank, rows, rows_per_bank)) return s;
   if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
   if ((half & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u)) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
@@ -513,6 +517,7 @@ extern "C" int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, con
   if (rows < 0 || rows_per_bank < 1 || tokens < 1 || chunk_size < 1 || num_layers < 1 ||
       layer_index < 0 || layer_index >= num_layers || chunk_offset < 0)
     return GLSDM_ERR_ARGUMENT;
+  if (int s = check_rows(bank, rows, rows_per_bank)) return s;
   if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
   if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
   if (target_dtype != GLSDM_F32 && target_dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
@@ -617,6 +622,7 @@ extern "C" int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out
       grad_rows == nullptr || out_addresses == nullptr)
     return GLSDM_ERR_ARGUMENT;
   if (rows < 0 || rows_per_bank < 1 || width < 1 || half < 1) return GLSDM_ERR_ARGUMENT;
+  if (int s = check_rows(bank, rows, rows_per_bank)) return s;
   if (width > 32) return GLSDM_ERR_UNSUPPORTED;
   if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
   if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;

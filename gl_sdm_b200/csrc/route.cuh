@@ -40,6 +40,15 @@ inline int check_bank(const glsdm_bank* b) {
   return GLSDM_OK;
 }
 
+// Routing rows are laid out [bank, token, head]: with per-request banks, row r reads bank
+// r / rows_per_bank, so more rows than banks * rows_per_bank would index past the last bank.
+// (A single shared bank serves any number of rows; a request table is checked on the device.)
+inline int check_rows(const glsdm_bank* b, int64_t rows, int64_t rows_per_bank) {
+  if (rows < 0 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (b->banks > 1 && rows > b->banks * rows_per_bank) return GLSDM_ERR_ARGUMENT;
+  return GLSDM_OK;
+}
+
 // Offer one factor's `half` scores (fp32, contiguous) to a selector; key = score | index.
 // This is the general path (any length, any alignment, any score distribution); the bounded
 // selections below take the common shapes and fall back to it.

@@ -1,6 +1,9 @@
 """The three names the reference calls on its external-read backend
 (gl_sdm/memory/backends/urm.py:40-46,49-82,109-122), served by the in-tree kernels."""
+import torch
+
 from ... import _native
+from .. import autograd
 
 
 def verify_dependency():
@@ -21,8 +24,19 @@ def snapshot_read(values, addresses, weights):
 
 
 def routed_snapshot_read(values, scores, width, allow_large_route=False):
-    """Fused route + read; int32 indices as the reference's native path returns them."""
-    import torch
+    """Fused route + read of scores [B, T, H, 2*half] against values [B, H, S, D] (the logical
+    bank or the reference's zero-padded physical one, layers/stack.py:50-51); int32 indices as
+    the reference's native path returns them (memory/backends/urm.py:109-122). Differentiable
+    in the bank and the scores."""
+    _native.require_cuda(values)
+    if scores.ndim != 4 or values.ndim != 4:
+        raise ValueError("routed_snapshot_read expects values [B, H, S, D] and scores [B, T, H, 2*half]")
+    _native.require_device(scores)
     B, T, H, _ = scores.shape
+    if values.shape[0] not in (1, B) or values.shape[1] != H:
+        raise ValueError("scores and memory disagree on batch or heads")
+    if autograd.needs_grad(values, scores):
+        readings, index, weights = autograd.RoutedRead.apply(values, scores, width)
+        return readings, index.to(torch.int32), weights
     return _native.pk_select_read(values, scores.float().contiguous(), width, rows_per_bank=T * H,
                                   index_dtype=torch.int32)

@@ -19,8 +19,7 @@ def torch_routed_read(memory, scores, width, reference=False):
     if reference:
         return oracle_hook.get("routed_read")(memory, scores, width)
     _native.require_cuda(memory)
-    if not scores.is_cuda:
-        raise ValueError("GL-SDM native kernels require contiguous CUDA tensors")
+    _native.require_device(scores)
     B, T, H, _ = scores.shape
     if memory.shape[0] not in (1, B) or memory.shape[1] != H:
         raise ValueError("scores and memory disagree on batch or heads")

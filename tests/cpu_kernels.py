@@ -96,3 +96,51 @@ def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_s
                             num_layers, layer_index, out)
     flat = shard.view(-1, D)
     commit_rows(flat, a, d, s, out=flat, key_bits=key_bits)
+
+
+# --- stand-ins for the entry points gl_sdm_b200.memory calls (chunk-clock API) ---------------
+# Used by tests/test_ref_stack_cpu.py to run the host side of the package shim (views, caches,
+# pending proposals, the commit clock, autograd wiring) under the unmodified reference stack
+# on a machine without a GPU. They are built from oracle/torch_port.py.
+
+def memory_api_standins():
+    from oracle import torch_port as port
+
+    def require_cuda(*tensors):
+        return None
+
+    def pk_select_read(values, scores, width, rows_per_bank, want_routes=True, index_dtype=torch.int64,
+                       slot_lo=0, slots=None):
+        readings, index, weights = port.routed_read(values, scores, width)
+        return readings, index.to(index_dtype), weights
+
+    def gather_rows(flat, addresses):
+        return flat[addresses]
+
+    def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_base=0):
+        new = port.commit(values, addresses, deltas, keys)
+        if out is None:
+            return new
+        out.copy_(new)
+        return out
+
+    def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half):
+        lead, width, dim = index.shape[:-1], index.shape[-1], values.shape[-1]
+        if index.ndim == 4:
+            addresses = port.flat_rows(values, index.long())
+        else:
+            raise ValueError("stand-in expects [B, T, H, K] routes")
+        rows = values.flatten(0, 2)[addresses].float()
+        grad_w = (rows * grad_out.unsqueeze(-2)).sum(-1)
+        if grad_weights is not None:
+            grad_w = grad_w + grad_weights
+        grad_sum = weights * (grad_w - (grad_w * weights).sum(-1, keepdim=True))   # softmax backward
+        grad_scores = torch.zeros(*lead, 2 * half)
+        idx = index.long()
+        grad_scores.scatter_add_(-1, idx // half, grad_sum)
+        grad_scores.scatter_add_(-1, half + idx % half, grad_sum)
+        grad_rows = (weights.unsqueeze(-1) * grad_out.unsqueeze(-2)).reshape(-1, dim)
+        return grad_scores, addresses.reshape(-1), grad_rows
+
+    return dict(require_cuda=require_cuda, require_device=require_cuda, pk_select_read=pk_select_read, gather_rows=gather_rows,
+                commit_rows=commit_rows, read_backward=read_backward)

@@ -52,6 +52,26 @@ def test_argument_errors_need_no_device(native):
     assert lib.glsdm_topk_merge(fake, fake, 2, 4, 40, fake, 1, fake, null) == 2
 
 
+def test_rows_beyond_the_banks_are_rejected_before_any_launch(native):
+    """Per-request banks: routing row r reads bank r / rows_per_bank, so a call whose rows do
+    not fit banks * rows_per_bank would read past the last bank. Every entry that takes
+    rows_per_bank must refuse it on the host (nothing is launched; the pointers are fake)."""
+    lib = native.library()
+    null, fake = ctypes.c_void_p(0), ctypes.c_void_p(4096)
+    two = native.Bank(4096, 0, 2, 1, 16, 8, 0, 16)       # 2 banks, 1 head, 16 slots (half 4), dim 8
+    one = native.Bank(4096, 0, 1, 1, 16, 8, 0, 16)
+    ok, bad = 2 * 5, 2 * 5 + 1                            # rows_per_bank = 5
+    assert lib.glsdm_snapshot_read(ctypes.byref(two), fake, 1, fake, null, bad, 5, 2, fake, null, null) == 1
+    assert lib.glsdm_pk_select_read(ctypes.byref(two), fake, bad, 5, 4, 2, fake, fake, 1, fake, null, null) == 1
+    assert lib.glsdm_pk_propose(ctypes.byref(two), fake, fake, 0, fake, fake, null, bad, 5, 5, 4, 2, 0, 8, 1, 0,
+                                fake, fake, fake, null, null) == 1
+    assert lib.glsdm_read_backward(ctypes.byref(two), fake, null, fake, 1, fake, bad, 5, 2, 4, fake, fake, fake,
+                                   null) == 1
+    assert lib.glsdm_overlay_read(ctypes.byref(two), fake, 1, fake, bad, 5, 2, 0, null, null, null, fake, null,
+                                  null) == 1
+    del ok, one
+
+
 def test_score_topk_plans_cover_every_block_and_tile_once():
     """Host-side work decomposition of the dense-key routing kernels (no GPU involved): the
     uniform parts and the extra cuts of the last wave's row blocks tile rows x key tiles exactly."""

@@ -1,0 +1,122 @@
+"""The UNMODIFIED reference stack (gl_sdm/layers/stack.py and everything above it, staged
+under oracle/_ref) running on the CUDA kernels, against the same source on the reference's
+own torch path - both on the GPU, same parameters, same tokens.
+
+Two bindings are exercised: the package seam (gl_sdm_b200.install replaces gl_sdm.memory) and
+the backend seam (the reference's own memory package with gl_memory_backend="urm" calling
+gl_sdm_b200.memory.backends.urm / .commit). Bounds are the reference's own gate
+(gl_sdm/experiments/verify.py:98-165). Skipped when oracle/_ref is not staged.
+"""
+import types
+from unittest.mock import patch
+
+import pytest
+import torch
+
+import ref_package
+import ref_stack_checks as checks
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# widths of benchmark configuration 2; the clocked tests shorten the chunk so that a short
+# sequence crosses several commits
+FAST_CLOCK = dict(num_hidden_layers=4, gl_chunk_size=16, gl_local_window=16, vocab_size=4096)
+
+
+@pytest.fixture(autouse=True)
+def _staged(native):
+    ref_package.require()
+    yield
+    native.raise_on_device_status(DEV)
+
+
+def test_prefill_at_c2_widths_fp32():
+    """16 layers, 8 heads, 16,384 slots, 16 routes, 512-token chunks; 2 x 1024 tokens."""
+    out = checks.prefill_matches(ref_package.stack_config(), DEV, batch=2, length=1024, redraw=0.02)
+    assert out["commits"] == 2
+    print("c2-width fp32 prefill:", out)
+
+
+def test_gradients_fp32():
+    out = checks.gradients_match(ref_package.stack_config(**FAST_CLOCK), DEV, batch=2, length=65)
+    print("fp32 gradients:", out)
+
+
+def test_continuation_reset_causality_fast_clock():
+    out = checks.continuation_reset_causality(ref_package.stack_config(**FAST_CLOCK), DEV, batch=2, length=65)
+    print("continuation (16-token chunks):", out)
+
+
+def test_continuation_across_512_token_commits():
+    """17 + 1081 + 1 + 1 tokens: pending proposals carried between calls, commits at the
+    absolute positions 512 and 1024 (layers/stack.py:41-68)."""
+    out = checks.continuation_reset_causality(ref_package.stack_config(), DEV, batch=1, length=1100)
+    print("continuation (512-token chunks):", out)
+
+
+def test_teacher_forced_replay_bf16_at_c2_widths():
+    """bf16 weights (scores are bf16 GEMM outputs: exact ties at the selection boundary are
+    common): every call's routes bit-exact. The end-to-end drift of a free-running bf16 stack
+    is reported separately, bounded like the reference bounds bf16 runs (verify.py:19-28)."""
+    cfg = ref_package.stack_config(dtype="bfloat16")
+    seen = checks.teacher_forced_replay(cfg, DEV, batch=2, length=1024, redraw=0.02)
+    assert seen["reads"] == 32 and seen["commits"] == 2 and seen["entries"] == 2 * 2 * 512 * 8 * 16 * 8
+    assert seen["tie_rows"] > 0, "bf16 scores are expected to tie at the selection boundary"
+    want = seen.pop("logits")
+    shim = ref_package.load("shim")
+    reference, expected, _, actual = checks.seeded_pair(cfg, DEV, "shim", redraw=0.02)
+    actual.eval()
+    with shim:
+        got, _ = actual.prefill(checks.tokens(cfg, 2, 1024, DEV))
+    drift = checks.relative_l2(got, want)
+    print("bf16 replay:", seen, "free-running relative L2", drift)
+    assert drift < 0.05
+
+
+def test_backend_seam_prefill_and_gradients():
+    """verify.py:32-42: with gl_memory_backend="urm" the reference's memory package must reach
+    backends.urm.routed_snapshot_read and backends.commit.commit; both are ours here. Under
+    grad mode the stack hands the zero-padded 128-wide physical bank (stack.py:50-51)."""
+    from gl_sdm_b200.memory.backends import commit, urm
+    cfg = ref_package.stack_config(**FAST_CLOCK, gl_memory_backend="urm")
+    widths = []
+    inner = urm.routed_snapshot_read
+
+    def spy(values, scores, width, allow_large_route=False):
+        widths.append(values.shape[-1])
+        out = inner(values, scores, width, allow_large_route=allow_large_route)
+        assert out[1].dtype == torch.int32
+        return out
+
+    with patch.object(urm, "routed_snapshot_read", spy), patch.object(commit, "commit", wraps=commit.commit) as commits:
+        checks.prefill_matches(cfg, DEV, batch=2, length=65, kind="seam")
+        assert len(widths) == 2 * 2 * 5 and set(widths) == {64} and commits.call_count == 4
+        widths.clear()
+        checks.gradients_match(cfg, DEV, batch=2, length=65, kind="seam")
+        assert set(widths) == {128}, "the padded physical bank did not reach the read"
+        assert commits.call_count > 4
+
+
+def test_backend_seam_five_dimensional_scores():
+    """memory/routing.py:48-55: [batch, reasoning, token, head, factor] scores are split in
+    groups of passes, each flattened for the native read and reshaped back."""
+    seam, reference = ref_package.load("seam"), ref_package.load("reference")
+    gen = torch.Generator().manual_seed(11)
+    memory = (torch.randn(2, 3, 64 * 64, 64, generator=gen) * 0.1).to(DEV)
+    scores = torch.randn(2, 3, 700, 3, 128, generator=gen).bfloat16().float().to(DEV)
+    block = types.SimpleNamespace(attn=types.SimpleNamespace(reference=False, backend="urm", experimental_large_route=False))
+    physical = torch.nn.functional.pad(memory, (0, 64))
+    with seam:
+        got = seam.module("gl_sdm.memory.routing").routed_read(block, memory, scores, 8, physical)
+    with reference:
+        flat = reference.module("gl_sdm.memory.routing").torch_routed_read(memory, scores.flatten(1, 2), 8)
+    want = tuple(t.reshape(2, 3, 700, 3, -1) for t in flat)
+    assert got[0].shape == (2, 3, 700, 3, 64) and got[1].dtype == torch.int32
+    assert torch.equal(got[1].long(), want[1])
+    torch.testing.assert_close(got[2], want[2], atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(got[0], want[0], atol=1e-6, rtol=1e-5)
+    # the package seam takes the same call through its own dispatcher
+    from gl_sdm_b200.memory import routing as ours
+    mine = ours.routed_read(block, memory, scores, 8, physical)
+    assert mine[0].shape == (2, 3, 700, 3, 64) and torch.equal(mine[1], want[1])
+    torch.testing.assert_close(mine[0], want[0], atol=1e-6, rtol=1e-5)
