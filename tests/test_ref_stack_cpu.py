@@ -57,6 +57,11 @@ def test_teacher_forced_replay(standins):
     assert seen["reads"] == 2 * 2 * 3 and seen["commits"] == 2
 
 
+def test_audited_free_run(standins):
+    out = checks.audited_free_run(checks.ref_package.stack_config(**SMALL), "cpu", batch=2, length=40)
+    assert out["reads"] == 12 and out["commits"] == 2 and out["first_split_call"] is None
+
+
 def test_backend_seam_runs_the_stack(standins):
     """Config "urm": the reference's own memory package calls backends.urm / backends.commit."""
     from gl_sdm_b200.memory.backends import commit, urm
