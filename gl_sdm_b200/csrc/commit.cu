@@ -3,14 +3,18 @@
 // Replaces gl_sdm/memory/transactions.py:69-97 and gl_sdm/memory/backends/commit.py:12-58.
 //
 // Phases (all on the caller's stream, no host synchronisation, no float atomics):
-//   1. prepare     keys -> order-preserving u64, entry ids, per-digit histograms (8 x 256)
-//   2. plan        a digit on which every key agrees needs no pass; record source buffers
-//   3. per digit   count (per tile) -> scan -> stable scatter, ping-ponging two buffers
-//   4. gather      sorted address of every position
-//   5. reduce      one warp per 32 sorted positions; each segment head sums its segment
+//   1. clear       one memset of the histogram, the plan and the look-back words
+//   2. prepare     keys -> order-preserving u64, entry ids, per-digit histograms (8 x 256);
+//                  the block that finishes last writes the plan (a digit on which every key
+//                  agrees needs no pass)
+//   3. per digit   ONE launch: each tile counts its digits, learns the counts of the earlier
+//                  tiles by looking back along a chain of published words, and scatters
+//                  stably, ping-ponging two buffers; the last pass also writes the sorted
+//                  address of every position
+//   4. reduce      one warp per 32 sorted positions; each segment head sums its segment
 //                  left to right and updates its bank row; segments longer than
 //                  kLongSegment are queued
-//   6. long        one block per queued segment: fixed 256-entry chunks summed left to
+//   5. long        one block per queued segment: fixed 256-entry chunks summed left to
 //                  right by warps, chunk sums added left to right, row updated
 #include <mutex>
 
@@ -309,21 +313,23 @@ int commit_impl(const void* values_in, void* values_out, int dtype, int64_t row_
   if (key_bits < 0 || key_bits > 64) return GLSDM_ERR_ARGUMENT;
   const size_t elem = dtype == GLSDM_F32 ? 4 : 2;
   if (values_out == nullptr) values_out = const_cast<void*>(values_in);
+  Workspace w;
+  if (entries > 0) {
+    // every check comes before the first byte of values_out is written
+    if (addresses == nullptr || deltas == nullptr || workspace == nullptr) return GLSDM_ERR_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GLSDM_ERR_ARGUMENT;
+    const size_t need = carve(&w, static_cast<char*>(workspace), entries, dim);
+    if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
+  }
   if (values_out != values_in) {
     GLSDM_CUDA_OK(cudaMemcpyAsync(values_out, values_in, elem * bank_rows * dim,
                                   cudaMemcpyDeviceToDevice, stream), "commit bank copy");
   }
   if (entries == 0) return GLSDM_OK;
-  if (addresses == nullptr || deltas == nullptr || workspace == nullptr) return GLSDM_ERR_ARGUMENT;
-  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GLSDM_ERR_ARGUMENT;
-  Workspace w;
-  const size_t need = carve(&w, static_cast<char*>(workspace), entries, dim);
-  if (workspace_bytes < need) return GLSDM_ERR_WORKSPACE;
   if (keys == nullptr) keys = addresses;
-  if (int s = run_sort(w, keys, entries, sort_passes(key_bits), stream)) return s;
-  gather_address_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, addresses, entries);
-  GLSDM_CUDA_OK(cudaGetLastError(), "commit gather launch");
-  count_launches(1);
+  w.device_status = device_status;
+  const SortGather gather = {addresses, nullptr, nullptr};
+  if (int s = run_sort(w, keys, entries, sort_passes(key_bits), gather, stream)) return s;
 
   ReduceArgs a;
   a.values_in = values_in;
@@ -456,8 +462,8 @@ extern "C" int glsdm_commit_static(const void* values_in, void* values_out, int 
   void* scratch = nullptr;
   if (int s = static_scratch(&scratch)) return s;
   // The array still holds whatever the previous call left; glsdm_commit clears the digit
-  // histogram and its plan kernel resets the queue counters, nothing else is read before it
-  // is written.
+  // histogram, the plan (queue counters, tickets) and the look-back words with one memset,
+  // nothing else is read before it is written.
   return glsdm_commit(values_in, values_out, dtype, row_base, bank_rows, dim, addresses, deltas, keys, entries,
                       key_bits, scratch, kStaticScratchBytes, device_status, stream);
 }

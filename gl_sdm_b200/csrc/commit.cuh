@@ -27,26 +27,34 @@ struct Plan {
   uint32_t skip[kDigits];    // 1 = all keys share this digit
   uint32_t source[kDigits];  // buffer (0/1) holding the input of this pass
   uint32_t final_buffer;     // buffer holding the fully sorted order
+  uint32_t last_pass;        // the last pass that moves keys; the gather rides on it
   uint32_t long_count;       // queued long segments
   uint32_t chunk_cursor;     // partial-sum rows handed out so far
-  uint32_t pad;
+  uint32_t ticket[kDigits];  // next tile of each pass (tiles are taken in this order)
+  uint32_t entry_ticket;     // next block of the entry stage
+  uint32_t done;             // blocks of the entry stage that have finished
+  uint32_t pad[2];
 };
 
 struct Workspace {
   uint64_t* keys[2];
   uint32_t* ids[2];
   int64_t* sorted_address;
-  uint32_t* histogram;   // [kDigits][kRadix]
-  uint32_t* tile_count;  // [kRadix][tiles], scanned in place
+  uint32_t* histogram;          // [kDigits][kRadix]
   Plan* plan;
-  uint2* long_list;      // (start, length) of queued segments
-  float* partial;        // [partial_rows][dim]
+  unsigned long long* status;   // [tiles][kRadix] look-back words of the pass in flight
+  uint2* long_list;             // (start, length) of queued segments
+  float* partial;               // [partial_rows][dim]
   int64_t partial_rows;
   int64_t long_capacity;
   int tiles;
+  // histogram, plan and status lie together and must be zero when a commit starts: one clear.
+  void* zero_from;
+  size_t zero_bytes;
   // When set, the number of live entries is read on the device (a list whose length the
   // host does not know): grids stay sized for the capacity, blocks past the end do nothing.
   const uint32_t* live;
+  uint32_t* device_status;      // where a wait that ran out is reported (may be null)
 };
 
 __device__ __forceinline__ int64_t live_entries(const uint32_t* live, int64_t capacity) {
@@ -69,6 +77,7 @@ size_t carve(Workspace* w, char* base, int64_t entries, int32_t dim) {
   Workspace* o = w ? w : &local;
   o->tiles = tiles;
   o->live = nullptr;
+  o->device_status = nullptr;
   o->long_capacity = long_capacity;
   o->partial_rows = partial_rows;
   o->keys[0] = reinterpret_cast<uint64_t*>(take(sizeof(uint64_t) * entries));
@@ -76,11 +85,16 @@ size_t carve(Workspace* w, char* base, int64_t entries, int32_t dim) {
   o->ids[0] = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * entries));
   o->ids[1] = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * entries));
   o->sorted_address = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
-  o->histogram = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * kDigits * kRadix));
-  o->tile_count = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * kRadix * static_cast<size_t>(tiles)));
-  o->plan = reinterpret_cast<Plan*>(take(sizeof(Plan)));
   o->long_list = reinterpret_cast<uint2*>(take(sizeof(uint2) * long_capacity));
   o->partial = reinterpret_cast<float*>(take(sizeof(float) * partial_rows * dim));
+  // The zeroed region comes last, so that zeroed scratch of a caller can follow it directly.
+  const size_t zero_at = at;
+  o->histogram = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * kDigits * kRadix));
+  o->plan = reinterpret_cast<Plan*>(take(sizeof(Plan)));
+  o->status = reinterpret_cast<unsigned long long*>(
+      take(sizeof(unsigned long long) * kRadix * static_cast<size_t>(tiles)));
+  o->zero_from = base ? base + zero_at : nullptr;
+  o->zero_bytes = at - zero_at;
   return at;
 }
 
@@ -88,13 +102,102 @@ __device__ __forceinline__ uint32_t digit_of(uint64_t key, int pass) {
   return static_cast<uint32_t>(key >> (pass * kRadixBits)) & (kRadix - 1);
 }
 
+// ---- words that one block publishes and later blocks poll ------------------------------------
+//
+// A word carries a 32-bit count, the pass it belongs to and its kind in ONE 64-bit value, so a
+// reader needs no ordering beyond the load itself: kind 0 = nothing yet, kAggregate = the count
+// of this block alone, kPrefix = the count of this block and every block before it. Blocks
+// take their place in a chain from a ticket counter, so every block a reader waits for has
+// already started running; the wait is bounded all the same and, when it runs out, reports
+// GLSDM_DEV_WAIT_EXPIRED and goes on with what it has (the result is then wrong and flagged).
+constexpr unsigned long long kAggregate = 1ull << 62;
+constexpr unsigned long long kPrefix = 2ull << 62;
+constexpr int kPollLimit = 1 << 20;
+
+__device__ __forceinline__ unsigned long long chain_word(unsigned long long kind, int tag, uint32_t count) {
+  return kind | (static_cast<unsigned long long>(tag & 63) << 56) | count;
+}
+
+__device__ __forceinline__ void chain_publish(unsigned long long* slot, unsigned long long word) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(slot), "l"(word) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long chain_peek(const unsigned long long* slot) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+  return v;
+}
+
+// Sum of the counts of chain positions [0, position) of one chain whose words lie `stride`
+// apart: walks back over aggregates until it meets a prefix.
+__device__ __forceinline__ uint32_t chain_look_back(const unsigned long long* words, size_t stride,
+                                                    int64_t position, int tag, uint32_t* device_status) {
+  uint32_t before = 0;
+  for (int64_t t = position - 1; t >= 0; --t) {
+    const unsigned long long* slot = words + static_cast<size_t>(t) * stride;
+    unsigned long long v = chain_peek(slot);
+    int polls = 0;
+    while ((v >> 62) == 0 || static_cast<int>((v >> 56) & 63) != (tag & 63)) {
+      if (++polls > kPollLimit) {
+        if (device_status != nullptr) atomicOr(device_status, GLSDM_DEV_WAIT_EXPIRED);
+        return before;
+      }
+      __nanosleep(20);
+      v = chain_peek(slot);
+    }
+    before += static_cast<uint32_t>(v);
+    if ((v >> 62) == 2) break;
+  }
+  return before;
+}
+
+// ---- entry stage: order-preserving keys, entry ids, digit histograms, the plan ------------------
+
+// End of the entry stage, called by every block with its own digit counts in shared memory:
+// adds them to the global histogram; the block that finishes last writes the plan (a digit on
+// which every key agrees needs no pass; pass 0 always runs, so that some pass carries the
+// gather). `entries_known` is the entry count when the host knows it, else w.live is read.
+__device__ __forceinline__ void finish_entry_stage(const Workspace& w, int passes, int64_t entries_known,
+                                                   const uint32_t (*local)[kRadix]) {
+  __shared__ uint32_t uniform[kDigits];
+  __shared__ int is_last;
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x) {
+    const uint32_t c = (&local[0][0])[i];
+    if (c) atomicAdd(w.histogram + i, c);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&w.plan->done, 1u) == gridDim.x - 1;
+  if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int64_t entries = w.live != nullptr
+                              ? static_cast<int64_t>(*reinterpret_cast<const volatile uint32_t*>(w.live))
+                              : entries_known;
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
+    if (__ldcg(w.histogram + i) == static_cast<uint32_t>(entries)) uniform[i / kRadix] = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t buffer = 0, last = 0;
+    for (int p = 0; p < kDigits; ++p) {
+      const uint32_t skip = (p >= passes) ? 1u : (p == 0 ? 0u : uniform[p]);
+      w.plan->skip[p] = skip;
+      w.plan->source[p] = buffer;
+      if (!skip) {
+        buffer ^= 1u;
+        last = p;
+      }
+    }
+    w.plan->final_buffer = buffer;
+    w.plan->last_pass = last;
+  }
+}
+
 __global__ void __launch_bounds__(kSortThreads)
-prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, const uint32_t* live, int passes,
-               uint64_t* __restrict__ out_keys, uint32_t* __restrict__ out_ids,
-               uint32_t* __restrict__ histogram) {
+prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes, Workspace w) {
   __shared__ uint32_t local[kDigits][kRadix];
-  entries = live_entries(live, entries);
-  if (static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
   for (int i = threadIdx.x; i < kDigits * kRadix; i += kSortThreads) (&local[0][0])[i] = 0;
   __syncthreads();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
@@ -102,121 +205,47 @@ prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, const uint32_t
     const int64_t i = base + r * kSortThreads + threadIdx.x;
     if (i < entries) {
       const uint64_t k = static_cast<uint64_t>(keys[i]) ^ 0x8000000000000000ull;
-      out_keys[i] = k;
-      out_ids[i] = static_cast<uint32_t>(i);
+      w.keys[0][i] = k;
+      w.ids[0][i] = static_cast<uint32_t>(i);
       for (int p = 0; p < passes; ++p) atomicAdd(&local[p][digit_of(k, p)], 1u);
     }
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) {
-    const uint32_t c = (&local[0][0])[i];
-    if (c) atomicAdd(histogram + i, c);
-  }
+  finish_entry_stage(w, passes, entries, local);
 }
 
-__global__ void plan_kernel(const uint32_t* __restrict__ histogram, int64_t entries, const uint32_t* live,
-                            int passes, Plan* plan) {
-  __shared__ uint32_t uniform[kDigits];
-  entries = live_entries(live, entries);
-  if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
-    if (histogram[i] == static_cast<uint32_t>(entries)) uniform[i / kRadix] = 1;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t buffer = 0;
-    for (int p = 0; p < kDigits; ++p) {
-      const uint32_t skip = (p >= passes) ? 1u : uniform[p];
-      plan->skip[p] = skip;
-      plan->source[p] = buffer;
-      if (!skip) buffer ^= 1u;
-    }
-    plan->final_buffer = buffer;
-    plan->long_count = 0;
-    plan->chunk_cursor = 0;
-  }
-}
+// What rides on the last pass: the address (and, for the factored commit, the 16-byte
+// record) of every entry, written at the entry's sorted position.
+struct SortGather {
+  const int64_t* addresses;  // [entries] by entry id
+  const uint4* records;      // [entries] by entry id, or null
+  uint4* sorted_records;     // [entries] by sorted position
+};
 
+// One radix pass in one launch. A block takes the next tile (2048 keys; a warp owns 256
+// consecutive keys and takes them 32 at a time, so (warp, round, lane) order is input order;
+// ranks inside a round come from match_any), publishes its digit counts, obtains the counts
+// of all earlier tiles by looking back along the chain, and scatters. Stable.
 __global__ void __launch_bounds__(kSortThreads)
-count_kernel(Workspace w, int64_t entries, int pass) {
+radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
   if (w.plan->skip[pass]) return;
-  __shared__ uint32_t local[kRadix];
-  entries = live_entries(w.live, entries);
-  // With a device-side count the scan reads only the tiles that hold live entries.
-  if (w.live != nullptr && static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
-  local[threadIdx.x] = 0;
-  __syncthreads();
-  const uint64_t* __restrict__ keys = w.keys[w.plan->source[pass]];
-  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
-  for (int r = 0; r < kItems; ++r) {
-    const int64_t i = base + r * kSortThreads + threadIdx.x;
-    if (i < entries) atomicAdd(&local[digit_of(keys[i], pass)], 1u);
-  }
-  __syncthreads();
-  w.tile_count[static_cast<size_t>(threadIdx.x) * w.tiles + blockIdx.x] = local[threadIdx.x];
-}
-
-// Exclusive scan of tile_count ([digit][tile] flattened): block d owns digit d. Its base is
-// the number of keys with a smaller digit (from the global histogram of this pass); inside
-// the digit the tiles are scanned 256 at a time with a running carry.
-__global__ void __launch_bounds__(kSortThreads)
-scan_kernel(Workspace w, int pass) {
-  if (w.plan->skip[pass]) return;
-  __shared__ uint32_t part[kSortThreads];
-  __shared__ uint32_t carry;
-  const int d = blockIdx.x;
-  const uint32_t* __restrict__ hist = w.histogram + pass * kRadix;
-  part[threadIdx.x] = (static_cast<int>(threadIdx.x) < d) ? hist[threadIdx.x] : 0u;
-  __syncthreads();
-  for (int off = kSortThreads / 2; off > 0; off >>= 1) {
-    if (static_cast<int>(threadIdx.x) < off) part[threadIdx.x] += part[threadIdx.x + off];
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) carry = part[0];
-  __syncthreads();
-  uint32_t* __restrict__ row = w.tile_count + static_cast<size_t>(d) * w.tiles;
-  int tiles = w.tiles;   // only the tiles that hold live entries need their bases
-  if (w.live != nullptr) {
-    const int64_t used = (static_cast<int64_t>(*w.live) + kTile - 1) / kTile;
-    if (used < tiles) tiles = static_cast<int>(used);
-  }
-  for (int t0 = 0; t0 < tiles; t0 += kSortThreads) {
-    const int t = t0 + threadIdx.x;
-    const uint32_t c = t < tiles ? row[t] : 0u;
-    part[threadIdx.x] = c;
-    __syncthreads();
-    for (int off = 1; off < kSortThreads; off <<= 1) {
-      const uint32_t add = (static_cast<int>(threadIdx.x) >= off) ? part[threadIdx.x - off] : 0u;
-      __syncthreads();
-      part[threadIdx.x] += add;
-      __syncthreads();
-    }
-    const uint32_t base = carry;
-    if (t < tiles) row[t] = base + part[threadIdx.x] - c;
-    __syncthreads();
-    if (threadIdx.x == kSortThreads - 1) carry = base + part[threadIdx.x];
-    __syncthreads();
-  }
-}
-
-// Stable scatter of one tile. A warp owns 256 consecutive keys and takes them 32 at a time,
-// so (warp, round, lane) order is input order; ranks inside a round come from match_any.
-__global__ void __launch_bounds__(kSortThreads)
-scatter_kernel(Workspace w, int64_t entries, int pass) {
-  if (w.plan->skip[pass]) return;
-  entries = live_entries(w.live, entries);
-  if (static_cast<int64_t>(blockIdx.x) * kTile >= entries) return;
   constexpr int kWarps = kSortThreads / 32;
   __shared__ uint32_t warp_count[kWarps][kRadix];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ uint32_t digit_base[kRadix];
+  __shared__ uint32_t scan_carry[kWarps];
+  __shared__ uint32_t my_tile;
+  entries = live_entries(w.live, entries);
+  if (threadIdx.x == 0) my_tile = atomicAdd(&w.plan->ticket[pass], 1u);
   for (int i = threadIdx.x; i < kWarps * kRadix; i += kSortThreads) (&warp_count[0][0])[i] = 0;
   __syncthreads();
+  const int64_t tile = my_tile;
+  if (tile * kTile >= entries) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t src = w.plan->source[pass];
   const uint64_t* __restrict__ keys = w.keys[src];
   const uint32_t* __restrict__ ids = w.ids[src];
   uint64_t* __restrict__ out_keys = w.keys[src ^ 1u];
   uint32_t* __restrict__ out_ids = w.ids[src ^ 1u];
-  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItems * 32);
+  const int64_t base = tile * kTile + warp * (kItems * 32);
   uint64_t key[kItems];
   uint32_t id[kItems];
   uint32_t rank[kItems];
@@ -238,32 +267,54 @@ scatter_kernel(Workspace w, int64_t entries, int pass) {
   }
   __syncthreads();
   {
-    const int d = threadIdx.x;  // kSortThreads == kRadix
-    uint32_t run = w.tile_count[static_cast<size_t>(d) * w.tiles + blockIdx.x];
+    const int d = threadIdx.x;  // kSortThreads == kRadix: thread d owns digit d
+    // keys with a smaller digit, over the whole input: exclusive scan of this pass's histogram
+    const uint32_t h = __ldcg(w.histogram + pass * kRadix + d);
+    uint32_t inclusive = h;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(kFullMask, inclusive, o);
+      if (lane >= o) inclusive += t;
+    }
+    if (lane == 31) scan_carry[warp] = inclusive;
+    // this tile's count of digit d, and the warps' offsets inside it
+    uint32_t total = 0;
     for (int q = 0; q < kWarps; ++q) {
       const uint32_t c = warp_count[q][d];
-      warp_count[q][d] = run;
-      run += c;
+      warp_count[q][d] = total;
+      total += c;
     }
+    unsigned long long* mine = w.status + static_cast<size_t>(tile) * kRadix + d;
+    const int tag = pass + 1;
+    uint32_t before = 0;
+    if (tile == 0) {
+      chain_publish(mine, chain_word(kPrefix, tag, total));
+    } else {
+      chain_publish(mine, chain_word(kAggregate, tag, total));
+      before = chain_look_back(w.status + d, kRadix, tile, tag, w.device_status);
+      chain_publish(mine, chain_word(kPrefix, tag, before + total));
+    }
+    __syncthreads();
+    uint32_t smaller = inclusive - h;
+    for (int q = 0; q < warp; ++q) smaller += scan_carry[q];
+    digit_base[d] = smaller + before;
   }
   __syncthreads();
+  const bool last = static_cast<uint32_t>(pass) == w.plan->last_pass && g.addresses != nullptr;
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int64_t i = base + r * 32 + lane;
     if (i < entries) {
-      const uint32_t at = warp_count[warp][digit_of(key[r], pass)] + rank[r];
+      const uint32_t d = digit_of(key[r], pass);
+      const uint32_t at = digit_base[d] + warp_count[warp][d] + rank[r];
       out_keys[at] = key[r];
       out_ids[at] = id[r];
+      if (last) {
+        w.sorted_address[at] = g.addresses[id[r]];
+        if (g.records != nullptr) g.sorted_records[at] = g.records[id[r]];
+      }
     }
   }
-}
-
-__global__ void gather_address_kernel(Workspace w, const int64_t* __restrict__ addresses,
-                                      int64_t entries) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= live_entries(w.live, entries)) return;
-  const uint32_t* __restrict__ ids = w.ids[w.plan->final_buffer];
-  w.sorted_address[i] = addresses[ids[i]];
 }
 
 // Per-lane slice of a dim-wide fp32 row: lanes own column blocks of 32*V floats.
@@ -434,26 +485,34 @@ __device__ __forceinline__ int64_t segment_length(const int64_t* __restrict__ so
   }
 }
 
-// Sort (keys[i], i) for i in [0, entries): prepare -> plan -> one count/scan/scatter round per
-// digit that is not uniform. Afterwards w.ids[w.plan->final_buffer] holds the entry ids in
-// stable key order; the callers gather what their reducer needs from it.
-inline int run_sort(const Workspace& w, const int64_t* keys, int64_t entries, int passes,
-                    glsdm_stream_t stream) {
-  GLSDM_CUDA_OK(cudaMemsetAsync(w.histogram, 0, sizeof(uint32_t) * kDigits * kRadix, stream),
-                "commit histogram clear");
-  prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, w.live, passes, w.keys[0], w.ids[0],
-                                                       w.histogram);
-  GLSDM_CUDA_OK(cudaGetLastError(), "commit prepare launch");
-  plan_kernel<<<1, 256, 0, stream>>>(w.histogram, entries, w.live, passes, w.plan);
-  GLSDM_CUDA_OK(cudaGetLastError(), "commit plan launch");
-  for (int p = 0; p < passes; ++p) {
-    count_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
-    scan_kernel<<<kRadix, kSortThreads, 0, stream>>>(w, p);
-    scatter_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p);
-    GLSDM_CUDA_OK(cudaGetLastError(), "commit sort launch");
-  }
-  count_launches(2 + 3 * passes);
+// Everything a commit polls or counts starts at zero; `extra_bytes` extends the clear over
+// zeroed scratch the caller placed directly behind the workspace.
+inline int clear_sort_state(const Workspace& w, size_t extra_bytes, glsdm_stream_t stream) {
+  GLSDM_CUDA_OK(cudaMemsetAsync(w.zero_from, 0, w.zero_bytes + extra_bytes, stream), "commit state clear");
   return GLSDM_OK;
+}
+
+// The passes of the sort, after an entry stage has written w.keys[0], w.ids[0], the histogram
+// and the plan: one launch per digit (a digit all keys agree on returns at once). Afterwards
+// w.ids[w.plan->final_buffer] holds the entry ids in stable key order, w.sorted_address the
+// address of every sorted position (and g.sorted_records its record).
+inline int run_passes(const Workspace& w, int64_t entries, int passes, const SortGather& g,
+                      glsdm_stream_t stream) {
+  for (int p = 0; p < passes; ++p)
+    radix_pass_kernel<<<w.tiles, kSortThreads, 0, stream>>>(w, entries, p, g);
+  GLSDM_CUDA_OK(cudaGetLastError(), "commit sort launch");
+  count_launches(passes);
+  return GLSDM_OK;
+}
+
+// Sort (keys[i], i) for i in [0, entries): clear, prepare, passes.
+inline int run_sort(const Workspace& w, const int64_t* keys, int64_t entries, int passes,
+                    const SortGather& g, glsdm_stream_t stream) {
+  if (int s = clear_sort_state(w, 0, stream)) return s;
+  prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, passes, w);
+  GLSDM_CUDA_OK(cudaGetLastError(), "commit prepare launch");
+  count_launches(1);
+  return run_passes(w, entries, passes, g, stream);
 }
 
 // Keys are compared as signed 64-bit integers: the top digit always carries the sign.

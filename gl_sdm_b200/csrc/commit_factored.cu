@@ -31,17 +31,19 @@ struct __align__(16) Descriptor {
 };
 
 struct FactoredScratch {
-  int64_t* keys;          // [entries] unsorted sort keys
-  int64_t* addresses;     // [entries] unsorted shard-local rows
-  Descriptor* described;  // [entries] unsorted
+  int64_t* addresses;     // [entries] shard-local row of every listed entry
+  Descriptor* described;  // [entries] by entry
   Descriptor* sorted;     // [entries] in key order
-  // Dense numbering only: which addresses are written more than once.
+  // Single-writer path only (all three are cleared with the sort state they follow in memory):
+  unsigned long long* chain;  // [row blocks] look-back words of the compaction
   uint32_t* seen;         // [bits / 32] an entry has this address (modulo bits)
   uint32_t* twice;        // [bits / 32] a second entry had it too
-  uint32_t* block_shared; // [entries / 8 + 2] entries per block of rows that need the sort, then its exclusive scan
   uint32_t* live;         // [1] how many entries need the sort
   uint32_t bit_mask;      // bits - 1
+  size_t zero_extra;      // bytes of chain, maps and live behind the workspace's zeroed region
 };
+
+constexpr int kEntryRows = 4;   // routing rows per warp of the entry stage
 
 // Bits of each address map: a power of two >= 16 per entry. A bank with more rows than bits
 // folds several addresses onto one bit; they then all take the sorted path, which is always correct.
@@ -60,16 +62,19 @@ size_t carve_factored(Workspace* w, FactoredScratch* f, char* base, int64_t entr
   };
   FactoredScratch local;
   FactoredScratch* o = f ? f : &local;
-  o->keys = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
+  // zeroed scratch first: it continues the zeroed region that ends the workspace
+  const size_t zero_at = at;
+  o->chain = reinterpret_cast<unsigned long long*>(
+      take(sizeof(unsigned long long) * (entries / (kWarpsPerBlock * kEntryRows) + 2)));
+  const int64_t bits = address_bits_for(entries);
+  o->bit_mask = static_cast<uint32_t>(bits - 1);
+  o->seen = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(bits / 8) * 2));   // seen and twice
+  o->twice = o->seen != nullptr ? o->seen + bits / 32 : nullptr;
+  o->live = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t)));
+  o->zero_extra = at - zero_at;
   o->addresses = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
   o->described = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
   o->sorted = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
-  const int64_t bits = address_bits_for(entries);
-  o->bit_mask = static_cast<uint32_t>(bits - 1);
-  o->seen = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(bits / 8) * 2));   // seen and twice, one clear
-  o->twice = o->seen != nullptr ? o->seen + bits / 32 : nullptr;
-  o->block_shared = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t) * (entries / kWarpsPerBlock + 2)));
-  o->live = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t)));
   return at;
 }
 
@@ -83,59 +88,6 @@ struct EntryArgs {
   int64_t chunk_offset, key_stride;
   int width, num_layers, layer_index;
 };
-
-// One warp per routing row: address, sort key and descriptor of every route this shard owns
-// (addresses and keys as in gl_sdm/layers/global_layer.py:45,52-53).
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-factored_entries_kernel(BankView bank, EntryArgs a, FactoredScratch out) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-  if (row >= a.rows) return;
-  const int64_t block = row / a.block_rows, inner = row % a.block_rows;
-  int64_t slot = -1;
-  float w = 0.f;
-  if (lane < a.width) {
-    slot = a.index[block * a.route_stride + inner * a.width + lane];
-    w = a.weights[block * a.route_stride + inner * a.width + lane];
-  }
-  const bool owned = slot >= bank.slot_lo && slot < bank.slot_hi;
-  const unsigned mask = __ballot_sync(kFullMask, owned);
-  const int64_t head = row % bank.heads;
-  const int64_t token = row / bank.heads;
-  Descriptor d;
-  d.error_at = static_cast<uint32_t>(block * a.error_stride + inner * bank.dim);
-  d.weight = w;
-  d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
-  d.mass = a.mass != nullptr ? a.mass[token] : 1.0f;
-  if (a.offsets != nullptr) {
-    if (!owned) return;
-    const int64_t at = static_cast<int64_t>(a.offsets[row]) + __popc(mask & ((1u << lane) - 1u));
-    const int64_t position = a.chunk_offset + token % a.tokens;
-    out.addresses[at] = head * bank.part_stride_rows + (slot - bank.slot_lo);
-    out.keys[at] = (head * bank.slots + slot) * a.key_stride + position * a.num_layers + a.layer_index;
-    out.described[at] = d;
-  } else if (lane < a.width) {
-    // Dense numbering: every route has an entry. Entries are numbered token-major
-    // ((position, sequence, head), route): the canonical order inside an address is
-    // (position, layer, arrival = sequence), so a stable sort by the ADDRESS alone already
-    // yields it and the key needs no position bits (3 radix passes instead of 5 at 16M slots).
-    // A slot outside the bank takes the address one past the last, sorts last, and is dropped
-    // (and reported) by the reducer through its out-of-range row.
-    const int64_t sequence = token / a.tokens, position = token % a.tokens;
-    const int64_t at = (((position * a.sequences + sequence) * bank.heads + head) * a.width) + lane;
-    out.addresses[at] = owned ? head * bank.part_stride_rows + (slot - bank.slot_lo) : -1;
-    out.keys[at] = owned ? head * bank.slots + slot : static_cast<int64_t>(bank.heads) * bank.slots;
-    out.described[at] = d;
-  }
-}
-
-__global__ void gather_factored_kernel(Workspace w, FactoredScratch f, int64_t entries) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= live_entries(w.live, entries)) return;
-  const uint32_t id = w.ids[w.plan->final_buffer][i];
-  w.sorted_address[i] = f.addresses[id];
-  f.sorted[i] = f.described[id];
-}
 
 __device__ __forceinline__ Descriptor shfl_descriptor(const Descriptor& d, int src) {
   Descriptor o;
@@ -449,98 +401,124 @@ mark_addresses_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
   if (atomicOr(&f.seen[h >> 5], bit) & bit) atomicOr(&f.twice[h >> 5], bit);
 }
 
-// Entries of this block's rows (token-major) that need the sort.
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-count_shared_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
-  __shared__ uint32_t per_warp[kWarpsPerBlock];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-  uint32_t c = 0;
-  if (major < a.rows) {
-    const DenseLane l = dense_lane(bank, a, caller_row(bank, a, major), lane);
-    c = __popc(__ballot_sync(kFullMask, l.address >= 0 && written_twice(f, l.address)));
-  }
-  if (lane == 0) per_warp[warp] = c;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t total = 0;
-#pragma unroll
-    for (int q = 0; q < kWarpsPerBlock; ++q) total += per_warp[q];
-    f.block_shared[blockIdx.x] = total;
-  }
-}
+// ---- entry stage ---------------------------------------------------------------------------
+//
+// One launch lists the entries the sort has to order - address, order-preserving key, entry id
+// and descriptor of each - and counts their digits for every pass (the block that finishes
+// last writes the sort's plan). Which routes are listed, and where, depends on the numbering:
+//   kEveryRoute       one shard owns the bank and every entry is sorted: entry = token-major
+//                     row * width + route. The canonical order inside an address is (position,
+//                     layer, arrival = sequence), so a stable sort by the ADDRESS alone yields
+//                     it and the key needs no position bits. A slot outside the bank takes the
+//                     key one past the last address, sorts last, and is dropped (and reported)
+//                     by the reducer through its out-of-range row.
+//   kOwnedRoutes      a shard of several: the routes this shard owns, at offsets[row] + rank
+//                     among the row's owned routes; keys carry (address, position, layer) as
+//                     in gl_sdm/layers/global_layer.py:45,52-53.
+//   kSharedAddresses  single-writer path: only entries whose address is written more than
+//                     once, compacted in token-major order. A block learns how many entries
+//                     the earlier blocks list by looking back along a chain of published
+//                     counts (blocks take their rows from a ticket counter, so every block it
+//                     waits for is already running); the list's length stays on the device.
+enum EntryMode { kEveryRoute = 0, kOwnedRoutes = 1, kSharedAddresses = 2 };
 
-// In-place exclusive scan of counts[0, n); the total goes to *total.
-__global__ void __launch_bounds__(1024)
-scan_shared_kernel(uint32_t* __restrict__ counts, int64_t n, uint32_t* __restrict__ total) {
-  __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t carry;
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int passes, int64_t entries_known,
+                   uint32_t* device_status) {
+  __shared__ uint32_t local[kDigits][kRadix];
+  __shared__ uint32_t per_warp[kWarpsPerBlock];
+  __shared__ uint32_t block_first;
+  __shared__ uint32_t logical_block;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) carry = 0;
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
+  if (threadIdx.x == 0)
+    logical_block = MODE == kSharedAddresses ? atomicAdd(&w.plan->entry_ticket, 1u) : blockIdx.x;
   __syncthreads();
-  for (int64_t base = 0; base < n; base += 1024) {
-    const int64_t i = base + threadIdx.x;
-    const uint32_t c = i < n ? counts[i] : 0u;
-    uint32_t inclusive = c;
+  const int64_t logical = logical_block;
+  DenseLane l[kEntryRows];
+  int64_t row[kEntryRows];
+  unsigned mask[kEntryRows];
+  uint32_t listed = 0;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(kFullMask, inclusive, o);
-      if (lane >= o) inclusive += t;
-    }
-    if (lane == 31) warp_sum[warp] = inclusive;
-    __syncthreads();
-    if (warp == 0) {
-      const uint32_t mine = warp_sum[lane];
-      uint32_t running = mine;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_up_sync(kFullMask, running, o);
-        if (lane >= o) running += t;
+  for (int r = 0; r < kEntryRows; ++r) {
+    const int64_t major = (logical * kWarpsPerBlock + warp) * kEntryRows + r;
+    mask[r] = 0;
+    row[r] = 0;
+    l[r].address = -1; l[r].slot = -1; l[r].weight = 0.f; l[r].valid = false;
+    if (major < a.rows) {
+      row[r] = MODE == kOwnedRoutes ? major : caller_row(bank, a, major);
+      l[r] = dense_lane(bank, a, row[r], lane);
+      bool list = l[r].valid;
+      if (MODE == kOwnedRoutes) list = l[r].address >= 0;
+      if (MODE == kSharedAddresses) {
+        list = l[r].address >= 0 && written_twice(f, l[r].address);
+        if (l[r].valid && l[r].address < 0 && device_status != nullptr)
+          atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
       }
-      warp_sum[lane] = running - mine;
+      mask[r] = __ballot_sync(kFullMask, list);
+      listed += __popc(mask[r]);
+    }
+  }
+  uint32_t warp_first = 0;
+  if (MODE == kSharedAddresses) {
+    if (lane == 0) per_warp[warp] = listed;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t total = 0;
+#pragma unroll
+      for (int q = 0; q < kWarpsPerBlock; ++q) total += per_warp[q];
+      uint32_t before = 0;
+      unsigned long long* mine = f.chain + logical;
+      if (logical == 0) {
+        chain_publish(mine, chain_word(kPrefix, 1, total));
+      } else {
+        chain_publish(mine, chain_word(kAggregate, 1, total));
+        before = chain_look_back(f.chain, 1, logical, 1, device_status);
+        chain_publish(mine, chain_word(kPrefix, 1, before + total));
+      }
+      block_first = before;
+      if (logical == static_cast<int64_t>(gridDim.x) - 1) *f.live = before + total;
     }
     __syncthreads();
-    const uint32_t before = carry + warp_sum[warp] + inclusive - c;
-    if (i < n) counts[i] = before;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry = before + c;
-    __syncthreads();
+    warp_first = block_first;
+    for (int q = 0; q < warp; ++q) warp_first += per_warp[q];
   }
-  if (threadIdx.x == 0) *total = carry;
-}
-
-// Address, key and descriptor of every entry that needs the sort, in entry order.
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-compact_shared_kernel(BankView bank, EntryArgs a, FactoredScratch f, uint32_t* device_status) {
-  __shared__ uint32_t per_warp[kWarpsPerBlock];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t major = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-  DenseLane l;
-  l.address = -1; l.slot = -1; l.weight = 0.f; l.valid = false;
-  int64_t row = 0;
-  unsigned mask = 0;
-  if (major < a.rows) {
-    row = caller_row(bank, a, major);
-    l = dense_lane(bank, a, row, lane);
-    mask = __ballot_sync(kFullMask, l.address >= 0 && written_twice(f, l.address));
-    if (l.valid && l.address < 0 && device_status != nullptr) atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
+#pragma unroll
+  for (int r = 0; r < kEntryRows; ++r) {
+    if ((mask[r] >> lane) & 1u) {
+      const int64_t major = (logical * kWarpsPerBlock + warp) * kEntryRows + r;
+      const uint32_t rank = __popc(mask[r] & ((1u << lane) - 1u));
+      const int64_t head = row[r] % bank.heads, token = row[r] / bank.heads;
+      const int64_t block = row[r] / a.block_rows, inner = row[r] % a.block_rows;
+      int64_t at, key;
+      if (MODE == kEveryRoute) {
+        at = major * a.width + lane;
+        key = l[r].address >= 0 ? head * bank.slots + l[r].slot : static_cast<int64_t>(bank.heads) * bank.slots;
+      } else if (MODE == kOwnedRoutes) {
+        at = static_cast<int64_t>(a.offsets[row[r]]) + rank;
+        const int64_t position = a.chunk_offset + token % a.tokens;
+        key = (head * bank.slots + l[r].slot) * a.key_stride + position * a.num_layers + a.layer_index;
+      } else {
+        at = static_cast<int64_t>(warp_first) + rank;
+        key = head * bank.slots + l[r].slot;
+      }
+      Descriptor d;
+      d.error_at = static_cast<uint32_t>(block * a.error_stride + inner * bank.dim);
+      d.weight = l[r].weight;
+      d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
+      d.mass = a.mass != nullptr ? a.mass[token] : 1.0f;
+      f.addresses[at] = l[r].address;
+      f.described[at] = d;
+      const uint64_t k = static_cast<uint64_t>(key) ^ 0x8000000000000000ull;
+      w.keys[0][at] = k;
+      w.ids[0][at] = static_cast<uint32_t>(at);
+      for (int p = 0; p < passes; ++p) atomicAdd(&local[p][digit_of(k, p)], 1u);
+    }
+    if (MODE == kSharedAddresses) warp_first += __popc(mask[r]);
   }
-  if (lane == 0) per_warp[warp] = __popc(mask);
-  __syncthreads();
-  if (!((mask >> lane) & 1u)) return;
-  uint32_t at = f.block_shared[blockIdx.x] + __popc(mask & ((1u << lane) - 1u));
-  for (int q = 0; q < warp; ++q) at += per_warp[q];
-  const int64_t block = row / a.block_rows, inner = row % a.block_rows;
-  Descriptor d;
-  d.error_at = static_cast<uint32_t>(block * a.error_stride + inner * bank.dim);
-  d.weight = l.weight;
-  d.gate = a.error[block * a.error_stride + a.block_rows * bank.dim + inner];
-  d.mass = a.mass != nullptr ? a.mass[row / bank.heads] : 1.0f;
-  f.addresses[at] = l.address;
-  f.keys[at] = (row % bank.heads) * bank.slots + l.slot;
-  f.described[at] = d;
+  finish_entry_stage(w, passes, entries_known, local);
 }
-
 
 // Rows written by one entry only, updated straight from the routes: the token's error row is
 // read once per warp, the arithmetic is the single-entry case of the reducer.
@@ -736,32 +714,34 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   e.tokens = tokens; e.sequences = rows / (static_cast<int64_t>(v.heads) * tokens); e.chunk_offset = chunk_offset; e.key_stride = chunk_size * num_layers;
   e.width = width; e.num_layers = num_layers; e.layer_index = layer_index;
   }
+  w.device_status = device_status;
   if (phases & GLSDM_COMMIT_ORDER) {
-  if (once) {
-    const int row_blocks = blocks_for(rows, kWarpsPerBlock);
-    GLSDM_CUDA_OK(cudaMemsetAsync(f.seen, 0, (static_cast<size_t>(f.bit_mask) + 1) / 8 * 2, stream),
-                  "factored address map clear");
-    mark_addresses_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
-    count_shared_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
-    scan_shared_kernel<<<1, 1024, 0, stream>>>(f.block_shared, row_blocks, f.live);
-    compact_shared_kernel<<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(v, e, f, device_status);
-    GLSDM_CUDA_OK(cudaGetLastError(), "factored address map launches");
-    count_launches(3);
-  } else {
-  factored_entries_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
-  GLSDM_CUDA_OK(cudaGetLastError(), "factored entries launch");
-  }
-  // Dense numbering sorts by address alone (one value past the last address marks a slot
-  // outside the bank).
-  // The compacted list of the single-writer path holds no such slot: one value fewer.
-  const int64_t largest_key = static_cast<int64_t>(v.heads) * v.slots - (once ? 1 : 0);
-  int address_bits = 1;
-  while (largest_key >> address_bits) ++address_bits;
-  const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
-  if (int s = run_sort(w, f.keys, entries, passes, stream)) return s;
-  gather_factored_kernel<<<blocks_for(entries, 256), 256, 0, stream>>>(w, f, entries);
-  GLSDM_CUDA_OK(cudaGetLastError(), "factored gather launch");
-  count_launches(2);
+    // Dense numbering sorts by address alone (one value past the last address marks a slot
+    // outside the bank; the compacted list of the single-writer path holds no such slot).
+    const int64_t largest_key = static_cast<int64_t>(v.heads) * v.slots - (once ? 1 : 0);
+    int address_bits = 1;
+    while (largest_key >> address_bits) ++address_bits;
+    const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
+    const int row_blocks = blocks_for(rows, kWarpsPerBlock * kEntryRows);
+    if (int s = clear_sort_state(w, once ? f.zero_extra : 0, stream)) return s;
+    if (once) {
+      mark_addresses_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
+      entry_stage_kernel<kSharedAddresses><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
+          v, e, f, w, passes, entries, device_status);
+      count_launches(2);
+    } else if (offsets == nullptr) {
+      entry_stage_kernel<kEveryRoute><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
+          v, e, f, w, passes, entries, device_status);
+      count_launches(1);
+    } else {
+      entry_stage_kernel<kOwnedRoutes><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
+          v, e, f, w, passes, entries, device_status);
+      count_launches(1);
+    }
+    GLSDM_CUDA_OK(cudaGetLastError(), "factored entry stage launch");
+    const SortGather gather = {f.addresses, reinterpret_cast<const uint4*>(f.described),
+                               reinterpret_cast<uint4*>(f.sorted)};
+    if (int s = run_passes(w, entries, passes, gather, stream)) return s;
   }
   if (!(phases & GLSDM_COMMIT_APPLY)) return GLSDM_OK;
 
