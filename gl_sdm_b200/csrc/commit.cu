@@ -31,6 +31,7 @@ __device__ __forceinline__ void sum_run(Slice<V>& acc, const uint32_t* __restric
   for (int64_t done = 0; done < count; done += 32) {
     const int n = (count - done < 32) ? static_cast<int>(count - done) : 32;
     const uint32_t mine = (lane < n) ? ids[start + done + lane] : 0u;
+    if (count > 8 && lane < n) prefetch_row(deltas + static_cast<int64_t>(mine) * dim, dim);   // lane t: entry t's row
     int t = 0;
     for (; t + 4 <= n; t += 4) {
       Slice<V> x[4];

@@ -129,24 +129,32 @@ __device__ __forceinline__ unsigned long long chain_peek(const unsigned long lon
 }
 
 // Sum of the counts of chain positions [0, position) of one chain whose words lie `stride`
-// apart: walks back over aggregates until it meets a prefix.
+// apart: walks back over aggregates until it meets a prefix. Eight words are requested at a
+// time, so a walk over many aggregates costs one memory latency per eight positions.
 __device__ __forceinline__ uint32_t chain_look_back(const unsigned long long* words, size_t stride,
                                                     int64_t position, int tag, uint32_t* device_status) {
+  constexpr int kWindow = 8;
   uint32_t before = 0;
-  for (int64_t t = position - 1; t >= 0; --t) {
-    const unsigned long long* slot = words + static_cast<size_t>(t) * stride;
-    unsigned long long v = chain_peek(slot);
-    int polls = 0;
-    while ((v >> 62) == 0 || static_cast<int>((v >> 56) & 63) != (tag & 63)) {
-      if (++polls > kPollLimit) {
-        if (device_status != nullptr) atomicOr(device_status, GLSDM_DEV_WAIT_EXPIRED);
-        return before;
+  for (int64_t t = position - 1; t >= 0; t -= kWindow) {
+    unsigned long long v[kWindow];
+#pragma unroll
+    for (int j = 0; j < kWindow; ++j)
+      v[j] = t - j >= 0 ? chain_peek(words + static_cast<size_t>(t - j) * stride) : 0ull;
+#pragma unroll
+    for (int j = 0; j < kWindow; ++j) {
+      if (t - j < 0) return before;
+      int polls = 0;
+      while ((v[j] >> 62) == 0 || static_cast<int>((v[j] >> 56) & 63) != (tag & 63)) {
+        if (++polls > kPollLimit) {
+          if (device_status != nullptr) atomicOr(device_status, GLSDM_DEV_WAIT_EXPIRED);
+          return before;
+        }
+        __nanosleep(20);
+        v[j] = chain_peek(words + static_cast<size_t>(t - j) * stride);
       }
-      __nanosleep(20);
-      v = chain_peek(slot);
+      before += static_cast<uint32_t>(v[j]);
+      if ((v[j] >> 62) == 2) return before;
     }
-    before += static_cast<uint32_t>(v);
-    if ((v >> 62) == 2) break;
   }
   return before;
 }
@@ -347,6 +355,12 @@ __device__ __forceinline__ void load_delta(Slice<V>& s, const float* __restrict_
     s.v[0] = a.x; s.v[1] = a.y; s.v[2] = a.z; s.v[3] = a.w;
     s.v[4] = b.x; s.v[5] = b.y; s.v[6] = b.z; s.v[7] = b.w;
   }
+}
+
+// Ask for a row of `floats` fp32 values to be brought into L1: the in-order sum of a long
+// segment reads one row after another, and what it waits for is each row's latency.
+__device__ __forceinline__ void prefetch_row(const float* row, int floats) {
+  for (int c = 0; c < floats; c += 32) asm volatile("prefetch.global.L1 [%0];" ::"l"(row + c));
 }
 
 template <int V>

@@ -117,6 +117,7 @@ __device__ __forceinline__ void sum_factored(Slice<V>& acc, const Descriptor* __
     const int n = (count - done < 32) ? static_cast<int>(count - done) : 32;
     Descriptor mine = {0u, 0.f, 0.f, 0.f};
     if (lane < n) mine = sorted[start + done + lane];
+    if (count > 8 && lane < n) prefetch_row(error + mine.error_at, 32 * V);   // lane t: the row of entry t
     constexpr int kAhead = V >= 8 ? 2 : 4;   // error rows requested before the first is used
     int t = 0;
     for (; t + kAhead <= n; t += kAhead) {
@@ -584,6 +585,51 @@ apply_split_kernel(Workspace w, FactoredArgs a, BankView bank, EntryArgs e, Fact
 }
 
 template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+apply_once_kernel(FactoredArgs a, BankView bank, EntryArgs e, FactoredScratch f) {
+  apply_once_block<T, V>(bank, e, f, a.values, blockIdx.x);
+}
+
+template <typename T, int V>
+int launch_once(const FactoredArgs& a, const BankView& v, const EntryArgs& e, const FactoredScratch& f,
+                glsdm_stream_t stream) {
+  apply_once_kernel<T, V><<<blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(a, v, e, f);
+  GLSDM_CUDA_OK(cudaGetLastError(), "factored single-writer apply launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+// A second stream per (host thread, device) for the one call that both orders and applies: the
+// single-writer rows need only the address maps, so they are updated on the caller's stream
+// while the shared-address entries are listed and sorted here; the caller's stream waits for
+// this one before it reduces them. Streams and events are created on first use and kept.
+struct SideLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+int side_lane(SideLane** out) {
+  constexpr int kMaxDevices = 64;
+  static thread_local SideLane lanes[kMaxDevices];
+  int device = -1;
+  GLSDM_CUDA_OK(cudaGetDevice(&device), "factored commit cudaGetDevice");
+  if (device < 0 || device >= kMaxDevices) return GLSDM_ERR_LIMIT;
+  SideLane& lane = lanes[device];
+  if (lane.stream == nullptr) {
+    // Highest priority: its few small kernels must not queue behind the thousands of blocks of
+    // the row update that runs beside them.
+    int least = 0, greatest = 0;
+    GLSDM_CUDA_OK(cudaDeviceGetStreamPriorityRange(&least, &greatest), "factored commit stream priorities");
+    GLSDM_CUDA_OK(cudaStreamCreateWithPriority(&lane.stream, cudaStreamNonBlocking, greatest),
+                  "factored commit side stream");
+    GLSDM_CUDA_OK(cudaEventCreateWithFlags(&lane.fork, cudaEventDisableTiming), "factored commit event");
+    GLSDM_CUDA_OK(cudaEventCreateWithFlags(&lane.join, cudaEventDisableTiming), "factored commit event");
+  }
+  *out = &lane;
+  return GLSDM_OK;
+}
+
+template <typename T, int V>
 int launch_split(const Workspace& w, const FactoredArgs& a, const BankView& v, const EntryArgs& e,
                  const FactoredScratch& f, glsdm_stream_t stream) {
   const int shared_blocks = blocks_for((a.entries + 31) / 32, kWarpsPerBlock);
@@ -715,6 +761,10 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   e.width = width; e.num_layers = num_layers; e.layer_index = layer_index;
   }
   w.device_status = device_status;
+  // One call doing both phases on the single-writer path: list and sort the shared-address
+  // entries on a second stream while the caller's stream updates the single-writer rows.
+  const bool overlap = once && phases == (GLSDM_COMMIT_ORDER | GLSDM_COMMIT_APPLY);
+  SideLane* side = nullptr;
   if (phases & GLSDM_COMMIT_ORDER) {
     // Dense numbering sorts by address alone (one value past the last address marks a slot
     // outside the bank; the compacted list of the single-writer path holds no such slot).
@@ -724,11 +774,19 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
     const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
     const int row_blocks = blocks_for(rows, kWarpsPerBlock * kEntryRows);
     if (int s = clear_sort_state(w, once ? f.zero_extra : 0, stream)) return s;
+    glsdm_stream_t order_stream = stream;
     if (once) {
       mark_addresses_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
-      entry_stage_kernel<kSharedAddresses><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
+      count_launches(1);
+      if (overlap) {
+        if (int s = side_lane(&side)) return s;
+        GLSDM_CUDA_OK(cudaEventRecord(side->fork, stream), "factored commit fork");
+        GLSDM_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0), "factored commit fork wait");
+        order_stream = side->stream;
+      }
+      entry_stage_kernel<kSharedAddresses><<<row_blocks, kWarpsPerBlock * 32, 0, order_stream>>>(
           v, e, f, w, passes, entries, device_status);
-      count_launches(2);
+      count_launches(1);
     } else if (offsets == nullptr) {
       entry_stage_kernel<kEveryRoute><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
           v, e, f, w, passes, entries, device_status);
@@ -741,7 +799,7 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
     GLSDM_CUDA_OK(cudaGetLastError(), "factored entry stage launch");
     const SortGather gather = {f.addresses, reinterpret_cast<const uint4*>(f.described),
                                reinterpret_cast<uint4*>(f.sorted)};
-    if (int s = run_passes(w, entries, passes, gather, stream)) return s;
+    if (int s = run_passes(w, entries, passes, gather, order_stream)) return s;
   }
   if (!(phases & GLSDM_COMMIT_APPLY)) return GLSDM_OK;
 
@@ -753,6 +811,25 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   a.bank_rows = static_cast<int64_t>(v.heads) * v.part_stride_rows;
   a.dim = v.dim;
   a.device_status = device_status;
+  if (overlap) {
+    const bool f32 = bank->dtype == GLSDM_F32;
+    int status;
+    switch (v.dim) {
+      case 32: status = f32 ? launch_once<float, 1>(a, v, e, f, stream) : launch_once<__nv_bfloat16, 1>(a, v, e, f, stream); break;
+      case 64: status = f32 ? launch_once<float, 2>(a, v, e, f, stream) : launch_once<__nv_bfloat16, 2>(a, v, e, f, stream); break;
+      case 128: status = f32 ? launch_once<float, 4>(a, v, e, f, stream) : launch_once<__nv_bfloat16, 4>(a, v, e, f, stream); break;
+      default: status = f32 ? launch_once<float, 8>(a, v, e, f, stream) : launch_once<__nv_bfloat16, 8>(a, v, e, f, stream); break;
+    }
+    if (status) return status;
+    // the shared addresses' rows are other rows than the single-writer ones: their reduction
+    // follows the sort on the side stream and the caller's stream only waits for its end
+    status = bank->dtype == GLSDM_F32 ? launch_factored<float>(w, a, aligned, side->stream)
+                                      : launch_factored<__nv_bfloat16>(w, a, aligned, side->stream);
+    if (status) return status;
+    GLSDM_CUDA_OK(cudaEventRecord(side->join, side->stream), "factored commit join");
+    GLSDM_CUDA_OK(cudaStreamWaitEvent(stream, side->join, 0), "factored commit join wait");
+    return GLSDM_OK;
+  }
   if (once) {
     const bool f32 = bank->dtype == GLSDM_F32;
     switch (v.dim) {

@@ -1,12 +1,17 @@
 """Dense-key routing on the tensor cores (glsdm_score_topk) against the CPU oracle.
 
 The scoring stage q @ keys^T has no counterpart in the reference (parity unpinned): the
-oracle computes it in float32 on the CPU, the kernel with bf16 tensor-core products and fp32
-accumulation in a different order. Scores therefore agree to ~1e-6, and the selected slots
-must be identical except where the oracle's own k-th and (k+1)-th scores are closer than that
-("documented exact-score ties"); those rows are counted and bounded. The selection rule
-itself (score descending, larger slot first among equals) is pinned by rows with bit-equal
-scores (duplicated keys)."""
+oracle computes it in float32 on the CPU, the kernel with bf16 tensor-core products (exact in
+float32) accumulated in float32 in a different order. What is checked:
+  * every reported score lies within the forward error bound of a d_k-term float32 sum,
+    2 * d_k * 2^-24 * sum_i |q_i * k_i| (twice the round-to-nearest bound: the accumulator of
+    the tensor cores may truncate), and the largest discrepancy actually seen is kept;
+  * the selected slots are identical to the oracle's, except on rows where a slot only one of
+    the two took lies within FOUR times that largest discrepancy of the oracle's k-th score
+    ("documented exact-score ties"): EVERY differing row is audited, and they are counted;
+  * the selection rule itself (score descending, larger slot first among equals) is pinned
+    by rows with bit-equal scores (duplicated keys);
+  * NaN scores are never candidates (the documented behaviour of glsdm_score_topk)."""
 import numpy as np
 import pytest
 import torch
@@ -15,7 +20,26 @@ from oracle import sdm_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-EPS = 2e-5
+UNIT = 2.0 ** -24
+
+
+def error_bound(q, keys, slots):
+    """Forward bound of the float32 sum for the given (row, slot) pairs: [rows, width]."""
+    magnitude = np.abs(q.float().numpy()) @ np.abs(keys.float().numpy()).T
+    return 2 * q.shape[1] * UNIT * np.take_along_axis(magnitude, slots, 1)
+
+
+def audit_rows(scores, got_slot, want_slot, want_score, window, col_base=0):
+    """Every row whose slots differ from the oracle's must differ only through slots within
+    `window` of the oracle's k-th score. Returns how many rows that is."""
+    exempt = 0
+    for r in np.flatnonzero((np.sort(got_slot, 1) != np.sort(want_slot, 1)).any(1)):
+        boundary = want_score[r].min()
+        for s in set(got_slot[r].tolist()) ^ set(want_slot[r].tolist()):
+            gap = abs(scores[r, s - col_base] - boundary)
+            assert gap <= window, f"row {r}: slot {s} is {gap} from the k-th score, window {window}"
+        exempt += 1
+    return exempt
 
 
 def _case(rows, slots, dk, seed, duplicate=0):
@@ -33,25 +57,23 @@ def _check(q, keys, width, got_score, got_slot, col_base=0):
     want_slot, want_score = oracle.top_routes(scores, width, slot_base=col_base)
     got_slot, got_score = got_slot.cpu().numpy().astype(np.int64), got_score.cpu().numpy()
     assert (got_slot >= col_base).all() and (got_slot < col_base + keys.shape[0]).all()
-    # scores reported for the chosen slots are the oracle's scores of those slots
-    np.testing.assert_allclose(got_score, np.take_along_axis(scores, got_slot - col_base, 1), rtol=0, atol=EPS)
+    # scores reported for the chosen slots are the oracle's scores of those slots, to the bound
+    off = np.abs(got_score - np.take_along_axis(scores, got_slot - col_base, 1))
+    assert (off <= error_bound(q, keys, got_slot - col_base)).all()
+    seen = float(off.max())
     # best first, and slots distinct
     assert (np.diff(got_score, axis=1) <= 0).all()
     assert all(len(set(r)) == width for r in got_slot)
-    near_tie_rows = 0
-    for r in range(q.shape[0]):
-        if np.array_equal(got_slot[r], want_slot[r]):
-            continue
-        # any slot on one side only must sit within EPS of the oracle's k-th score
-        boundary = want_score[r, -1]
-        for s in set(got_slot[r]) ^ set(want_slot[r]):
-            assert abs(scores[r, s - col_base] - boundary) <= EPS, (r, s, scores[r, s - col_base], boundary)
-        # and where the sets agree but the order differs the scores must be within EPS too
-        if set(got_slot[r]) == set(want_slot[r]):
-            np.testing.assert_allclose(np.sort(got_score[r]), np.sort(want_score[r]), rtol=0, atol=EPS)
-        near_tie_rows += 1
-    assert near_tie_rows <= max(2, q.shape[0] // 50), f"{near_tie_rows} rows differ from the oracle"
-    return near_tie_rows
+    window = max(4 * seen, 1e-7)
+    exempt = audit_rows(scores, got_slot, want_slot, want_score, window, col_base)
+    # rows with the oracle's slots in another order: their scores must tie within the window too
+    for r in np.flatnonzero((got_slot != want_slot).any(1)):
+        if set(got_slot[r].tolist()) == set(want_slot[r].tolist()):
+            np.testing.assert_allclose(np.sort(got_score[r]), np.sort(want_score[r]), rtol=0, atol=window)
+    print(f"score_topk {q.shape[0]}x{keys.shape[0]}: largest score discrepancy {seen:.2e}, "
+          f"{exempt} documented near-tie rows")
+    assert exempt <= max(2, q.shape[0] // 100), f"{exempt} rows differ from the oracle"
+    return exempt
 
 
 @pytest.fixture(params=[0, 1, 2], ids=["one-cta", "cta-pair", "wide-tile"])
@@ -104,7 +126,8 @@ def test_score_topk_feeds_the_merge_and_read(native):
     scores = oracle.flat_scores(q.float().numpy(), keys.float().numpy())
     want_slot, want_w = oracle.canonical_routes(*oracle.top_routes(scores, 8))
     same = (index.cpu().numpy() == want_slot).all(1)
-    assert same.mean() > 0.97
+    top_slot, top_score = oracle.top_routes(scores, 8)
+    assert audit_rows(scores, index.cpu().numpy(), top_slot, top_score, 2e-6) == int((~same).sum()) <= 2
     np.testing.assert_allclose(weights.cpu().numpy()[same], want_w[same], rtol=1e-4, atol=1e-5)
     bank = torch.randn(1, 1, 4096, 64, generator=torch.Generator().manual_seed(1)).to(DEV)
     out = native.snapshot_read(bank, index.view(1, 128, 1, 8), weights.view(1, 128, 1, 8), rows_per_bank=128)
@@ -129,14 +152,42 @@ def test_pk_gemm_select_matches_the_product_key_oracle(native, rows, half, width
     got = index.cpu().numpy()
     assert (np.diff(got, axis=1) > 0).all() and got.min() >= 0 and got.max() < half * half
     same = (got == want_index).all(1)
-    assert same.mean() > 0.95, f"{(~same).sum()} of {rows} rows differ"
     np.testing.assert_allclose(weights.cpu().numpy()[same], want_weights[same], rtol=1e-4, atol=1e-5)
-    # rows that differ must differ only through candidates whose sums tie within rounding
+    # every row that differs must differ only through candidates whose sums (two 64-term
+    # float32 sums each) tie within 4e-5
     left, right = scores[:, :half], scores[:, half:]
+    window = 4e-5
     for r in np.flatnonzero(~same):
         boundary = np.sort((left[r][:, None] + right[r][None, :]).ravel())[-width]
         for s in set(got[r]) ^ set(want_index[r]):
-            assert abs(left[r, s // half] + right[r, s % half] - boundary) <= 2 * EPS
+            assert abs(left[r, s // half] + right[r, s % half] - boundary) <= window
+    print(f"pk_gemm {rows}x{half}^2: {(~same).sum()} documented near-tie rows, window {window:.1e}")
+    assert (~same).sum() <= max(2, rows // 50), f"{(~same).sum()} of {rows} rows differ"
+
+
+def test_nan_scores_are_never_candidates(native, variant):
+    """glsdm_score_topk keeps the `width` largest scores that are not NaN: a slot whose key holds
+    a NaN is never selected, and a row whose query holds a NaN has no candidates at all - its
+    list is padding (score -inf, slot -1), which glsdm_topk_merge ranks below every real
+    candidate. (The product-key kernels follow the reference's sort order, NaN first; a dense
+    score can only be NaN when the operands already are.)"""
+    q, keys = _case(300, 5000, 128, seed=21)
+    keys[7] = float("nan")
+    keys[4000] = float("nan")
+    q[5] = float("nan")
+    score, slot = native.score_topk(q.to(DEV), keys.to(DEV), 16)
+    native.raise_on_device_status(DEV)
+    got_slot, got_score = slot.cpu().numpy().astype(np.int64), score.cpu().numpy()
+    assert (got_slot[5] == -1).all() and np.isneginf(got_score[5]).all()
+    rest = np.r_[0:5, 6:300]
+    assert not np.isin(got_slot[rest], [7, 4000]).any() and np.isfinite(got_score[rest]).all()
+    clean = keys.clone()
+    clean[7] = 0
+    clean[4000] = 0
+    scores = oracle.flat_scores(q.float().numpy()[rest], clean.float().numpy())
+    scores[:, [7, 4000]] = -np.inf
+    want_slot, want_score = oracle.top_routes(scores, 16)
+    assert audit_rows(scores, got_slot[rest], want_slot, want_score, 2e-6) <= 3
 
 
 def test_tail_split_units_agree_with_the_uniform_plan(native):
