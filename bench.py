@@ -143,7 +143,7 @@ def workload_config(w, args, world):
 
 def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
     """Time the CPU port on `sample_tokens` tokens of one epoch per step. Returns (tokens/s, n, s)."""
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     from oracle import torch_port as port
     torch.set_num_threads(threads)
     gen = "cuda" if torch.cuda.is_available() else "cpu"
@@ -177,7 +177,7 @@ def run_torch_on_gpu(w, dev, sequences=16):
     second comparison beside the CPU baseline. Product-key scores in, `sequences` x chunk
     tokens of one epoch, functional commit as the reference does it (whole-bank copy) and the
     in-place variant. Returns a dict of per-stage milliseconds and tokens/s."""
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     from oracle import torch_port as port
     bank = workloads.make_bank(w, dev, banks=1)
     x = workloads.make_epoch_inputs(w, dev, 9000, sequences, w.chunk)
@@ -248,7 +248,7 @@ def reference_arm(args, w, rank):
 def api_inputs(w, device, seed):
     """Factor scores and write operands of every (epoch, global layer) of one step; the same
     distributions as make_epoch_inputs, one bank per request."""
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     return [[workloads.make_epoch_inputs(w, device, seed + 100 * e + layer) for layer in range(w.global_layers)]
             for e in range(w.epochs)]
 
@@ -329,7 +329,7 @@ def per_request_config(w):
 def per_request_cpu_port(w, seconds=5.0):
     """The CPU port through api_step on all host cores: c1 whole, c2 one request x one chunk
     (8 layers); repeated until `seconds` have passed, median step. Returns the cpu_baseline."""
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     sample = w if w.name == "c1" else w.scaled(sequences=1, seq_len=w.chunk)
@@ -355,7 +355,8 @@ def per_request_arm(args, w, rank):
     if rank != 0:
         return
     import gl_sdm_b200.memory as memory
-    from gl_sdm_b200 import _native, workloads
+    from gl_sdm_b200 import _native
+    import bench_workloads as workloads
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     lib = _native.library()
@@ -414,13 +415,107 @@ def per_request_arm(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+# ---- correctness of the multi-GPU path, recorded with every number ---------------------------------
+
+def parity_check(routing, rank, world, dist, dev):
+    """One small commit epoch through the same ShardedBankOperator the timed run uses (same
+    collectives, same kernels, `world` ranks), checked on rank 0 against the CPU port of the
+    reference path (the checker, outside any timed region): 2 sequences x 512 tokens per rank
+    on a bf16 bank of 65,536 slots, d_v 128, top-16. Returns the `parity` object of the JSON
+    line: how many routing rows have the oracle's routes, how many differ only at a documented
+    near tie of the tensor-core scores (dense keys; product-key routes admit none), how many
+    are wrong; the largest error of the readings and of the committed bank relative to their
+    largest value; and whether all ranks hold the same routes."""
+    import bench_workloads as workloads
+    from gl_sdm_b200.sharded import ShardedBankOperator
+    w = workloads.Workload("parity", "one epoch of 2 x 512 tokens per rank, 65,536 slots, d_v 128, top-16", 1, 256, 128,
+                           128, 16, 2 * world, 512, torch.bfloat16)
+    bank = workloads.make_bank(w, dev)
+    mine = slice(2 * rank, 2 * rank + 2)
+    if routing == "dense":
+        keys = workloads.make_keys(w, dev)
+        x = workloads.make_epoch_inputs_dense(w, dev, 4242)
+        op = ShardedBankOperator(bank.clone(), w.width, w.width, dist, chunk_size=w.chunk, keys=keys)
+        readings = op.epoch_dense(*[x[k][mine].contiguous() for k in ("q", "kq", "target", "beta", "log_decay")])
+    else:
+        keys = None
+        x = workloads.make_epoch_inputs(w, dev, 4242)
+        op = ShardedBankOperator(bank.clone(), w.width, w.width, dist, chunk_size=w.chunk)
+        readings = op.epoch(*[x[k][mine].contiguous() for k in ("q_scores", "k_scores", "target", "beta", "log_decay")])
+    read_slots, read_weights, write_slots, _ = op.last_routes()
+    digest = torch.stack([(read_slots.long() * 1000003 % 2147483629).sum(), (write_slots.long() * 999983 % 2147483629).sum(),
+                          (read_weights.double().sum() * 1e6).long()]).view(1, 3)
+    every_digest = torch.empty(world, 3, dtype=torch.long, device=dev)
+    every_reading = torch.empty(world, *readings.shape, dtype=readings.dtype, device=dev)
+    if dist is not None:
+        dist.all_gather_into_tensor(every_digest, digest)
+        dist.all_gather_into_tensor(every_reading, readings.contiguous())
+    else:
+        every_digest.copy_(digest)
+        every_reading[0].copy_(readings)
+    after = op.gather_bank()
+    from gl_sdm_b200 import _native
+    _native.raise_on_device_status(dev)
+    if rank != 0:
+        return None
+    from oracle import torch_port as port
+    torch.set_num_threads(os.cpu_count() or 1)
+    cpu = {k: v.cpu() for k, v in x.items()}
+    got_reads = every_reading.flatten(0, 1).cpu().reshape(-1, w.dim)
+    got = {"read": read_slots.cpu().long(), "write": write_slots.cpu().long()}
+    rows = got["read"].shape[0]
+    exempt = {"read": torch.zeros(rows, dtype=torch.bool), "write": torch.zeros(rows, dtype=torch.bool)}
+    wrong = 0
+    if routing == "dense":
+        host_keys = keys.cpu().float()
+        sides = {"read": cpu["q"].float().reshape(-1, w.dk), "write": cpu["kq"].float().reshape(-1, w.dk)}
+        for side, q in sides.items():
+            scores = q @ host_keys.T
+            want, _ = port.flat_routes(q, host_keys, w.width)
+            differs = (want != got[side]).any(-1)
+            for r in torch.nonzero(differs).flatten().tolist():
+                kth = scores[r, want[r]].min()
+                only = set(want[r].tolist()) ^ set(got[side][r].tolist())
+                if all(abs(float(scores[r, s] - kth)) <= 8e-6 for s in only):
+                    exempt[side][r] = True
+                else:
+                    wrong += 1
+        want_reads, want_bank = port.dense_epoch(bank.cpu().clone(), host_keys, cpu["q"].float(), cpu["kq"].float(), w.width,
+                                                 cpu["target"].float(), cpu["beta"], cpu["log_decay"], w.chunk)
+    else:
+        for side, name in (("read", "q_scores"), ("write", "k_scores")):
+            want, _ = port.select_routes(cpu[name].reshape(-1, cpu[name].shape[-1]), w.width)
+            wrong += int((want != got[side]).any(-1).sum())
+        host_bank = bank.cpu().clone()
+        want_reads, _, _ = port.routed_read(host_bank, cpu["q_scores"], w.width)
+        a, d, k = port.propose(host_bank, cpu["k_scores"], w.width, cpu["target"].float(), cpu["beta"], cpu["log_decay"],
+                               None, 0, 0, w.chunk, 1)
+        want_bank = port.commit(host_bank, a, d, k, in_place=True)
+    want_reads = want_reads.reshape(-1, w.dim)
+    keep = ~exempt["read"]
+    read_err = float((got_reads[keep] - want_reads[keep]).abs().max() / want_reads.abs().max())
+    loose = torch.zeros(w.slots, dtype=torch.bool)
+    if exempt["write"].any():
+        loose[got["write"][exempt["write"]].flatten()] = True     # rows a differently routed write may touch
+        loose[port.flat_routes(sides["write"][exempt["write"]], host_keys, w.width)[0].flatten()] = True
+    got_bank, want_bank = after.cpu().float().view(-1, w.dim), want_bank.float().view(-1, w.dim)
+    bank_err = float((got_bank[~loose] - want_bank[~loose]).abs().max() / want_bank.abs().max())
+    near = int(exempt["read"].sum() + exempt["write"].sum())
+    agree = bool((every_digest == every_digest[0]).all())
+    return {"workload": w.description + f", {world} rank(s), routing {routing}", "routing_rows": 2 * rows,
+            "routes_identical": 2 * rows - near - wrong, "near_tie_exempt": near, "wrong": wrong,
+            "ranks_agree_on_routes": agree, "readings_max_rel_err": read_err, "bank_max_rel_err": bank_err,
+            "tolerance": 2e-2, "ok": wrong == 0 and agree and read_err <= 2e-2 and bank_err <= 2e-2,
+            "checker": "oracle/torch_port.py on rank 0, outside the timed region"}
+
+
 # ---- our arm ---------------------------------------------------------------------------------------
 
 class Runner:
     """Binds a workload to the operator for one routing mode: device inputs and one epoch call."""
 
     def __init__(self, w, routing, dev, rank, world, dist, factored=True):
-        from gl_sdm_b200 import workloads
+        import bench_workloads as workloads
         from gl_sdm_b200.operator import SharedBankOperator
         from gl_sdm_b200.sharded import ShardedBankOperator
         self.w, self.routing, self.dev, self.world = w, routing, dev, world
@@ -552,7 +647,7 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
 
 
 def pk_roofline(w, runner, world, peaks, peak_kind):
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     if world > 1:
         return pk_sharded_roofline(w, runner, world, peaks, peak_kind)
     phase, unique = phase_times_pk(runner)
@@ -676,6 +771,7 @@ def ours(args, w, rank, world, local, dist):
     torch.cuda.set_device(dev)
     lib = _native.library()
     peaks, peak_kind = measured_peaks()
+    parity = None if args.no_parity else parity_check(args.routing, rank, world, dist, dev)
     runner = Runner(w, args.routing, dev, rank, world, dist, not args.delta_rows)
     for _ in range(args.warmup):
         runner.step()
@@ -721,7 +817,7 @@ def ours(args, w, rank, world, local, dist):
         "vs_baseline": None,
         "dtype": ("bf16 tensor-core scores, " if args.routing == "dense" else "") + "f32 accumulate over %s bank" % bank_dtype_name(w),
         "data": "synthetic", "config": workload_config(w, args, world), "roofline": roofline, "cpu_baseline": cpu,
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "parity": parity,
     }
     if extra is not None:
         line["product_key_scores"] = extra
@@ -729,7 +825,7 @@ def ours(args, w, rank, world, local, dist):
 
 
 def main():
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -747,6 +843,7 @@ def main():
                     help="write the proposal's delta rows to memory and commit them (the two-step path) instead of the "
                          "factored commit")
     ap.add_argument("--no-pk-block", action="store_true", help="skip the attached product-key-scores measurement")
+    ap.add_argument("--no-parity", action="store_true", help="skip the small checked epoch that precedes the timing")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.sequences or args.seq_len:

@@ -390,7 +390,7 @@ COMMIT_ORDER, COMMIT_APPLY = 1, 2
 
 def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
                     offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
-                    layer_index, key_bits=0, phases=COMMIT_ORDER | COMMIT_APPLY):
+                    layer_index, key_bits=0, phases=COMMIT_ORDER | COMMIT_APPLY, owner=None):
     """Commit the proposal of these write routes into ``shard`` in place without ever writing
     its delta rows: the reducer rebuilds them from ``errors`` (the write_error buffer, laid out
     as for shard_propose) and the bank rows it updates. ``offsets=None`` (unsharded bank):
@@ -411,7 +411,7 @@ def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_s
     bank = bank_of(shard, slot_lo, None, slots)
     dim = shard.shape[-1]
     lib = library()
-    work = _workspace(shard.device, lib.glsdm_commit_factored_workspace_bytes(entries, dim))
+    work = _workspace(shard.device, lib.glsdm_commit_factored_workspace_bytes(entries, dim), owner)
     _check(lib.glsdm_commit_factored_phased(ctypes.byref(bank), index_ptr, weights_ptr,
                                             _at(errors, 0), _ptr(mass), _ptr(offsets), entries, rows, block_rows,
                                             route_stride, error_stride, tokens, width, chunk_offset, chunk_size,
@@ -422,13 +422,15 @@ def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_s
 _workspaces = threading.local()
 
 
-def _workspace(device, nbytes):
-    """Scratch for the commit's sort, one buffer per (host thread, device): two threads that
-    enqueue commits on the same stream must not share it, their launches interleave."""
+def _workspace(device, nbytes, owner=None):
+    """Scratch for the commit's sort, one buffer per (host thread, device, stream): two threads
+    that enqueue commits on the same stream must not share it (their launches interleave), and
+    neither may two streams of one thread (their kernels overlap). A caller that runs the two
+    phases of one commit on different streams, ordered by events, names the buffer by ``owner``."""
     table = getattr(_workspaces, "table", None)
     if table is None:
         table = _workspaces.table = {}
-    key = torch.device(device).index
+    key = (torch.device(device).index, owner if owner is not None else torch.cuda.current_stream(device).cuda_stream)
     buf = table.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

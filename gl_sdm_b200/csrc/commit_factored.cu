@@ -40,7 +40,8 @@ struct FactoredScratch {
   uint32_t* twice;        // [bits / 32] a second entry had it too
   uint32_t* live;         // [1] how many entries need the sort
   uint32_t bit_mask;      // bits - 1
-  size_t zero_extra;      // bytes of chain, maps and live behind the workspace's zeroed region
+  size_t zero_chain;      // bytes of chain and live behind the workspace's zeroed region ...
+  size_t zero_extra;      // ... and of the maps as well
 };
 
 constexpr int kEntryRows = 4;   // routing rows per warp of the entry stage
@@ -66,11 +67,12 @@ size_t carve_factored(Workspace* w, FactoredScratch* f, char* base, int64_t entr
   const size_t zero_at = at;
   o->chain = reinterpret_cast<unsigned long long*>(
       take(sizeof(unsigned long long) * (entries / (kWarpsPerBlock * kEntryRows) + 2)));
+  o->live = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t)));
+  o->zero_chain = at - zero_at;
   const int64_t bits = address_bits_for(entries);
   o->bit_mask = static_cast<uint32_t>(bits - 1);
   o->seen = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(bits / 8) * 2));   // seen and twice
   o->twice = o->seen != nullptr ? o->seen + bits / 32 : nullptr;
-  o->live = reinterpret_cast<uint32_t*>(take(sizeof(uint32_t)));
   o->zero_extra = at - zero_at;
   o->addresses = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * entries));
   o->described = reinterpret_cast<Descriptor*>(take(sizeof(Descriptor) * entries));
@@ -416,17 +418,21 @@ mark_addresses_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
 //   kOwnedRoutes      a shard of several: the routes this shard owns, at offsets[row] + rank
 //                     among the row's owned routes; keys carry (address, position, layer) as
 //                     in gl_sdm/layers/global_layer.py:45,52-53.
+//   kOwnedCompact     a shard of several, without a host-side count: the routes whose slot this
+//                     shard owns, compacted in token-major order like kSharedAddresses (so the
+//                     address alone is the key); the list's length stays on the device.
 //   kSharedAddresses  single-writer path: only entries whose address is written more than
-//                     once, compacted in token-major order. A block learns how many entries
+//                     once (and, on a shard, owned), compacted in token-major order. A block learns how many entries
 //                     the earlier blocks list by looking back along a chain of published
 //                     counts (blocks take their rows from a ticket counter, so every block it
 //                     waits for is already running); the list's length stays on the device.
-enum EntryMode { kEveryRoute = 0, kOwnedRoutes = 1, kSharedAddresses = 2 };
+enum EntryMode { kEveryRoute = 0, kOwnedRoutes = 1, kSharedAddresses = 2, kOwnedCompact = 3 };
 
 template <int MODE>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int passes, int64_t entries_known,
                    uint32_t* device_status) {
+  constexpr bool kCompacts = MODE == kSharedAddresses || MODE == kOwnedCompact;
   __shared__ uint32_t local[kDigits][kRadix];
   __shared__ uint32_t per_warp[kWarpsPerBlock];
   __shared__ uint32_t block_first;
@@ -434,7 +440,7 @@ entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, i
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
   if (threadIdx.x == 0)
-    logical_block = MODE == kSharedAddresses ? atomicAdd(&w.plan->entry_ticket, 1u) : blockIdx.x;
+    logical_block = kCompacts ? atomicAdd(&w.plan->entry_ticket, 1u) : blockIdx.x;
   __syncthreads();
   const int64_t logical = logical_block;
   DenseLane l[kEntryRows];
@@ -451,18 +457,16 @@ entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, i
       row[r] = MODE == kOwnedRoutes ? major : caller_row(bank, a, major);
       l[r] = dense_lane(bank, a, row[r], lane);
       bool list = l[r].valid;
-      if (MODE == kOwnedRoutes) list = l[r].address >= 0;
-      if (MODE == kSharedAddresses) {
-        list = l[r].address >= 0 && written_twice(f, l[r].address);
-        if (l[r].valid && l[r].address < 0 && device_status != nullptr)
-          atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);
-      }
+      if (MODE == kOwnedRoutes || MODE == kOwnedCompact) list = l[r].address >= 0;
+      if (MODE == kSharedAddresses) list = l[r].address >= 0 && written_twice(f, l[r].address);
+      if (kCompacts && l[r].valid && (l[r].slot < 0 || l[r].slot >= bank.slots) && device_status != nullptr)
+        atomicOr(device_status, GLSDM_DEV_ADDRESS_OUT_OF_RANGE);   // not a slot of any shard
       mask[r] = __ballot_sync(kFullMask, list);
       listed += __popc(mask[r]);
     }
   }
   uint32_t warp_first = 0;
-  if (MODE == kSharedAddresses) {
+  if (kCompacts) {
     if (lane == 0) per_warp[warp] = listed;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -516,7 +520,7 @@ entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, i
       w.ids[0][at] = static_cast<uint32_t>(at);
       for (int p = 0; p < passes; ++p) atomicAdd(&local[p][digit_of(k, p)], 1u);
     }
-    if (MODE == kSharedAddresses) warp_first += __popc(mask[r]);
+    if (kCompacts) warp_first += __popc(mask[r]);
   }
   finish_entry_stage(w, passes, entries_known, local);
 }
@@ -749,10 +753,14 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   const bool aligned = (reinterpret_cast<uintptr_t>(error) & 15u) == 0 &&
                        (reinterpret_cast<uintptr_t>(bank->values) & 15u) == 0 &&
                        (error_stride % 4 == 0 || block_rows >= rows) && v.dim % 4 == 0;
+  // A shard of several owns only some of the routes it is shown: about entries * (its slots / all).
+  const bool shard = v.slot_lo != 0 || v.slot_hi != v.slots;
+  const int64_t expected = shard ? entries * (v.slot_hi - v.slot_lo) / v.slots : entries;
   const bool once = offsets == nullptr && aligned &&
-                    once_path_pays(entries, static_cast<int64_t>(v.heads) * v.part_stride_rows) &&
+                    once_path_pays(expected, static_cast<int64_t>(v.heads) * v.part_stride_rows) &&
                     (v.dim == 32 || v.dim == 64 || v.dim == 128 || v.dim == 256);
-  if (once) w.live = f.live;
+  const bool compact_owned = offsets == nullptr && shard && !once;
+  if (once || compact_owned) w.live = f.live;
   EntryArgs e;
   {
   e.index = index; e.weights = weights; e.error = error; e.mass = mass; e.offsets = offsets;
@@ -768,12 +776,12 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   if (phases & GLSDM_COMMIT_ORDER) {
     // Dense numbering sorts by address alone (one value past the last address marks a slot
     // outside the bank; the compacted list of the single-writer path holds no such slot).
-    const int64_t largest_key = static_cast<int64_t>(v.heads) * v.slots - (once ? 1 : 0);
+    const int64_t largest_key = static_cast<int64_t>(v.heads) * v.slots - ((once || compact_owned) ? 1 : 0);
     int address_bits = 1;
     while (largest_key >> address_bits) ++address_bits;
     const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
     const int row_blocks = blocks_for(rows, kWarpsPerBlock * kEntryRows);
-    if (int s = clear_sort_state(w, once ? f.zero_extra : 0, stream)) return s;
+    if (int s = clear_sort_state(w, once ? f.zero_extra : (compact_owned ? f.zero_chain : 0), stream)) return s;
     glsdm_stream_t order_stream = stream;
     if (once) {
       mark_addresses_kernel<<<blocks_for(rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(v, e, f);
@@ -785,6 +793,10 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
         order_stream = side->stream;
       }
       entry_stage_kernel<kSharedAddresses><<<row_blocks, kWarpsPerBlock * 32, 0, order_stream>>>(
+          v, e, f, w, passes, entries, device_status);
+      count_launches(1);
+    } else if (compact_owned) {
+      entry_stage_kernel<kOwnedCompact><<<row_blocks, kWarpsPerBlock * 32, 0, stream>>>(
           v, e, f, w, passes, entries, device_status);
       count_launches(1);
     } else if (offsets == nullptr) {

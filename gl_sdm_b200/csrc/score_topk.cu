@@ -27,7 +27,7 @@
 //
 // Tie rule (gl_sdm/memory/routing.py:21-24): equal scores prefer the larger slot. Slots are
 // scanned in ascending order, so a score equal to the current k-th one replaces it.
-#include "score_topk_pair.cuh"
+#include "score_topk.cuh"
 #include "score_topk_wide.cuh"
 
 namespace glsdm {
@@ -497,24 +497,22 @@ int sm_count_cached() {
 }
 
 // Which kernel runs: 0 = one CTA per 256 rows, key tiles of 128 slots (128x128x16 MMAs);
-// 1 = a CTA pair per 256 rows (cta_group::2); 2 = one CTA per 128 rows, key tiles of 256
-// slots (128x256x16 MMAs). Set by glsdm_score_topk_variant() or GLSDM_SCORE_TOPK_VARIANT.
+// 2 = one CTA per 128 rows, key tiles of 256 slots (128x256x16 MMAs). Set by
+// glsdm_score_topk_variant() or GLSDM_SCORE_TOPK_VARIANT. (1 named a CTA-pair kernel that
+// measured slower than both and was removed; the number is kept free.)
 constexpr int kDefaultVariant = 2;
 int g_variant = -1;
 
 int variant() {
   if (g_variant < 0) {
     const char* env = getenv("GLSDM_SCORE_TOPK_VARIANT");
-    g_variant = (env != nullptr && env[0] >= '0' && env[0] <= '2') ? env[0] - '0' : kDefaultVariant;
+    g_variant = (env != nullptr && (env[0] == '0' || env[0] == '2')) ? env[0] - '0' : kDefaultVariant;
   }
   return g_variant;
 }
 
-bool use_pair() { return variant() == 1; }
-
 Plan plan_for(int64_t rows, int64_t slots, int width) {
   switch (variant()) {
-    case 1: return make_plan(rows, slots, sm_count_cached() / 2, width, kPairTileCols);
     case 2: return make_plan_with_tail(rows, slots, sm_count_cached(), width, kWideTileCols, kBlockRows);
     default: return make_plan(rows, slots, sm_count_cached(), width);
   }
@@ -528,16 +526,15 @@ using namespace glsdm;
 
 extern "C" int glsdm_score_topk_variant(int which) {
   const int before = variant();
-  if (which >= 0 && which <= 2) g_variant = which;
+  if (which == 0 || which == 2) g_variant = which;
   return before;
 }
 
 extern "C" int glsdm_score_topk_plan(int64_t rows, int64_t slots, int32_t width, int32_t which, int32_t sms,
                                      int32_t* out) {
-  if (rows < 1 || slots < 1 || width < 1 || sms < 1 || out == nullptr || which < 0 || which > 2) return GLSDM_ERR_ARGUMENT;
-  const Plan pl = which == 1   ? make_plan(rows, slots, sms / 2 > 0 ? sms / 2 : 1, width, kPairTileCols)
-                  : which == 2 ? make_plan_with_tail(rows, slots, sms, width, kWideTileCols, kBlockRows)
-                               : make_plan(rows, slots, sms, width);
+  if (rows < 1 || slots < 1 || width < 1 || sms < 1 || out == nullptr || (which != 0 && which != 2)) return GLSDM_ERR_ARGUMENT;
+  const Plan pl = which == 2 ? make_plan_with_tail(rows, slots, sms, width, kWideTileCols, kBlockRows)
+                             : make_plan(rows, slots, sms, width);
   out[0] = pl.unit_pairs;
   out[1] = pl.splits;
   out[2] = pl.tiles_per_split;
@@ -578,7 +575,6 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) return GLSDM_ERR_ARGUMENT;
   if (rows == 0) return GLSDM_OK;
   const int sms = sm_count_cached();
-  const bool pair = use_pair();
   const bool wide = variant() == 2;
   const Plan pl = plan_for(rows, slots, width);
   Params p;
@@ -621,31 +617,7 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   }
   const int units = pl.unit_pairs * pl.splits + pl.tail_blocks * pl.tail_splits;
   const int grid = units < sms ? units : sms;
-  if (pair) {
-    const int clusters = units < sms / 2 ? units : sms / 2;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(2 * clusters);
-    config.blockDim = dim3(kPairThreads);
-    config.stream = stream;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = 2;
-    attribute.val.clusterDim.y = 1;
-    attribute.val.clusterDim.z = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    if (dk == 128) {
-      config.dynamicSmemBytes = PairLayout<2>::total();
-      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PairLayout<2>::total()), "score_topk pair shared memory");
-      GLSDM_CUDA_OK(cudaLaunchKernelEx(&config, score_topk_pair_kernel<2>, map_q, map_k, p), "score_topk pair launch");
-    } else {
-      config.dynamicSmemBytes = PairLayout<1>::total();
-      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PairLayout<1>::total()), "score_topk pair shared memory");
-      GLSDM_CUDA_OK(cudaLaunchKernelEx(&config, score_topk_pair_kernel<1>, map_q, map_k, p), "score_topk pair launch");
-    }
-  } else if (wide) {
+  if (wide) {
     if (dk == 128) {
       const int smem = WideLayout<2>::total();
       GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),

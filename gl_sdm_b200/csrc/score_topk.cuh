@@ -1,5 +1,5 @@
-// Building blocks shared by the dense-key routing kernels (score_topk.cu: one CTA per unit;
-// score_topk_pair.cu: a CTA pair per unit with cta_group::2 MMAs): mbarrier / TMA / tcgen05
+// Building blocks shared by the dense-key routing kernels (score_topk.cu: 128x128x16 MMAs over
+// 256 rows; score_topk_wide.cuh: 128x256x16 MMAs over 128 rows): mbarrier / TMA / tcgen05
 // wrappers, the shared-memory matrix descriptor, and the scanner -> inserter candidate queue.
 #pragma once
 

@@ -91,7 +91,7 @@ class SharedBankOperator:
         rows = index.numel() // width
         _native.commit_factored(self.values, 0, self.slots, (index, weights), 0, 0, 0, packed, 0, None, None,
                                 rows * width, rows, rows, tokens, width, offset, self.chunk_size, self.num_layers,
-                                self.layer_index, self.key_bits, phases=phases)
+                                self.layer_index, self.key_bits, phases=phases, owner=("operator", id(self)))
         if phases & _native.COMMIT_APPLY:
             self.version += 1
 
@@ -120,44 +120,3 @@ class SharedBankOperator:
         main.wait_event(ordered)
         self.commit_operands(*operands, offset, phases=_native.COMMIT_APPLY)
         return readings
-
-
-class GraphedEpoch:
-    """One epoch of an unsharded operator, captured once as a CUDA graph and replayed.
-
-    For callers that are bound by the cost of issuing an epoch's ~25 kernel launches from the
-    host (a serving loop doing other Python work between epochs). Shapes are fixed at
-    construction; every call copies its inputs into the captured buffers and returns the
-    captured output tensor (valid until the next call). Measured on B200 with the benchmark's
-    back-to-back epochs the replay is NOT faster than eager launches (c5: 173 against 162 us
-    per 2,048-token epoch; the input copies cost more than the launches), so the benchmark
-    does not use it. Works for operators whose epoch makes
-    no host synchronisation: ``SharedBankOperator`` and a single-rank ``ShardedBankOperator``
-    with the factored commit.
-    """
-
-    def __init__(self, epoch_fn, bank, example_inputs, warmup=2):
-        self.inputs = [t.clone() for t in example_inputs]
-        saved = bank.clone()                       # the warm-up epochs commit for real: undo them
-        side = torch.cuda.Stream(bank.device)
-        side.wait_stream(torch.cuda.current_stream(bank.device))
-        with torch.cuda.stream(side):              # workspaces, status words, kernel attributes
-            for _ in range(warmup):
-                epoch_fn(*self.inputs)
-        torch.cuda.current_stream(bank.device).wait_stream(side)
-        bank.copy_(saved)
-        del saved
-        self.graph = torch.cuda.CUDAGraph()
-        counter = _native.library().glsdm_kernel_launches
-        before = counter()
-        with torch.cuda.graph(self.graph):
-            self.output = epoch_fn(*self.inputs)
-        self.launches_per_replay = int(counter() - before)   # kernels of this library inside the graph
-        self.replays = 0
-
-    def __call__(self, *inputs):
-        for mine, given in zip(self.inputs, inputs):
-            mine.copy_(given)
-        self.graph.replay()
-        self.replays += 1
-        return self.output

@@ -10,8 +10,10 @@ routing, product-key scores (`epoch`): each rank routes its own tokens (their fa
   query and write side): K candidates per token instead of value rows.
 routing, dense keys (`epoch_dense`): the queries are all-gathered (2*dk bytes per token), each
   rank scores ALL tokens against its own key shard on the tensor cores and keeps a partial
-  top-k (`glsdm_score_topk`), the K candidates per rank are all-gathered, and every rank runs
-  the same deterministic merge (`glsdm_topk_merge`), so all ranks hold identical global routes.
+  top-k (`glsdm_score_topk`); the K candidates of a token go to the rank that owns the token
+  (all-to-all), which merges the R partial lists of its own tokens (`glsdm_topk_merge`: one
+  deterministic order, whatever the arrival order); the finished routes (K slots + weights per
+  token) are all-gathered, so all ranks hold identical global routes.
 read: every rank forms partial readings of all tokens over the rows it owns; a reduce-scatter
   returns each rank the finished readings / write predictions of its own tokens.
 commit clock: the write operands go to the owning shard as an all-gather of the per-token
@@ -20,8 +22,9 @@ commit clock: the write operands go to the owning shard as an all-gather of the 
   gl_sdm/runtime/dense.py:11-14) and commits locally. The factored form moves dim+1 floats
   per token over NVLink instead of K*(dim+4) for expanded deltas.
 
-Entry order inside a shard is (global token row, route), so the stable commit sums each
-address in the same order as the unsharded operator.
+The factored commit of a shard lists, on the device, the routes whose slot it owns in
+(position, sequence, head, route) order, so the stable sort by address sums each address in
+the same order as the unsharded operator; no entry count comes back to the host.
 """
 import torch
 
@@ -57,6 +60,10 @@ class SingleProcess:
     @staticmethod
     def all_gather(outs, inp, group=None):
         outs[0].copy_(inp)
+
+    @staticmethod
+    def all_to_all_single(out, inp, group=None):
+        out.view(-1).copy_(inp.reshape(-1))
 
 
 class ShardedBankOperator:
@@ -145,23 +152,33 @@ class ShardedBankOperator:
         k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo,
                      out=(mine[:rows * K].view(torch.float32).view(rows, K), mine[rows * K:].view(rows, K)))
         self._mark("merge")
-        if R > 1:
-            gathered = self._buffer("cand_all", R * 2 * rows * K, torch.int32)
-            self.dist.all_gather_into_tensor(gathered, mine, group=self.group)
-        else:
-            gathered = mine
-        routes = self._buffer("routes_all", 2 * rows * K, torch.int32)
-        k.topk_merge_packed(gathered, R, rows, K, out=(routes[:rows * K].view(rows, K),
-                                                       routes[rows * K:].view(torch.float32).view(rows, K)))
         region = n * K
-        return dict(routes=routes, stride=2 * region, read_weights_at=rows * K, write_index_at=region,
-                    write_weights_at=rows * K + region)
+        if R == 1:
+            routes = self._buffer("routes_all", 4 * region, torch.int32)
+            k.topk_merge_packed(mine, 1, rows, K, out=(routes[:2 * region].view(rows, K),
+                                                       routes[2 * region:].view(torch.float32).view(rows, K)))
+        else:
+            # candidates of the tokens of rank o, scores then slots, contiguous per destination
+            outgoing = self._buffer("cand_out", 2 * rows * K, torch.int32)
+            outgoing.view(R, 2, 2 * region).copy_(mine.view(2, R, 2 * region).transpose(0, 1))
+            incoming = self._buffer("cand_in", 2 * rows * K, torch.int32)
+            self.dist.all_to_all_single(incoming, outgoing, group=self.group)
+            # R partial lists for each of this rank's 2n rows -> its final routes [slots | weights]
+            own = self._buffer("routes_send", 4 * region, torch.int32)
+            k.topk_merge_packed(incoming, R, 2 * n, K, out=(own[:2 * region].view(2 * n, K),
+                                                             own[2 * region:].view(torch.float32).view(2 * n, K)))
+            routes = self._buffer("routes_all", R * 4 * region, torch.int32)
+            self.dist.all_gather_into_tensor(routes, own, group=self.group)
+        # per rank block: [slots of the query rows | slots of the write rows | weights, same order]
+        return dict(routes=routes, stride=4 * region, read_weights_at=2 * region, write_index_at=region,
+                    write_weights_at=3 * region)
 
     # -- read, proposal, commit --------------------------------------------------------------------
 
     def _finish(self, plan, n, lead, target, beta, log_decay, tokens, offset):
         k, dist, R, K, D = self.k, self.dist, self.world, self.width, self.dim
         routes, stride = plan["routes"], plan["stride"]
+        self._last_plan, self._last_n = plan, n
         self._mark("read")
         # partial readings of every rank's query and write rows over the owned slots
         partial = k.shard_read(self.shard, self.slot_lo, self.slots, routes, 0, plan["read_weights_at"], R * 2 * n,
@@ -182,10 +199,10 @@ class ShardedBankOperator:
             dist.all_gather_into_tensor(errors, packed, group=self.group)
         else:
             errors = packed
-        if R == 1 and self.factored:
-            # one shard owns every route: entries are numbered row * K + route, nothing to count,
-            # no host synchronisation in the epoch
-            offsets, entries = None, n * K
+        if self.factored:
+            # every route of every rank is shown to the commit, which lists the ones this shard owns
+            # on the device: nothing to count here, no host synchronisation in the epoch
+            offsets, entries = None, R * n * K
         else:
             offsets = k.shard_offsets(routes, plan["write_index_at"], R * n, n, stride, K, self.slot_lo, self.slot_hi)
             entries = int(offsets[-1].item())
@@ -206,7 +223,7 @@ class ShardedBankOperator:
             self._mark("commit")
             k.commit_rows(flat, a, d, s, out=flat, key_bits=self.key_bits)
         self._mark("end")
-        self.last_entries = entries
+        self.last_entries = entries // R if self.factored else entries   # owned entries (expected, when listed on the device)
         self.version += 1
         return readings
 
@@ -225,6 +242,22 @@ class ShardedBankOperator:
         plan = self._routes_dense(queries, write_queries, n)
         lead = (*queries.shape[:-1], 1)
         return self._finish(plan, n, lead, target, beta, log_decay, queries.shape[1], offset)
+
+    def last_routes(self):
+        """Routes of the last epoch as every rank holds them: (read slots, read weights, write
+        slots, write weights), each [ranks * n, K] in global row order (rank, sequence, token,
+        head). For checks; identical on every rank by construction."""
+        plan, n, K, R = self._last_plan, self._last_n, self.width, self.world
+        blocks = plan["routes"][:R * plan["stride"]].view(R, plan["stride"])
+        region = n * K
+
+        def take(at, as_float):
+            part = blocks[:, at:at + region]
+            part = part.view(torch.float32) if as_float else part
+            return part.reshape(R * n, K).clone()
+
+        return (take(0, False), take(plan["read_weights_at"], True), take(plan["write_index_at"], False),
+                take(plan["write_weights_at"], True))
 
     def gather_bank(self):
         """The whole bank [1, H, S, D] on every rank (tests and checkpoints)."""

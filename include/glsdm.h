@@ -322,7 +322,12 @@ int64_t glsdm_commit_static_max_entries(void);
  *   queries [rows, dk] bf16, keys [slots, dk] bf16 (this rank's shard), dk in {64,128}
  *   col_base  global slot number of keys row 0
  *   out_score [rows, width] fp32 and out_slot [rows, width] int32: the `width` best
- *   (score, slot) pairs of this shard, best first; ties prefer the larger slot. */
+ *   (score, slot) pairs of this shard, best first; ties prefer the larger slot.
+ *   NaN scores (only possible when a query or key already holds NaN or infinities) are never
+ *   candidates: a row keeps its `width` largest scores that are not NaN, +inf first, and a
+ *   row with fewer than `width` of them pads its list with (score -inf, slot -1), which
+ *   glsdm_topk_merge ranks below every real candidate. (The product-key entry points follow
+ *   the reference's sort order instead, NaN above +inf: their scores are caller data.) */
 size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width);
 int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_t slots,
                      int32_t dk, int32_t width, int64_t col_base, float* out_score,
@@ -330,9 +335,8 @@ int glsdm_score_topk(const void* queries, const void* keys, int64_t rows, int64_
                      uint32_t* device_status, glsdm_stream_t stream);
 
 /* Choose the kernel behind glsdm_score_topk: 2 = one CTA per 128 rows, key tiles of 256 slots,
- * 128x256x16 MMAs (default); 0 = one CTA per 256 rows, key tiles of 128 slots, 128x128x16 MMAs;
- * 1 = a CTA pair per 256 rows (cta_group::2, each CTA loads half of every key tile). Any other
- * value only queries. Returns the previous setting. Same results whichever runs. */
+ * 128x256x16 MMAs (default); 0 = one CTA per 256 rows, key tiles of 128 slots, 128x128x16 MMAs.
+ * Any other value only queries. Returns the previous setting. Same results whichever runs. */
 int glsdm_score_topk_variant(int which);
 /* The work decomposition glsdm_score_topk would use (host arithmetic only, no GPU needed):
  * out[8] = row blocks with uniform parts, parts, key tiles per part, key tiles in all, row

@@ -88,8 +88,15 @@ def commit_rows(values, addresses, deltas, keys=None, out=None, key_bits=0, row_
 def commit_factored(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride, mass,
                     offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size, num_layers,
                     layer_index, key_bits=0):
-    """The factored commit is defined as proposal expansion followed by the in-place commit."""
+    """The factored commit is defined as proposal expansion followed by the in-place commit.
+    Without offsets every route of every rank is shown and the shard lists the ones it owns."""
     D = shard.shape[-1]
+    if offsets is None:
+        local = shard.shape[2]
+        offsets = shard_offsets(routes, index_at, rows, block_rows, route_stride, width, slot_lo, slot_lo + local)
+        entries = int(offsets[-1])
+        if entries == 0:
+            return
     out = (torch.empty(entries, dtype=torch.int64), torch.empty(entries, D), torch.empty(entries, dtype=torch.int64))
     a, d, s = shard_propose(shard, slot_lo, slots, routes, index_at, weights_at, route_stride, errors, error_stride,
                             mass, offsets, entries, rows, block_rows, tokens, width, chunk_offset, chunk_size,

@@ -184,7 +184,7 @@ def c1_step_case(name="c1_step"):
     drawn on the CPU so that every machine rebuilds the same tensors: "c1_step" is all of c1
     (2 x 1024 tokens, one layer), "c2_chunk_step" one request and one 512-token chunk of c2
     (eight global layers writing into one commit)."""
-    from gl_sdm_b200 import workloads
+    import bench_workloads as workloads
     w = workloads.WORKLOADS["c1"] if name == "c1_step" else workloads.WORKLOADS["c2"].scaled(sequences=1, seq_len=512)
     values = workloads.make_bank(w, "cpu")
     inputs = [[workloads.make_epoch_inputs(w, "cpu", 1000 + 100 * e + layer) for layer in range(w.global_layers)]

@@ -1,5 +1,7 @@
 """Launched under torchrun by tests/test_gpu_sharded.py: the sharded operator over NCCL on
-2+ GPUs against the unsharded fused operator run on rank 0's GPU."""
+2+ GPUs against the unsharded fused operator run on each rank's GPU (product-key scores,
+float32 and bfloat16 banks), then both routing modes against the CPU oracle through the same
+checked epoch the benchmark records (bench.parity_check)."""
 import os
 import sys
 
@@ -33,6 +35,14 @@ def main():
                            dx["beta"][mine].contiguous(), dx["log_decay"][mine].contiguous())
             torch.testing.assert_close(got, want[e][mine], **tol)
         torch.testing.assert_close(op.gather_bank().float(), single.values.float(), **tol)
+    import bench
+    for routing in ("pk", "dense"):
+        parity = bench.parity_check(routing, rank, world, dist, dev)
+        if rank == 0:
+            print("parity", routing, parity)
+            assert parity["ok"] and parity["wrong"] == 0 and parity["ranks_agree_on_routes"], parity
+            if routing == "pk":
+                assert parity["near_tie_exempt"] == 0
     dist.barrier()
     if rank == 0:
         print("sharded-nccl-ok")

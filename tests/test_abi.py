@@ -79,7 +79,7 @@ def test_score_topk_plans_cover_every_block_and_tile_once():
     from gl_sdm_b200 import _native
     lib = _native.library()
     out = (ctypes.c_int32 * 8)()
-    for which in (0, 1, 2):
+    for which in (0, 2):
         for sms in (148, 132, 8):
             for rows in (1, 127, 128, 129, 5000, 19000, 65536, 70001):
                 for slots in (1, 255, 4096, 70000, 1 << 20, (1 << 24) - 3):

@@ -69,9 +69,13 @@ def test_virtual_ranks_match_the_unsharded_operator(native, world, dtype):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_nccl_two_gpus_match_the_unsharded_operator(native):
+    import socket
+    with socket.socket() as probe:          # a port nobody listens on right now
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29544", os.path.join(ROOT, "tests", "nccl_sharded_check.py")]
+           "--master-port", str(port), os.path.join(ROOT, "tests", "nccl_sharded_check.py")]
     done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
     assert "sharded-nccl-ok" in done.stdout
@@ -144,3 +148,22 @@ def test_dense_key_epochs_match_the_oracle(native, world):
     for a, b in zip(results, results[1:]):
         assert torch.equal(a[1], b[1]), "ranks disagree on the gathered bank"
     native.raise_on_device_status(DEV)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("routing", ["pk", "dense"])
+def test_benchmark_parity_epoch(native, world, routing):
+    """The checked epoch bench.py records beside every number (2 x 512 tokens per rank, 65,536
+    slots, against the CPU port of the reference path): no wrong route, identical routes on
+    all ranks, readings and bank within 2e-2 of their scale (bf16 bank)."""
+    import bench
+    tw = ThreadWorld(world)
+
+    def body(rank, dist):
+        torch.cuda.set_device(0)
+        return bench.parity_check(routing, rank, world, dist if world > 1 else None, torch.device(DEV))
+
+    parity = tw.run(body)[0]
+    print(parity)
+    assert parity["ok"] and parity["wrong"] == 0 and parity["ranks_agree_on_routes"]
+    assert parity["near_tie_exempt"] <= (4 if routing == "dense" else 0)

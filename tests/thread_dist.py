@@ -74,3 +74,9 @@ class _RankDist:
         for o, p in zip(outs, pieces):
             o.copy_(p)
         self.w.barrier.wait()
+
+    def all_to_all_single(self, out, inp, group=None):
+        pieces = self._exchange(inp)
+        n = out.numel() // self.w.world
+        out.view(self.w.world, n).copy_(torch.stack([p.reshape(self.w.world, n)[self.rank] for p in pieces]))
+        self.w.barrier.wait()
