@@ -139,7 +139,104 @@ def workload_config(w, args, world):
             "l2": "inputs larger than L2: every epoch streams the whole key shard (>= 0.5 GB) or >= 1 GB of factor scores"}
 
 
-# ---- CPU port (cpu_baseline and --impl reference) ---------------------------------------------------
+# ---- the reference on the host cores (cpu_baseline and --impl reference) ----------------------------
+
+def staged_reference():
+    """The unmodified reference package when it is staged beside the oracle (oracle/make_ref.py):
+    (its gl_sdm.memory module, its runtime.dense.proposal_delta). None when it is not there; the
+    CPU port of oracle/torch_port.py then stands in (kind "port")."""
+    from oracle import make_ref
+    path = make_ref.ref_path()
+    if path is None:
+        return None
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    import importlib
+    try:
+        memory = importlib.import_module("gl_sdm.memory")
+        importlib.import_module("gl_sdm.memory.routing")
+        dense = importlib.import_module("gl_sdm.runtime.dense")
+    except Exception:   # noqa: BLE001 - an unusable staging falls back to the port
+        return None
+    return memory, dense.proposal_delta
+
+
+def run_cpu_reference(w, routing, steps, warmup, sample_tokens, threads, budget_s=150.0):
+    """Time the reference's own code on `sample_tokens` tokens of one epoch per step, on the
+    full-size bank as the reference holds it: float32 values (gl_sdm/memory/state.py:14), the
+    batch's tokens folded into one request's token axis (one shared bank), routed read
+    (memory/routing.py:10-28), row gather and addresses (:31-42), proposal_delta
+    (runtime/dense.py:11-14), keys (layers/global_layer.py:52-53), merge and the functional
+    commit with its whole-bank copy (memory/transactions.py:62-97). With dense keys the scoring
+    stage q x keys^T + top-k has no counterpart in the reference and is the port's
+    (oracle/torch_port.py flat_routes); everything after it is the reference's. The whole-bank
+    copy makes a step take seconds on the large banks, so at most `budget_s` seconds are spent:
+    one warm-up step and then as many of the `steps` as fit (at least one). Returns
+    (tokens/s, tokens, median seconds, steps timed) or None when the reference is not staged."""
+    ref = staged_reference()
+    if ref is None:
+        return None
+    memory, proposal_delta = ref
+    import bench_workloads as workloads
+    from oracle import torch_port as port
+    torch.set_num_threads(threads)
+    gen = "cuda" if torch.cuda.is_available() else "cpu"
+    values = workloads.make_bank(w, gen, banks=1).cpu().float()
+    keys = workloads.make_keys(w, gen).cpu() if routing == "dense" else None
+    seqs = max(1, sample_tokens // w.chunk)
+    tokens = min(w.chunk, sample_tokens)
+    n = seqs * tokens
+    times = []
+    warmup = min(warmup, 1)
+    begun = time.perf_counter()
+    for i in range(warmup + steps):
+        if times and time.perf_counter() - begun + times[-1] > budget_s:
+            break
+        view = memory.MemoryView(values)
+        if routing == "dense":
+            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs_dense(w, gen, 7000 + i, seqs, tokens,
+                                                                          keys=keys.to(gen)).items()}
+            t0 = time.perf_counter()
+            index, weights = port.flat_routes(x["q"].reshape(-1, w.dk), keys, w.width)
+            index, weights = index.view(1, n, 1, -1), weights.view(1, n, 1, -1)
+            rows = memory.routing.gather_rows(view.values, index)
+            (rows * weights[..., None]).sum(-2)
+            windex, wweights = port.flat_routes(x["kq"].reshape(-1, w.dk), keys, w.width)
+            windex, wweights = windex.view(1, n, 1, -1), wweights.view(1, n, 1, -1)
+            rows = memory.routing.gather_rows(view.values, windex)
+            prediction = (rows * wweights[..., None]).sum(-2)
+        else:
+            x = {k: v.cpu() for k, v in workloads.make_epoch_inputs(w, gen, 7000 + i, seqs, tokens).items()}
+            fold = lambda t: t.reshape(1, n, *t.shape[2:])   # noqa: E731
+            t0 = time.perf_counter()
+            memory.routing.torch_routed_read(view.values, fold(x["q_scores"]), w.width)
+            prediction, windex, wweights = memory.routing.torch_routed_read(view.values, fold(x["k_scores"]), w.width)
+            rows = memory.routing.gather_rows(view.values, windex)
+        addresses = memory.routing.absolute_addresses(view.values, windex)
+        shape = (1, n, w.heads)
+        delta = proposal_delta(rows, wweights, prediction, x["target"].float().reshape(*shape, w.dim),
+                               x["beta"].reshape(*shape, 1), x["log_decay"].reshape(*shape, 1), torch.ones(1, n))
+        position = (torch.arange(n) % tokens).view(1, n, 1, 1)
+        sort_keys = addresses * w.chunk + position
+        proposal = memory.WriteProposal(view.version, addresses.flatten(), delta.flatten(0, 3), view.lineage,
+                                        sort_keys.flatten())
+        after = memory.commit(view, memory.merge(view, [proposal]))
+        dt = time.perf_counter() - t0
+        del after, delta, rows
+        if i >= warmup:
+            times.append(dt)
+    return n / statistics.median(times), n, statistics.median(times), len(times)
+
+
+def reference_sample_text(w, routing, n, sec):
+    scoring = ("q x keys^T + top-k by torch ops (no counterpart in the reference), then " if routing == "dense" else "")
+    return (f"{n} tokens of one commit epoch on the full {w.slots}-slot bank held as the reference holds it (float32, "
+            f"one shared request), {sec:.2f} s per step: {scoring}the reference's own torch_routed_read / gather_rows / "
+            "proposal_delta / merge / functional commit (whole-bank copy included), unmodified package staged under "
+            "oracle/_ref")
+
+
+# ---- CPU port (stands in when the reference is not staged) -------------------------------------------
 
 def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
     """Time the CPU port on `sample_tokens` tokens of one epoch per step. Returns (tokens/s, n, s)."""
@@ -215,6 +312,17 @@ def cpu_sample_text(w, routing, n, sec):
             f"{w.slots}-slot bank, {sec:.2f} s; PyTorch CPU port of the reference path")
 
 
+def enough_host_memory(w):
+    """The reference holds the bank in float32 and its commit returns a second copy: allow for
+    three banks of head room before taking that path on this machine."""
+    try:
+        import psutil
+        available = psutil.virtual_memory().available
+    except Exception:   # noqa: BLE001
+        return False
+    return available > 3 * w.heads * w.slots * w.dim * 4 + (16 << 30)
+
+
 def reference_arm(args, w, rank):
     if rank != 0:
         return
@@ -230,14 +338,20 @@ def reference_arm(args, w, rank):
         return
     threads = os.cpu_count() or 1
     tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
-    value, n, sec = run_cpu_port(w, args.routing, args.steps, args.warmup, tokens, threads)
+    kind, measured = "reference", None
+    if enough_host_memory(w):
+        measured = run_cpu_reference(w, args.routing, args.steps, args.warmup, tokens, threads)
+    if measured is None:
+        kind, measured = "port", (*run_cpu_port(w, args.routing, args.steps, args.warmup, tokens, threads), args.steps)
+    value, n, sec, timed = measured
     line = {
         "impl": "reference", "metric": "memory-op tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "steps": timed, "warmup": args.warmup if kind == "port" else min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(w, args, 1),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": cpu_sample_text(w, args.routing, n, sec)},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": kind,
+                         "sample": (reference_sample_text if kind == "reference" else cpu_sample_text)(w, args.routing, n, sec)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -335,7 +449,8 @@ def per_request_cpu_port(w, seconds=5.0):
     sample = w if w.name == "c1" else w.scaled(sequences=1, seq_len=w.chunk)
     values = workloads.make_bank(sample, "cpu")
     inputs = api_inputs(sample, "cpu", 1000)
-    port = PortMemory()
+    ref = staged_reference()
+    port = PortMemory() if ref is None else ref[0]      # the reference's own gl_sdm.memory when it is staged
     api_step(sample, values, inputs, port)
     times, begun = [], time.perf_counter()
     while not times or (time.perf_counter() - begun < seconds and len(times) < 50):
@@ -343,11 +458,180 @@ def per_request_cpu_port(w, seconds=5.0):
         api_step(sample, values, inputs, port)
         times.append(time.perf_counter() - t)
     sec = statistics.median(times)
-    return {"value": sample.tokens_per_step / sec, "unit": "tokens/s", "cores": threads, "kind": "port",
+    what = ("PyTorch CPU port of the reference path" if ref is None else
+            "the reference's own gl_sdm.memory (unmodified package staged under oracle/_ref)")
+    return {"value": sample.tokens_per_step / sec, "unit": "tokens/s", "cores": threads,
+            "kind": "port" if ref is None else "reference",
             "sample": f"{sample.sequences} x {sample.seq_len} tokens, {sample.global_layers} global layer(s), through the same "
-                      f"call sequence (functional commit), median of {len(times)} steps of {sec:.2f} s; PyTorch CPU port of "
-                      "the reference path",
+                      f"call sequence (functional commit), median of {len(times)} steps of {sec:.2f} s; {what}",
             "ms_per_step": sec * 1e3}
+
+
+# ---- c2 as the reference runs it: its own 16-layer stack, unmodified, on this package --------------
+
+STACK_CONFIG = dict(arch_type="gl_sdm", vocab_size=32000, hidden_size=512, head_dim=64, num_hidden_layers=16,
+                    intermediate_size=2048, dtype="bfloat16", gl_layer_pattern=["local", "global"], gl_local_window=256,
+                    gl_chunk_size=512, gl_slots=16384, gl_reads=16, gl_writes=16, gl_memory_backend="torch")
+
+
+def stack_model(device, shim):
+    """The reference's create_model at the widths of configuration 2 (gl_sdm/model.py), every
+    matrix re-drawn N(0, 0.02) from a fixed seed, the learned bank left at its own float32
+    initialiser. With `shim` the reference's gl_sdm.memory is replaced by gl_sdm_b200.memory
+    BEFORE the model modules are imported, which is all it takes (gl_sdm_b200/install.py)."""
+    from oracle import make_ref
+    path = make_ref.ref_path()
+    if path is None:
+        raise SystemExit("the reference package is not staged under oracle/_ref (python oracle/make_ref.py <checkout>)")
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    if shim:
+        from gl_sdm_b200 import install
+        install.install()
+    import importlib
+    torch.manual_seed(1234)
+    model = importlib.import_module("gl_sdm.model").create_model(STACK_CONFIG)
+    gen = torch.Generator().manual_seed(1234)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.ndim >= 2 and name != "bank.memory":
+                p.copy_((torch.randn(p.shape, generator=gen) * 0.02).to(p.dtype))
+    return model.to(device).eval()
+
+
+def stack_reference_arm(args, w, rank):
+    """--impl reference --stack: the same model on the reference's own memory package (torch
+    path) on the host cores, 1 x 1024 tokens per step (a reduced batch; the full one is 8 x 4096)."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    model = stack_model("cpu", shim=False)
+    ids = torch.randint(STACK_CONFIG["vocab_size"], (1, 1024), generator=torch.Generator().manual_seed(7))
+    times, begun = [], time.perf_counter()
+    with torch.inference_mode():
+        for i in range(1 + args.steps):
+            if times and time.perf_counter() - begun + times[-1] > 150.0:
+                break
+            t0 = time.perf_counter()
+            model.hidden(ids, model.new_cache(1))
+            if i:
+                times.append(time.perf_counter() - t0)
+            else:
+                first = time.perf_counter() - t0
+    sec = statistics.median(times or [first])
+    value = ids.numel() / sec
+    print(json.dumps({
+        "impl": "reference", "metric": "stack forward tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 weights, f32 banks", "data": "synthetic",
+        "config": {"workload": "c2: the reference's 16-layer stack (8 local + 8 global layers, hidden 512, 16,384 slots, "
+                               "top-16, 512-token chunks), forward with every chunk committed", "batch": "1 x 1024 (reduced)"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "reference",
+                         "sample": f"1 x 1024 tokens, the unmodified reference model on its own torch memory path, {sec:.2f} s per step"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+def stack_arm(args, w, rank):
+    """--workload c2 --stack: the reference's own model, unmodified, on the CUDA operator.
+    A step = Model.hidden over 8 x 4096 token ids with a fresh request cache (16 layers, 8
+    commit epochs, 128 routed reads, 64 row gathers, 8 commits of 4,194,304 entries).
+    `value` counts the WHOLE forward (dense surround included); the time inside the memory
+    operator is measured on a separate pass with events around its calls."""
+    if rank != 0:
+        return
+    from unittest.mock import patch
+    from gl_sdm_b200 import _native
+    import gl_sdm_b200.memory as memory
+    import bench_workloads as workloads
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _native.library()
+    peaks, peak_kind = measured_peaks()
+    model = stack_model(dev, shim=True)
+    import importlib
+    stack = importlib.import_module("gl_sdm.layers.stack")
+    assert stack.commit is memory.commit, "the reference stack is not bound to gl_sdm_b200.memory"
+    B, T = w.sequences, w.seq_len
+    host_ids = torch.randint(STACK_CONFIG["vocab_size"], (B, T), generator=torch.Generator().manual_seed(7)).pin_memory()
+    ids = host_ids.to(dev)
+
+    def forward(tokens):
+        with torch.inference_mode():
+            hidden, _, _ = model.hidden(tokens, model.new_cache(B))
+        return hidden
+
+    for _ in range(args.warmup):
+        forward(ids)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = lib.glsdm_kernel_launches()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    start.record()
+    for _ in range(args.steps):
+        forward(ids)
+    stop.record()
+    torch.cuda.synchronize(dev)
+    ms = start.elapsed_time(stop) / args.steps
+    launches = lib.glsdm_kernel_launches() - launches0
+    clocks = sampler.stop()
+    _native.raise_on_device_status(dev)
+
+    # time inside the operator: events around every call the stack makes into the package
+    spans = {"routed_read": [], "gather_rows": [], "commit": []}
+
+    def timed(name, fn):
+        def call(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **k)
+            e1.record()
+            spans[name].append((e0, e1))
+            return out
+        return call
+
+    with patch.object(memory.routing, "routed_read", timed("routed_read", memory.routing.routed_read)), \
+            patch.object(memory.routing, "gather_rows", timed("gather_rows", memory.routing.gather_rows)), \
+            patch.object(stack, "commit", timed("commit", stack.commit)):
+        forward(ids)
+    torch.cuda.synchronize(dev)
+    inside = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in spans.items()}
+    calls = {k: len(v) for k, v in spans.items()}
+    op_ms = sum(inside.values())
+
+    e2e_steps = max(1, min(args.steps, 3))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    t0.record()
+    for _ in range(e2e_steps):
+        last = forward(host_ids.to(dev, non_blocking=True))[:, -1].float().cpu()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    algo = workloads.algorithmic_bytes(w, w.tokens_per_step, 1.0)
+    algo["bank_copy"] = w.epochs * 2 * B * w.heads * w.slots * w.dim * 4
+    total = sum(algo.values())
+    gbs = total / (op_ms / 1e3) / 1e9
+    tokens = B * T
+    print(json.dumps({
+        "metric": "stack forward tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 weights, f32 banks and memory arithmetic", "data": "synthetic",
+        "config": {"workload": "c2: the reference's 16-layer stack (8 local + 8 global layers, hidden 512, 16,384 slots, "
+                               "top-16, 512-token chunks), forward with every chunk committed, unmodified reference code "
+                               "bound to gl_sdm_b200.memory", "batch": f"{B} x {T}",
+                   "l2": "per-request banks of 256 MB in all and 4.2 GB of factor scores per layer call: larger than L2"},
+        "memory_operator": {"ms_per_step": op_ms, "share_of_forward": op_ms / ms, "tokens_per_s": tokens / (op_ms / 1e3),
+                            "ms_by_call": inside, "calls": calls},
+        "roofline": {"bound": "hbm", "kernel": "memory operator inside the stack (pk_select_read, gather_rows, commit sort + "
+                                                "reduce, whole-bank copy of the functional commit)",
+                     "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "algorithmic_bytes_per_step": total},
+        "cpu_baseline": None,
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "h2d_bytes_per_step": host_ids.numel() * 8, "d2h_bytes_per_step": last.numel() * 4},
+        "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
 
 def per_request_arm(args, w, rank):
@@ -788,17 +1072,18 @@ def ours(args, w, rank, world, local, dist):
     e2e = None if args.no_e2e else end_to_end(args, w, runner, dev, dist, world)
 
     extra = None
-    if args.routing == "dense" and world == 1 and not args.no_pk_block:
+    if args.routing == "dense" and not args.no_pk_block:
         del runner
         torch.cuda.empty_cache()
         pk = Runner(w, "pk", dev, rank, world, dist, not args.delta_rows)
         pk_ms = timed_steps(pk, args.steps, args.warmup, dist, dev)
         extra = {"note": "same workload with the reference's operator contract: factor scores [tokens, 2*half] fp32 in",
                  "value": w.tokens_per_step / (pk_ms / 1e3), "unit": "tokens/s", "ms_per_step": pk_ms,
-                 "roofline": pk_roofline(w, pk, world, peaks, peak_kind)}
+                 "roofline": pk_roofline(w, pk, world, peaks, peak_kind),
+                 "parity": None if args.no_parity else parity_check("pk", rank, world, dist, dev)}
         del pk
         torch.cuda.empty_cache()
-        if not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline:
             extra["torch_on_gpu"] = run_torch_on_gpu(w, dev)
             torch.cuda.empty_cache()
 
@@ -808,9 +1093,14 @@ def ours(args, w, rank, world, local, dist):
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
-        cv, n, sec = run_cpu_port(w, args.routing, 1, 1, tokens, threads)
-        cpu = {"value": cv, "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": cpu_sample_text(w, args.routing, n, sec)}
+        kind, measured = "reference", None
+        if enough_host_memory(w):
+            measured = run_cpu_reference(w, args.routing, 1, 1, tokens, threads)
+        if measured is None:
+            kind, measured = "port", (*run_cpu_port(w, args.routing, 1, 1, tokens, threads), 1)
+        cv, n, sec, _ = measured
+        cpu = {"value": cv, "unit": "tokens/s", "cores": threads, "kind": kind,
+               "sample": (reference_sample_text if kind == "reference" else cpu_sample_text)(w, args.routing, n, sec)}
     line = {
         "metric": "memory-op tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
@@ -843,12 +1133,22 @@ def main():
                     help="write the proposal's delta rows to memory and commit them (the two-step path) instead of the "
                          "factored commit")
     ap.add_argument("--no-pk-block", action="store_true", help="skip the attached product-key-scores measurement")
+    ap.add_argument("--stack", action="store_true",
+                    help="with --workload c2: drive the reference's own 16-layer model (staged under oracle/_ref), "
+                         "unmodified, over this package instead of the memory API alone")
     ap.add_argument("--no-parity", action="store_true", help="skip the small checked epoch that precedes the timing")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.sequences or args.seq_len:
         w = w.scaled(args.sequences, args.seq_len)
     rank, world, local, dist = dist_setup(args)
+    if args.stack:
+        if args.workload != "c2":
+            raise SystemExit("--stack runs configuration c2 (the reference's own model)")
+        (stack_reference_arm if args.impl == "reference" else stack_arm)(args, w, rank)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     if args.impl == "reference":
         reference_arm(args, w, rank)
         return
