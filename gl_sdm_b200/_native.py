@@ -19,6 +19,7 @@ LIBRARY_PATH = os.path.join(_HERE, "libglsdm_b200.so")
 F32, BF16 = 0, 1
 DEV_ADDRESS_OUT_OF_RANGE = 1
 DEV_WAIT_EXPIRED = 2
+DEV_LOG_NOT_ASCENDING = 4
 MAX_WIDTH = 32
 
 _lock = threading.Lock()
@@ -64,6 +65,7 @@ SIGNATURES = {
                                           _i64, _i32, _i32, _i32, _i32, _p, _sz, _p, _p]),
     "glsdm_commit_static": (_i, [_p, _p, _i, _i64, _i64, _i32, _p, _p, _p, _i64, _i32, _p, _p]),
     "glsdm_commit_static_max_entries": (_i64, []),
+    "glsdm_wait_probe": (_i, [_p, _i64, _p, _p, _p]),
     "glsdm_score_topk_workspace_bytes": (_sz, [_i64, _i64, _i32, _i32]),
     "glsdm_score_topk": (_i, [_p, _p, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_score_topk_variant": (_i, [_i]),
@@ -175,8 +177,22 @@ def raise_on_device_status(device):
     if bits:
         word.zero_()
         names = [n for b, n in ((DEV_ADDRESS_OUT_OF_RANGE, "address out of range"),
-                                (DEV_WAIT_EXPIRED, "bounded wait expired")) if bits & b]
+                                (DEV_WAIT_EXPIRED, "bounded wait expired"),
+                                (DEV_LOG_NOT_ASCENDING, "undo log addresses not ascending")) if bits & b]
         raise RuntimeError("glsdm device status: " + ", ".join(names))
+
+
+def wait_probe(words, position):
+    """Run the commit kernels' bounded look-back over `words` (int64 chain words) up to
+    `position`; returns the count it reached (a one-element int32 tensor). A word that is never
+    published makes the wait run out: the status word then carries DEV_WAIT_EXPIRED."""
+    require_cuda(words)
+    if words.dtype != torch.int64:
+        raise ValueError("chain words are int64")
+    out = torch.zeros(1, dtype=torch.int32, device=words.device)
+    _check(library().glsdm_wait_probe(_ptr(words), position, _ptr(status_word(words.device)), _ptr(out),
+                                      _stream(words.device)))
+    return out
 
 
 def pk_select_into(scores, width, routes, index_at, weights_at):

@@ -105,6 +105,9 @@ reduce_kernel(Workspace w, ReduceArgs a) {
   const bool is_head = at < a.entries && (at == 0 || mine != prev);
   const unsigned all_heads = __ballot_sync(kFullMask, is_head);
   unsigned heads = all_heads;
+  // An undo log is searched by bisection later: say so now if its addresses ever descend.
+  if (a.undo_rows != nullptr && a.device_status != nullptr && at > 0 && at < a.entries && prev > mine)
+    atomicOr(a.device_status, GLSDM_DEV_LOG_NOT_ASCENDING);
   if constexpr (V > 0) {
     // Fast path for addresses that received exactly one entry (the common case): a few such
     // rows at a time, all their delta rows and old bank rows requested before any is used.
@@ -113,7 +116,8 @@ reduce_kernel(Workspace w, ReduceArgs a) {
     const uint32_t my_id = at < a.entries ? ids[at] : 0u;
     unsigned singles = __ballot_sync(kFullMask, is_head && mine != next && mine_local >= 0 && mine_local < a.bank_rows);
     heads &= ~singles;
-    constexpr int kB = GLSDM_SINGLES_BATCH;
+    // narrower rows leave registers for more rows in flight (what a latency-bound warp needs)
+    constexpr int kB = V >= 8 ? GLSDM_SINGLES_BATCH : (V >= 4 ? 2 * GLSDM_SINGLES_BATCH : 4 * GLSDM_SINGLES_BATCH);
     while (singles) {
       int pick[kB];
 #pragma unroll
@@ -408,6 +412,26 @@ extern "C" int glsdm_undo_apply(void* values, int dtype, int64_t row_base, int64
         static_cast<const __nv_bfloat16*>(undo_rows), entries);
   }
   GLSDM_CUDA_OK(cudaGetLastError(), "undo_apply launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+// ---- the bounded wait on its own -------------------------------------------------------------
+namespace glsdm {
+namespace {
+__global__ void wait_probe_kernel(const unsigned long long* words, int64_t position, uint32_t* device_status,
+                                  uint32_t* out_count) {
+  const uint32_t before = chain_look_back(words, 1, position, 1, device_status);
+  if (out_count != nullptr) *out_count = before;
+}
+}  // namespace
+}  // namespace glsdm
+
+extern "C" int glsdm_wait_probe(const void* words, int64_t position, uint32_t* device_status, uint32_t* out_count,
+                                glsdm_stream_t stream) {
+  if (words == nullptr || position < 0 || (reinterpret_cast<uintptr_t>(words) & 7u)) return GLSDM_ERR_ARGUMENT;
+  wait_probe_kernel<<<1, 1, 0, stream>>>(static_cast<const unsigned long long*>(words), position, device_status, out_count);
+  GLSDM_CUDA_OK(cudaGetLastError(), "wait probe launch");
   count_launches(1);
   return GLSDM_OK;
 }

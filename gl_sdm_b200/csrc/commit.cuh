@@ -161,13 +161,39 @@ __device__ __forceinline__ uint32_t chain_look_back(const unsigned long long* wo
 
 // ---- entry stage: order-preserving keys, entry ids, digit histograms, the plan ------------------
 
+// The sort's plan from the finished histogram, by one whole block: a digit on which every key
+// agrees needs no pass; pass 0 always runs, so that some pass carries the gather. Only the
+// fields of the plan that describe the passes are written.
+__device__ __forceinline__ void write_plan(const uint32_t* histogram, int passes, int64_t entries, Plan* plan) {
+  __shared__ uint32_t uniform[kDigits];
+  if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
+    if (__ldcg(histogram + i) == static_cast<uint32_t>(entries)) uniform[i / kRadix] = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t buffer = 0, last = 0;
+    for (int p = 0; p < kDigits; ++p) {
+      const uint32_t skip = (p >= passes) ? 1u : (p == 0 ? 0u : uniform[p]);
+      plan->skip[p] = skip;
+      plan->source[p] = buffer;
+      if (!skip) {
+        buffer ^= 1u;
+        last = p;
+      }
+    }
+    plan->final_buffer = buffer;
+    plan->last_pass = last;
+  }
+  __syncthreads();
+}
+
 // End of the entry stage, called by every block with its own digit counts in shared memory:
 // adds them to the global histogram; the block that finishes last writes the plan (a digit on
 // which every key agrees needs no pass; pass 0 always runs, so that some pass carries the
 // gather). `entries_known` is the entry count when the host knows it, else w.live is read.
 __device__ __forceinline__ void finish_entry_stage(const Workspace& w, int passes, int64_t entries_known,
                                                    const uint32_t (*local)[kRadix]) {
-  __shared__ uint32_t uniform[kDigits];
   __shared__ int is_last;
   __syncthreads();
   for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x) {
@@ -177,30 +203,13 @@ __device__ __forceinline__ void finish_entry_stage(const Workspace& w, int passe
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) is_last = atomicAdd(&w.plan->done, 1u) == gridDim.x - 1;
-  if (threadIdx.x < kDigits) uniform[threadIdx.x] = 0;
   __syncthreads();
   if (!is_last) return;
   __threadfence();
   const int64_t entries = w.live != nullptr
                               ? static_cast<int64_t>(*reinterpret_cast<const volatile uint32_t*>(w.live))
                               : entries_known;
-  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x)
-    if (__ldcg(w.histogram + i) == static_cast<uint32_t>(entries)) uniform[i / kRadix] = 1;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t buffer = 0, last = 0;
-    for (int p = 0; p < kDigits; ++p) {
-      const uint32_t skip = (p >= passes) ? 1u : (p == 0 ? 0u : uniform[p]);
-      w.plan->skip[p] = skip;
-      w.plan->source[p] = buffer;
-      if (!skip) {
-        buffer ^= 1u;
-        last = p;
-      }
-    }
-    w.plan->final_buffer = buffer;
-    w.plan->last_pass = last;
-  }
+  write_plan(w.histogram, passes, entries, w.plan);
 }
 
 __global__ void __launch_bounds__(kSortThreads)
@@ -233,22 +242,17 @@ struct SortGather {
 // consecutive keys and takes them 32 at a time, so (warp, round, lane) order is input order;
 // ranks inside a round come from match_any), publishes its digit counts, obtains the counts
 // of all earlier tiles by looking back along the chain, and scatters. Stable.
-__global__ void __launch_bounds__(kSortThreads)
-radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
-  if (w.plan->skip[pass]) return;
+__device__ __forceinline__ void radix_pass_tile(const Workspace& w, const Plan& plan, int64_t entries, int pass,
+                                                const SortGather& g, int64_t tile) {
   constexpr int kWarps = kSortThreads / 32;
   __shared__ uint32_t warp_count[kWarps][kRadix];
   __shared__ uint32_t digit_base[kRadix];
   __shared__ uint32_t scan_carry[kWarps];
-  __shared__ uint32_t my_tile;
-  entries = live_entries(w.live, entries);
-  if (threadIdx.x == 0) my_tile = atomicAdd(&w.plan->ticket[pass], 1u);
+  __syncthreads();   // the previous tile of this block is done with the shared arrays
   for (int i = threadIdx.x; i < kWarps * kRadix; i += kSortThreads) (&warp_count[0][0])[i] = 0;
   __syncthreads();
-  const int64_t tile = my_tile;
-  if (tile * kTile >= entries) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t src = w.plan->source[pass];
+  const uint32_t src = plan.source[pass];
   const uint64_t* __restrict__ keys = w.keys[src];
   const uint32_t* __restrict__ ids = w.ids[src];
   uint64_t* __restrict__ out_keys = w.keys[src ^ 1u];
@@ -308,7 +312,7 @@ radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
     digit_base[d] = smaller + before;
   }
   __syncthreads();
-  const bool last = static_cast<uint32_t>(pass) == w.plan->last_pass && g.addresses != nullptr;
+  const bool last = static_cast<uint32_t>(pass) == plan.last_pass && g.addresses != nullptr;
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int64_t i = base + r * 32 + lane;
@@ -323,6 +327,18 @@ radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
+  if (w.plan->skip[pass]) return;
+  __shared__ uint32_t my_tile;
+  entries = live_entries(w.live, entries);
+  if (threadIdx.x == 0) my_tile = atomicAdd(&w.plan->ticket[pass], 1u);
+  __syncthreads();
+  const int64_t tile = my_tile;
+  if (tile * kTile >= entries) return;
+  radix_pass_tile(w, *w.plan, entries, pass, g, tile);
 }
 
 // Per-lane slice of a dim-wide fp32 row: lanes own column blocks of 32*V floats.

@@ -13,6 +13,8 @@
 //
 // The arithmetic is the materialised path's, operation for operation (same fp32 products,
 // sums and order), so both commits produce bit-identical banks.
+#include <cooperative_groups.h>
+
 #include <atomic>
 #include <cstdlib>
 
@@ -177,7 +179,12 @@ struct FactoredArgs {
   uint32_t* device_status;
 };
 
-constexpr int kFactoredBatch = 2;   // single-entry rows in flight per warp (as in the delta-row reducer)
+// Single-entry rows in flight per warp: 2 for 256-wide rows (as in the delta-row reducer); narrower
+// rows leave registers for more, which is what a latency-bound warp needs.
+template <int V>
+struct FactoredBatch {
+  static constexpr int value = V >= 8 ? 2 : (V >= 4 ? 4 : 8);
+};
 
 template <typename T, int V>
 __device__ __forceinline__ void reduce_factored_block(const Workspace& w, const FactoredArgs& a, int64_t block) {
@@ -199,6 +206,7 @@ __device__ __forceinline__ void reduce_factored_block(const Workspace& w, const 
     if (at < entries) my_d = a.sorted[at];
     unsigned singles = __ballot_sync(kFullMask, is_head && mine != next && mine >= 0 && mine < a.bank_rows);
     heads &= ~singles;
+    constexpr int kFactoredBatch = FactoredBatch<V>::value;
     while (singles) {
       int pick[kFactoredBatch];
 #pragma unroll
@@ -428,21 +436,17 @@ mark_addresses_kernel(BankView bank, EntryArgs a, FactoredScratch f) {
 //                     waits for is already running); the list's length stays on the device.
 enum EntryMode { kEveryRoute = 0, kOwnedRoutes = 1, kSharedAddresses = 2, kOwnedCompact = 3 };
 
+// The rows of entry block `logical` (of `blocks`): lists their entries and adds their digits to
+// the block's counts in `local`.
 template <int MODE>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int passes, int64_t entries_known,
-                   uint32_t* device_status) {
+__device__ __forceinline__ void entry_rows(const BankView& bank, const EntryArgs& a, const FactoredScratch& f,
+                                           const Workspace& w, int passes, uint32_t* device_status, int64_t logical,
+                                           int64_t blocks, uint32_t (*local)[kRadix]) {
   constexpr bool kCompacts = MODE == kSharedAddresses || MODE == kOwnedCompact;
-  __shared__ uint32_t local[kDigits][kRadix];
   __shared__ uint32_t per_warp[kWarpsPerBlock];
   __shared__ uint32_t block_first;
-  __shared__ uint32_t logical_block;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
-  if (threadIdx.x == 0)
-    logical_block = kCompacts ? atomicAdd(&w.plan->entry_ticket, 1u) : blockIdx.x;
-  __syncthreads();
-  const int64_t logical = logical_block;
+  __syncthreads();   // the previous block of rows is done with the shared words
   DenseLane l[kEntryRows];
   int64_t row[kEntryRows];
   unsigned mask[kEntryRows];
@@ -483,7 +487,7 @@ entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, i
         chain_publish(mine, chain_word(kPrefix, 1, before + total));
       }
       block_first = before;
-      if (logical == static_cast<int64_t>(gridDim.x) - 1) *f.live = before + total;
+      if (logical == blocks - 1) *f.live = before + total;
     }
     __syncthreads();
     warp_first = block_first;
@@ -522,8 +526,77 @@ entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, i
     }
     if (kCompacts) warp_first += __popc(mask[r]);
   }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+entry_stage_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int passes, int64_t entries_known,
+                   uint32_t* device_status) {
+  constexpr bool kCompacts = MODE == kSharedAddresses || MODE == kOwnedCompact;
+  __shared__ uint32_t local[kDigits][kRadix];
+  __shared__ uint32_t logical_block;
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
+  if (threadIdx.x == 0)
+    logical_block = kCompacts ? atomicAdd(&w.plan->entry_ticket, 1u) : blockIdx.x;
+  __syncthreads();
+  entry_rows<MODE>(bank, a, f, w, passes, device_status, logical_block, gridDim.x, local);
   finish_entry_stage(w, passes, entries_known, local);
 }
+
+// ---- the whole ordering phase in ONE launch ---------------------------------------------------
+//
+// Small and medium commits are bound by launches, not by bytes: clear, entry stage and three to
+// five passes are as many dependent launches of a few microseconds of work each. This kernel
+// runs them back to back on a grid small enough to be resident at once (a cooperative
+// launch), with a grid-wide barrier where a launch boundary used to be: clear | entry stage |
+// plan (every block computes the same one for itself) | pass, pass, ... Blocks walk the entry
+// blocks and the tiles in increasing order, so every block a look-back waits for belongs to
+// a resident block that reaches it no later.
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+order_all_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int passes, int64_t entries_known,
+                 size_t zero_extra, uint32_t* device_status, SortGather g) {
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+  __shared__ uint32_t local[kDigits][kRadix];
+  __shared__ Plan plan;
+  {
+    uint4* zero = static_cast<uint4*>(w.zero_from);
+    const size_t cells = (w.zero_bytes + zero_extra) / sizeof(uint4);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < cells;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+      zero[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
+  grid.sync();
+  const int64_t blocks = (a.rows + kWarpsPerBlock * kEntryRows - 1) / (kWarpsPerBlock * kEntryRows);
+  for (int64_t logical = blockIdx.x; logical < blocks; logical += gridDim.x)
+    entry_rows<MODE>(bank, a, f, w, passes, device_status, logical, blocks, local);
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x) {
+    const uint32_t c = (&local[0][0])[i];
+    if (c) atomicAdd(w.histogram + i, c);
+  }
+  grid.sync();
+  const int64_t entries = w.live != nullptr
+                              ? static_cast<int64_t>(*reinterpret_cast<const volatile uint32_t*>(w.live))
+                              : entries_known;
+  write_plan(w.histogram, passes, entries, &plan);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int p = 0; p < kDigits; ++p) {
+      w.plan->skip[p] = plan.skip[p];
+      w.plan->source[p] = plan.source[p];
+    }
+    w.plan->final_buffer = plan.final_buffer;
+    w.plan->last_pass = plan.last_pass;
+  }
+  const int64_t tiles = (entries + kTile - 1) / kTile;
+  for (int p = 0; p < passes; ++p) {
+    if (plan.skip[p]) continue;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) radix_pass_tile(w, plan, entries, p, g, tile);
+    if (static_cast<uint32_t>(p) != plan.last_pass) grid.sync();
+  }
+}
+
 
 // Rows written by one entry only, updated straight from the routes: the token's error row is
 // read once per warp, the arithmetic is the single-entry case of the reducer.
@@ -594,10 +667,120 @@ apply_once_kernel(FactoredArgs a, BankView bank, EntryArgs e, FactoredScratch f)
   apply_once_block<T, V>(bank, e, f, a.values, blockIdx.x);
 }
 
+// The same update with the rows moved by bulk copies (cp.async.bulk): every lane asks for the
+// bank row of its own route, whole rows land in shared memory (up to 32 x 512 bytes per warp
+// in flight, held by no register), the warp updates them there and bulk-stores them back. A
+// warp handles one routing row, so nothing in a block waits for anything but its own copies;
+// that wait is bounded.
+constexpr int kBulkWarps = 4;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kBulkWarps * 32)
+apply_once_bulk_kernel(FactoredArgs a, BankView bank, EntryArgs e, FactoredScratch f) {
+  constexpr int kRowBytes = 32 * V * static_cast<int>(sizeof(T));
+  extern __shared__ __align__(128) unsigned char staging[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* rows_s = staging + warp * (32 * kRowBytes);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(staging + kBulkWarps * 32 * kRowBytes) + warp;
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(shared_address(bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const int64_t major = static_cast<int64_t>(blockIdx.x) * kBulkWarps + warp;
+  if (major >= e.rows) return;
+  const int64_t row = caller_row(bank, e, major);
+  const DenseLane l = dense_lane(bank, e, row, lane);
+  const unsigned once = __ballot_sync(kFullMask, l.address >= 0 && !written_twice(f, l.address));
+  if (once == 0) return;
+  const bool mine = (once >> lane) & 1u;
+  const int place = __popc(once & ((1u << lane) - 1u));
+  T* __restrict__ values = static_cast<T*>(a.values);
+  if (lane == 0) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(bar)),
+                 "r"(static_cast<uint32_t>(__popc(once) * kRowBytes))
+                 : "memory");
+  }
+  __syncwarp();
+  if (mine) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     shared_address(rows_s + place * kRowBytes)),
+                 "l"(values + l.address * bank.dim), "r"(kRowBytes), "r"(shared_address(bar))
+                 : "memory");
+  }
+  // the token's error row and scalars, while the rows travel
+  const int64_t block = row / e.block_rows, inner = row % e.block_rows;
+  Descriptor d;
+  d.error_at = 0;
+  d.gate = e.error[block * e.error_stride + e.block_rows * bank.dim + inner];
+  d.mass = e.mass != nullptr ? e.mass[row / bank.heads] : 1.0f;
+  Slice<V> err;
+  load_delta<V>(err, e.error + block * e.error_stride + inner * bank.dim, lane);
+  bool landed = false;
+  for (int round = 0; round < 2 && !landed; ++round) {
+    for (uint32_t spin = 0; spin < (1u << 20) && !landed; ++spin) {
+      uint32_t done;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(done)
+          : "r"(shared_address(bar))
+          : "memory");
+      landed = done != 0;
+    }
+    // a first wait that runs out is reported; the second only keeps the shared memory alive
+    // for copies that may still arrive
+    if (!landed && round == 0 && lane == 0 && a.device_status != nullptr)
+      atomicOr(a.device_status, GLSDM_DEV_WAIT_EXPIRED);
+  }
+  if (!landed) return;
+  int at = 0;
+  for (unsigned m = once; m; m &= m - 1, ++at) {
+    d.weight = __shfl_sync(kFullMask, l.weight, __ffs(m) - 1);
+    T* row_s = reinterpret_cast<T*>(rows_s + at * kRowBytes);
+    Slice<V> old, x;
+    load_bank<T, V>(row_s, old, lane);
+    rebuild<V>(x, d, err, old);
+#pragma unroll
+    for (int i = 0; i < V; ++i) old.v[i] = __fadd_rn(old.v[i], __fadd_rn(0.f, x.v[i]));
+    store_bank<T, V>(row_s, old, lane);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (mine) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(values + l.address * bank.dim),
+                 "r"(shared_address(rows_s + place * kRowBytes)), "r"(kRowBytes)
+                 : "memory");
+  }
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// 0 = rows through registers, 1 = rows through bulk copies (GLSDM_ONCE_BULK overrides the default).
+bool once_bulk() {
+  static const bool on = [] {
+    const char* v = std::getenv("GLSDM_ONCE_BULK");
+    return v == nullptr || v[0] == '\0' ? true : v[0] != '0';
+  }();
+  return on;
+}
+
 template <typename T, int V>
 int launch_once(const FactoredArgs& a, const BankView& v, const EntryArgs& e, const FactoredScratch& f,
                 glsdm_stream_t stream) {
-  apply_once_kernel<T, V><<<blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(a, v, e, f);
+  if (once_bulk()) {
+    constexpr int kBytes = kBulkWarps * 32 * 32 * V * static_cast<int>(sizeof(T)) + 64;
+    GLSDM_CUDA_OK(cudaFuncSetAttribute(apply_once_bulk_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes),
+                  "factored single-writer shared memory");
+    apply_once_bulk_kernel<T, V><<<blocks_for(e.rows, kBulkWarps), kBulkWarps * 32, kBytes, stream>>>(a, v, e, f);
+  } else {
+    apply_once_kernel<T, V><<<blocks_for(e.rows, kWarpsPerBlock), kWarpsPerBlock * 32, 0, stream>>>(a, v, e, f);
+  }
   GLSDM_CUDA_OK(cudaGetLastError(), "factored single-writer apply launch");
   count_launches(1);
   return GLSDM_OK;
@@ -644,6 +827,48 @@ int launch_split(const Workspace& w, const FactoredArgs& a, const BankView& v, c
   long_factored_kernel<T, V><<<long_grid, kWarpsPerBlock * 32, 0, stream>>>(w, a);
   GLSDM_CUDA_OK(cudaGetLastError(), "factored long-segment launch");
   count_launches(2);
+  return GLSDM_OK;
+}
+
+// Largest list the one-launch ordering takes: beyond it the passes want the whole GPU each.
+constexpr int64_t kOrderAllMaxEntries = int64_t{1} << 20;
+
+// GLSDM_ORDER_ALL=0 keeps one launch per stage (for comparisons).
+bool order_all_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("GLSDM_ORDER_ALL");
+    return v == nullptr || v[0] == '\0' ? true : v[0] != '0';
+  }();
+  return on;
+}
+
+// Returns GLSDM_OK when the one-launch ordering ran, a negative value when it cannot run here
+// (the caller then takes the launch-per-stage path), or an error.
+template <int MODE>
+int launch_order_all(BankView v, EntryArgs e, FactoredScratch f, Workspace w, int passes, int64_t entries,
+                     size_t zero_extra, uint32_t* device_status, SortGather g, glsdm_stream_t stream) {
+  static thread_local int resident[64] = {};
+  int device = 0;
+  GLSDM_CUDA_OK(cudaGetDevice(&device), "factored commit cudaGetDevice");
+  if (device < 0 || device >= 64) return -1;
+  if (resident[device] == 0) {
+    int cooperative = 0, sms = 0, per_sm = 0;
+    GLSDM_CUDA_OK(cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device), "cooperative launch attribute");
+    GLSDM_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "SM count");
+    GLSDM_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, order_all_kernel<MODE>, kWarpsPerBlock * 32, 0),
+                  "order_all occupancy");
+    resident[device] = cooperative && per_sm > 0 ? sms * (per_sm < 2 ? per_sm : 2) : -1;
+  }
+  if (resident[device] < 0) return -1;
+  const int64_t row_blocks = (e.rows + kWarpsPerBlock * kEntryRows - 1) / (kWarpsPerBlock * kEntryRows);
+  int64_t want = row_blocks > w.tiles ? row_blocks : w.tiles;
+  if (want < 1) want = 1;
+  const int grid = static_cast<int>(want < resident[device] ? want : resident[device]);
+  void* args[] = {&v, &e, &f, &w, &passes, &entries, &zero_extra, &device_status, &g};
+  GLSDM_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(order_all_kernel<MODE>), dim3(grid),
+                                            dim3(kWarpsPerBlock * 32), args, 0, stream),
+                "factored ordering launch");
+  count_launches(1);
   return GLSDM_OK;
 }
 
@@ -781,6 +1006,19 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
     while (largest_key >> address_bits) ++address_bits;
     const int passes = sort_passes(offsets == nullptr ? address_bits : key_bits);
     const int row_blocks = blocks_for(rows, kWarpsPerBlock * kEntryRows);
+    const SortGather gather = {f.addresses, reinterpret_cast<const uint4*>(f.described),
+                               reinterpret_cast<uint4*>(f.sorted)};
+    int ordered = -1;
+    if (!once && entries <= kOrderAllMaxEntries && order_all_enabled()) {
+      if (compact_owned)
+        ordered = launch_order_all<kOwnedCompact>(v, e, f, w, passes, entries, f.zero_chain, device_status, gather, stream);
+      else if (offsets == nullptr)
+        ordered = launch_order_all<kEveryRoute>(v, e, f, w, passes, entries, 0, device_status, gather, stream);
+      else
+        ordered = launch_order_all<kOwnedRoutes>(v, e, f, w, passes, entries, 0, device_status, gather, stream);
+      if (ordered > 0) return ordered;
+    }
+    if (ordered != GLSDM_OK) {
     if (int s = clear_sort_state(w, once ? f.zero_extra : (compact_owned ? f.zero_chain : 0), stream)) return s;
     glsdm_stream_t order_stream = stream;
     if (once) {
@@ -809,9 +1047,8 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
       count_launches(1);
     }
     GLSDM_CUDA_OK(cudaGetLastError(), "factored entry stage launch");
-    const SortGather gather = {f.addresses, reinterpret_cast<const uint4*>(f.described),
-                               reinterpret_cast<uint4*>(f.sorted)};
     if (int s = run_passes(w, entries, passes, gather, order_stream)) return s;
+    }
   }
   if (!(phases & GLSDM_COMMIT_APPLY)) return GLSDM_OK;
 

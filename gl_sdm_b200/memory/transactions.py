@@ -93,7 +93,9 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
                  not be read afterwards;
       "overlay"  update in place AND keep the old view valid: the commit records the rows it
                  overwrites (an undo log of the touched rows only) and the old view reads
-                 through it (see ``MemoryView`` and ``memory.overlay``).
+                 through it (see ``MemoryView`` and ``memory.overlay``). The sort keys of such
+                 a commit must be monotone in the address, as the reference's keys are: the
+                 log is searched by bisection (a log that is not sets a device status bit).
     ``key_bits`` optionally bounds the sort keys.
     """
     _check_backend(backend)

@@ -243,6 +243,22 @@ class ShardedBankOperator:
         lead = (*queries.shape[:-1], 1)
         return self._finish(plan, n, lead, target, beta, log_decay, queries.shape[1], offset)
 
+    def validate_peers(self, rows):
+        """Optional start-of-epoch check (one small all-gather and a host synchronisation, so not
+        part of the timed path): every rank must be at the same bank version and bring the same
+        number of routing rows and routes per row, or the fixed-size exchanges of the epoch
+        would pair a rank's buffers with another epoch's or with truncated candidate lists.
+        Raises the reference's error for a stale transaction (gl_sdm/memory/transactions.py:72-73)."""
+        mine = torch.tensor([self.version, rows, self.width, self.slots], dtype=torch.int64, device=self.shard.device)
+        everyone = torch.empty(self.world * 4, dtype=torch.int64, device=self.shard.device)
+        self.dist.all_gather_into_tensor(everyone, mine, group=self.group)
+        table = everyone.view(self.world, 4).cpu()
+        if (table[:, 0] != table[0, 0]).any():
+            raise ValueError(f"stale memory transaction: ranks are at bank versions {table[:, 0].tolist()}")
+        if (table[:, 1:] != table[0, 1:]).any():
+            raise ValueError("ranks disagree on the epoch's candidate lists (rows, routes per row, slots): "
+                             f"{table[:, 1:].tolist()}")
+
     def last_routes(self):
         """Routes of the last epoch as every rank holds them: (read slots, read weights, write
         slots, write weights), each [ranks * n, K] in global row order (rank, sequence, token,

@@ -51,6 +51,7 @@ typedef enum { GLSDM_F32 = 0, GLSDM_BF16 = 1 } glsdm_dtype;
 /* Bits OR-ed into *device_status by kernels. */
 #define GLSDM_DEV_ADDRESS_OUT_OF_RANGE 1u
 #define GLSDM_DEV_WAIT_EXPIRED 2u
+#define GLSDM_DEV_LOG_NOT_ASCENDING 4u  /* an undo log whose addresses do not ascend (see glsdm_commit_undo) */
 
 int glsdm_abi_version(void);
 const char* glsdm_status_string(int status);
@@ -220,8 +221,15 @@ int glsdm_commit(const void* values_in, void* values_out, int dtype, int64_t row
  * before. An older version is then the current bank with the logs of all later commits
  * played back, oldest log winning.
  *   glsdm_commit_undo   as glsdm_commit in place, plus
- *     undo_addresses [entries] int64   the entries' addresses in sorted order (runs of equal
- *                                      addresses); valid after the call
+ *     undo_addresses [entries] int64   the entries' addresses in KEY order (runs of equal
+ *                                      addresses); valid after the call. glsdm_overlay_read
+ *                                      searches this array by bisection, so the keys of an
+ *                                      overlay commit must be monotone in the address (the
+ *                                      reference's keys address*(C*L) + position*L + layer
+ *                                      are; so is sorting by the address itself). A log whose
+ *                                      addresses descend anywhere sets
+ *                                      GLSDM_DEV_LOG_NOT_ASCENDING; glsdm_undo_apply does not
+ *                                      depend on the order and stays correct
  *     undo_rows      [entries, dim]    bank dtype; position p holds the old row of
  *                                      undo_addresses[p] iff p is the first of its run
  *   glsdm_undo_apply    writes every logged old row back into the bank (materialises the
@@ -308,12 +316,26 @@ int glsdm_commit_factored_mode(int mode);
  *   that device current; make that first call before any stream capture begins.
  *   All calls on a device share the one array: two calls whose kernels can overlap on the GPU
  *   (different streams without an ordering between them) race and corrupt each other's
- *   commit. Issue them on one stream, or order the streams with events. */
+ *   commit. Issue them on one stream, or order the streams with events. The calls must also
+ *   be serialised on the HOST: a commit is a dozen launches and a memset, and two host threads
+ *   that enqueue on the same stream interleave theirs. One enqueuing thread at a time. */
 int glsdm_commit_static(const void* values_in, void* values_out, int dtype, int64_t row_base,
                         int64_t bank_rows, int32_t dim, const int64_t* addresses,
                         const float* deltas, const int64_t* keys, int64_t entries, int32_t key_bits,
                         uint32_t* device_status, glsdm_stream_t stream);
 int64_t glsdm_commit_static_max_entries(void);
+
+/* The bounded wait of the commit's chained kernels, on its own (a diagnostic with no
+ * counterpart in the reference). One thread sums the 64-bit chain words [0, position) exactly
+ * as a sort tile or a compaction block does: a word whose top two bits are 0 has not been
+ * published yet and is polled, at most 2^20 times (about a second); then the kernel gives up,
+ * sets GLSDM_DEV_WAIT_EXPIRED in *device_status and RETURNS - it never spins for ever and
+ * never traps, so the context stays usable. Words are (kind << 62 | 1 << 56 | count) with
+ * kind 1 = count of one block, 2 = count of that block and all before it. *out_count
+ * receives the sum that was reached. Passing zeroed words shows how a kernel whose
+ * predecessor never arrives ends. */
+int glsdm_wait_probe(const void* words, int64_t position, uint32_t* device_status, uint32_t* out_count,
+                     glsdm_stream_t stream);
 
 /* Dense-key routing (flat keys): scores = queries x keys^T on the tensor cores, fused with
  * a running per-row top-k, so the [rows, slots] score matrix is never stored. The

@@ -126,3 +126,24 @@ def test_views_far_behind_are_rebuilt_once(native):
     assert not first.stale                                                 # rebuilt, not chained
     assert torch.equal(got, native.snapshot_read(bank, index, weights, rows_per_bank=16))
     np.testing.assert_array_equal(first.values.cpu().numpy(), bank.cpu().numpy())
+
+
+def test_keys_that_group_but_do_not_ascend_are_flagged(native):
+    """Keys only have to group equal addresses for the commit itself, but the overlay read
+    bisects the undo log: keys that order the addresses downwards must set the status bit (and
+    the rebuild through glsdm_undo_apply stays right whatever the order)."""
+    g = torch.Generator().manual_seed(3)
+    bank = torch.randn(1, 1, 64, 16, generator=g).to(DEV)
+    before = bank.clone()
+    addresses = torch.tensor([5, 9, 5, 40, 9], device=DEV)
+    deltas = torch.randn(5, 16, generator=g).to(DEV)
+    keys = (63 - addresses) * 8 + torch.arange(5, device=DEV)        # groups, but descending in the address
+    log_addresses, log_rows = native.commit_undo(bank, addresses, deltas, keys)
+    assert log_addresses.tolist() == [40, 9, 9, 5, 5]
+    with pytest.raises(RuntimeError, match="not ascending"):
+        native.raise_on_device_status(DEV)
+    native.undo_apply(bank, log_addresses, log_rows)
+    assert torch.equal(bank, before)
+    # ascending keys leave the status clear
+    native.commit_undo(bank, addresses, deltas, addresses * 8 + torch.arange(5, device=DEV))
+    native.raise_on_device_status(DEV)

@@ -48,6 +48,23 @@ def test_static_scratch_commit_matches_the_workspace_commit_twice(native, dtype)
         native.raise_on_device_status(DEV)
 
 
+def test_static_scratch_commit_at_its_documented_limit(native):
+    """65,536 entries of 256 values, the largest request the built-in array covers, with hot
+    addresses (segments longer than 256 entries take the chunked path and its partial sums)."""
+    rows, dim, entries = 5000, 256, 65536
+    bank = torch.randn(rows, dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    addresses, deltas, keys = _entries(13, rows, entries, dim)
+    addresses[:3000] = 7                        # one address receives 3000+ entries
+    keys[:3000] = 7 * 64 + (keys[:3000] % 64)
+    want = native.commit_rows(bank, addresses, deltas, keys)
+    for _ in range(2):
+        code, got = _commit_static(native, bank, addresses, deltas, keys)
+        assert code == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    native.raise_on_device_status(DEV)
+
+
 def test_static_scratch_commit_rejects_oversized_requests(native):
     lib = native.library()
     limit = lib.glsdm_commit_static_max_entries()
