@@ -60,6 +60,9 @@ WORKLOADS = {
                    128, 32, 16, 4096, torch.bfloat16),
     "c4": Workload("c4", "slot-sharded large bank: bf16 16,777,216 slots, d_v 256, top-32, 64 x 8192 tokens", 1, 4096,
                    256, 128, 32, 64, 8192, torch.bfloat16),
+    "c4s": Workload("c4s", "one quarter of c4's slots (the key shard a GPU holds at 4 GPUs): bf16 4,194,304 slots, d_v 256, "
+                    "top-32, 64 x 8192 tokens; for profiler captures that must stay small", 1, 2048, 256, 128, 32, 64, 8192,
+                    torch.bfloat16),
     "c5": Workload("c5", "skewed routing: bf16 bank 4,194,304 slots, d_v 128, top-16, 4 x 32768 tokens, Zipf(1.1)", 1,
                    2048, 128, 128, 16, 4, 32768, torch.bfloat16, zipf=1.1),
 }

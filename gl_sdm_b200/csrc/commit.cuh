@@ -238,95 +238,129 @@ struct SortGather {
   uint4* sorted_records;     // [entries] by sorted position
 };
 
-// One radix pass in one launch. A block takes the next tile (2048 keys; a warp owns 256
-// consecutive keys and takes them 32 at a time, so (warp, round, lane) order is input order;
-// ranks inside a round come from match_any), publishes its digit counts, obtains the counts
-// of all earlier tiles by looking back along the chain, and scatters. Stable.
-__device__ __forceinline__ void radix_pass_tile(const Workspace& w, const Plan& plan, int64_t entries, int pass,
-                                                const SortGather& g, int64_t tile) {
+// One tile (2048 keys) of one radix pass, in three steps that share the block's scratch:
+//   count    a warp owns 256 consecutive keys and takes them 32 at a time, so (warp, round,
+//            lane) order is input order; ranks inside a round come from match_any;
+//   place    thread d turns the warps' counts of digit d into offsets inside the tile, and
+//            learns how many keys with digit d the EARLIER tiles hold by looking back along
+//            the chain of published words;
+//   scatter  stable: smaller digits first, then earlier tiles, then earlier keys of the tile.
+struct SortScratch {
+  uint32_t warp_count[kSortThreads / 32][kRadix];
+  uint32_t digit_base[kRadix];
+  uint32_t scan_carry[kSortThreads / 32];
+};
+
+struct TileKeys {
+  uint64_t key[kItems];
+  uint32_t id[kItems];
+  uint32_t rank[kItems];
+};
+
+__device__ __forceinline__ void tile_count(const Workspace& w, const Plan& plan, int64_t entries, int pass,
+                                           int64_t tile, SortScratch& sh, TileKeys& k) {
   constexpr int kWarps = kSortThreads / 32;
-  __shared__ uint32_t warp_count[kWarps][kRadix];
-  __shared__ uint32_t digit_base[kRadix];
-  __shared__ uint32_t scan_carry[kWarps];
-  __syncthreads();   // the previous tile of this block is done with the shared arrays
-  for (int i = threadIdx.x; i < kWarps * kRadix; i += kSortThreads) (&warp_count[0][0])[i] = 0;
+  __syncthreads();   // the previous tile of this block is done with the scratch
+  for (int i = threadIdx.x; i < kWarps * kRadix; i += kSortThreads) (&sh.warp_count[0][0])[i] = 0;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t src = plan.source[pass];
   const uint64_t* __restrict__ keys = w.keys[src];
   const uint32_t* __restrict__ ids = w.ids[src];
-  uint64_t* __restrict__ out_keys = w.keys[src ^ 1u];
-  uint32_t* __restrict__ out_ids = w.ids[src ^ 1u];
   const int64_t base = tile * kTile + warp * (kItems * 32);
-  uint64_t key[kItems];
-  uint32_t id[kItems];
-  uint32_t rank[kItems];
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int64_t i = base + r * 32 + lane;
     const bool live = i < entries;
-    key[r] = live ? keys[i] : 0;
-    id[r] = live ? ids[i] : 0;
-    const uint32_t d = live ? digit_of(key[r], pass) : kRadix;  // dead lanes match only each other
+    k.key[r] = live ? keys[i] : 0;
+    k.id[r] = live ? ids[i] : 0;
+    const uint32_t d = live ? digit_of(k.key[r], pass) : kRadix;  // dead lanes match only each other
     const unsigned peers = __match_any_sync(kFullMask, d);
     const uint32_t before = __popc(peers & ((1u << lane) - 1u));
     uint32_t prior = 0;
-    if (live) prior = warp_count[warp][d];
+    if (live) prior = sh.warp_count[warp][d];
     __syncwarp();
-    if (live && before == 0) warp_count[warp][d] = prior + __popc(peers);
+    if (live && before == 0) sh.warp_count[warp][d] = prior + __popc(peers);
     __syncwarp();
-    rank[r] = prior + before;
+    k.rank[r] = prior + before;
   }
   __syncthreads();
-  {
-    const int d = threadIdx.x;  // kSortThreads == kRadix: thread d owns digit d
-    // keys with a smaller digit, over the whole input: exclusive scan of this pass's histogram
-    const uint32_t h = __ldcg(w.histogram + pass * kRadix + d);
-    uint32_t inclusive = h;
+}
+
+// Thread d: the tile's count of digit d; the warps' counts become their offsets inside the tile.
+__device__ __forceinline__ uint32_t tile_total(SortScratch& sh) {
+  const int d = threadIdx.x;  // kSortThreads == kRadix: thread d owns digit d
+  uint32_t total = 0;
+  for (int q = 0; q < kSortThreads / 32; ++q) {
+    const uint32_t c = sh.warp_count[q][d];
+    sh.warp_count[q][d] = total;
+    total += c;
+  }
+  return total;
+}
+
+// Thread d, given the count of digit d in earlier tiles: where digit d of this tile starts.
+__device__ __forceinline__ void tile_place(const Workspace& w, int pass, uint32_t earlier, SortScratch& sh) {
+  const int d = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // keys with a smaller digit, over the whole input: exclusive scan of this pass's histogram
+  const uint32_t h = __ldcg(w.histogram + pass * kRadix + d);
+  uint32_t inclusive = h;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(kFullMask, inclusive, o);
-      if (lane >= o) inclusive += t;
-    }
-    if (lane == 31) scan_carry[warp] = inclusive;
-    // this tile's count of digit d, and the warps' offsets inside it
-    uint32_t total = 0;
-    for (int q = 0; q < kWarps; ++q) {
-      const uint32_t c = warp_count[q][d];
-      warp_count[q][d] = total;
-      total += c;
-    }
-    unsigned long long* mine = w.status + static_cast<size_t>(tile) * kRadix + d;
-    const int tag = pass + 1;
-    uint32_t before = 0;
-    if (tile == 0) {
-      chain_publish(mine, chain_word(kPrefix, tag, total));
-    } else {
-      chain_publish(mine, chain_word(kAggregate, tag, total));
-      before = chain_look_back(w.status + d, kRadix, tile, tag, w.device_status);
-      chain_publish(mine, chain_word(kPrefix, tag, before + total));
-    }
-    __syncthreads();
-    uint32_t smaller = inclusive - h;
-    for (int q = 0; q < warp; ++q) smaller += scan_carry[q];
-    digit_base[d] = smaller + before;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(kFullMask, inclusive, o);
+    if (lane >= o) inclusive += t;
   }
+  if (lane == 31) sh.scan_carry[warp] = inclusive;
   __syncthreads();
+  uint32_t smaller = inclusive - h;
+  for (int q = 0; q < warp; ++q) smaller += sh.scan_carry[q];
+  sh.digit_base[d] = smaller + earlier;
+  __syncthreads();
+}
+
+__device__ __forceinline__ void tile_scatter(const Workspace& w, const Plan& plan, int64_t entries, int pass,
+                                             const SortGather& g, int64_t tile, const SortScratch& sh,
+                                             const TileKeys& k) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t src = plan.source[pass];
+  uint64_t* __restrict__ out_keys = w.keys[src ^ 1u];
+  uint32_t* __restrict__ out_ids = w.ids[src ^ 1u];
+  const int64_t base = tile * kTile + warp * (kItems * 32);
   const bool last = static_cast<uint32_t>(pass) == plan.last_pass && g.addresses != nullptr;
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int64_t i = base + r * 32 + lane;
     if (i < entries) {
-      const uint32_t d = digit_of(key[r], pass);
-      const uint32_t at = digit_base[d] + warp_count[warp][d] + rank[r];
-      out_keys[at] = key[r];
-      out_ids[at] = id[r];
+      const uint32_t d = digit_of(k.key[r], pass);
+      const uint32_t at = sh.digit_base[d] + sh.warp_count[warp][d] + k.rank[r];
+      out_keys[at] = k.key[r];
+      out_ids[at] = k.id[r];
       if (last) {
-        w.sorted_address[at] = g.addresses[id[r]];
-        if (g.records != nullptr) g.sorted_records[at] = g.records[id[r]];
+        w.sorted_address[at] = g.addresses[k.id[r]];
+        if (g.records != nullptr) g.sorted_records[at] = g.records[k.id[r]];
       }
     }
   }
+}
+
+// The three steps joined by the look-back chain.
+__device__ __forceinline__ void radix_pass_tile(const Workspace& w, const Plan& plan, int64_t entries, int pass,
+                                                const SortGather& g, int64_t tile, SortScratch& sh) {
+  TileKeys k;
+  tile_count(w, plan, entries, pass, tile, sh, k);
+  const uint32_t total = tile_total(sh);
+  unsigned long long* mine = w.status + static_cast<size_t>(tile) * kRadix + threadIdx.x;
+  const int tag = pass + 1;
+  uint32_t earlier = 0;
+  if (tile == 0) {
+    chain_publish(mine, chain_word(kPrefix, tag, total));
+  } else {
+    chain_publish(mine, chain_word(kAggregate, tag, total));
+    earlier = chain_look_back(w.status + threadIdx.x, kRadix, tile, tag, w.device_status);
+    chain_publish(mine, chain_word(kPrefix, tag, earlier + total));
+  }
+  tile_place(w, pass, earlier, sh);
+  tile_scatter(w, plan, entries, pass, g, tile, sh, k);
 }
 
 __global__ void __launch_bounds__(kSortThreads)
@@ -336,9 +370,10 @@ radix_pass_kernel(Workspace w, int64_t entries, int pass, SortGather g) {
   entries = live_entries(w.live, entries);
   if (threadIdx.x == 0) my_tile = atomicAdd(&w.plan->ticket[pass], 1u);
   __syncthreads();
+  __shared__ SortScratch scratch;
   const int64_t tile = my_tile;
   if (tile * kTile >= entries) return;
-  radix_pass_tile(w, *w.plan, entries, pass, g, tile);
+  radix_pass_tile(w, *w.plan, entries, pass, g, tile, scratch);
 }
 
 // Per-lane slice of a dim-wide fp32 row: lanes own column blocks of 32*V floats.

@@ -589,10 +589,14 @@ order_all_kernel(BankView bank, EntryArgs a, FactoredScratch f, Workspace w, int
     w.plan->final_buffer = plan.final_buffer;
     w.plan->last_pass = plan.last_pass;
   }
+  __shared__ SortScratch scratch;
   const int64_t tiles = (entries + kTile - 1) / kTile;
+  // (Replacing the look-back by a table of the tiles' counts, a grid-wide barrier and a plain
+  // sum was measured slower: a barrier over ~256 blocks costs more than the walk it saves.)
   for (int p = 0; p < passes; ++p) {
     if (plan.skip[p]) continue;
-    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) radix_pass_tile(w, plan, entries, p, g, tile);
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x)
+      radix_pass_tile(w, plan, entries, p, g, tile, scratch);
     if (static_cast<uint32_t>(p) != plan.last_pass) grid.sync();
   }
 }

@@ -205,6 +205,8 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       if (!__all_sync(kFullMask, ok)) { ok = false; break; }
       const int t0 = split * p.tiles_per_split;
       const int t1 = min(t0 + p.tiles_per_split, p.tiles_total);
+      // rows past the end of the batch (zero-filled, all scores equal) never queue anything
+      const bool row_live = static_cast<int64_t>(unit % p.unit_pairs) * kUnitRows + mb * kBlockRows + quarter * 32 + lane < p.rows;
       for (int t = t0; t < t1 && ok; ++t, ++tile_counter) {
         const uint32_t buf = tile_counter & 1u;
         ok = mbar_wait(&bars->acc_full[buf], acc_phase[buf], abort_flag);
@@ -222,7 +224,7 @@ score_topk_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tmem_load32(taddr + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
           tmem_load32(taddr + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
           tmem_wait_loads();
-          const float floor = *my_floor;
+          const float floor = row_live ? *my_floor : INFINITY;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             float group[11];
