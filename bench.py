@@ -270,15 +270,20 @@ def run_cpu_port(w, routing, steps, warmup, sample_tokens, threads):
 
 
 def run_torch_on_gpu(w, dev, sequences=16):
-    """The reference's tensor-op sequence (the port) on CUDA tensors of the same device: a
-    second comparison beside the CPU baseline. Product-key scores in, `sequences` x chunk
-    tokens of one epoch, functional commit as the reference does it (whole-bank copy) and the
-    in-place variant. Returns a dict of per-stage milliseconds and tokens/s."""
+    """The reference's own code on CUDA tensors of the same GPU: a second comparison beside the CPU
+    baseline. Product-key scores in, `sequences` x chunk tokens of one epoch on the full bank
+    held as the reference holds it (float32, tokens folded into one request): routed read,
+    write proposal (routed read + gather_rows + proposal_delta), the functional commit of
+    gl_sdm/memory/transactions.py (whole-bank copy) and the reference's Triton commit kernel
+    (gl_sdm/memory/backends/commit.py). Uses the staged reference package; where it is not
+    staged, the port's tensor-op sequence (oracle/torch_port.py). Returns per-stage milliseconds
+    and tokens/s."""
     import bench_workloads as workloads
     from oracle import torch_port as port
-    bank = workloads.make_bank(w, dev, banks=1)
+    ref = staged_reference()
     x = workloads.make_epoch_inputs(w, dev, 9000, sequences, w.chunk)
     marks = {}
+    n = sequences * w.chunk
 
     def timed(name, fn):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -289,20 +294,55 @@ def run_torch_on_gpu(w, dev, sequences=16):
         marks[name] = a.elapsed_time(b)
         return out
 
-    for attempt in range(2):   # the first round is the warm-up
-        timed("read_ms", lambda: port.routed_read(bank, x["q_scores"], w.width))
-        a, d, k = timed("proposal_ms", lambda: port.propose(bank, x["k_scores"], w.width, x["target"].float(), x["beta"],
-                                                             x["log_decay"], None, 0, 0, w.chunk, 1))
-        out = timed("commit_copy_ms", lambda: port.commit(bank, a, d, k, in_place=False))
-        del out
-        timed("commit_in_place_ms", lambda: port.commit(bank, a, d, k, in_place=True))
-        del a, d, k
-    n = sequences * w.chunk
-    total = marks["read_ms"] + marks["proposal_ms"] + marks["commit_in_place_ms"]
-    marks = {k: round(v, 3) for k, v in marks.items()}
+    if ref is None:
+        bank = workloads.make_bank(w, dev, banks=1)
+        for attempt in range(2):   # the first round is the warm-up
+            timed("read_ms", lambda: port.routed_read(bank, x["q_scores"], w.width))
+            a, d, k = timed("proposal_ms", lambda: port.propose(bank, x["k_scores"], w.width, x["target"].float(),
+                                                                 x["beta"], x["log_decay"], None, 0, 0, w.chunk, 1))
+            out = timed("commit_copy_ms", lambda: port.commit(bank, a, d, k, in_place=False))
+            del out
+            timed("commit_in_place_ms", lambda: port.commit(bank, a, d, k, in_place=True))
+            del a, d, k
+        total = marks["read_ms"] + marks["proposal_ms"] + marks["commit_in_place_ms"]
+        what = "PyTorch CUDA tensor ops of the reference path (port), in-place commit counted"
+    else:
+        memory, proposal_delta = ref
+        values = workloads.make_bank(w, dev, banks=1).float()
+        fold = lambda t: t.reshape(1, n, *t.shape[2:])   # noqa: E731
+        shape = (1, n, w.heads)
+
+        def propose():
+            prediction, index, weights = memory.routing.torch_routed_read(values, fold(x["k_scores"]), w.width)
+            rows = memory.routing.gather_rows(values, index)
+            addresses = memory.routing.absolute_addresses(values, index)
+            delta = proposal_delta(rows, weights, prediction, x["target"].float().reshape(*shape, w.dim),
+                                   x["beta"].reshape(*shape, 1), x["log_decay"].reshape(*shape, 1),
+                                   torch.ones(1, n, device=dev))
+            position = (torch.arange(n, device=dev) % w.chunk).view(1, n, 1, 1)
+            return addresses.flatten(), delta.flatten(0, 3), (addresses * w.chunk + position).flatten()
+
+        for attempt in range(2):
+            view = memory.MemoryView(values)
+            timed("read_ms", lambda: memory.routing.torch_routed_read(values, fold(x["q_scores"]), w.width))
+            a, d, k = timed("proposal_ms", propose)
+            proposal = memory.WriteProposal(view.version, a, d, view.lineage, k)
+            out = timed("commit_torch_ms", lambda: memory.commit(view, memory.merge(view, [proposal])))
+            del out
+            try:
+                import importlib
+                triton_commit = importlib.import_module("gl_sdm.memory.backends.commit").commit
+                out = timed("commit_triton_ms", lambda: triton_commit(values, a, d, k))
+                del out
+            except Exception as exc:   # noqa: BLE001 - Triton missing or unable to compile here
+                marks["commit_triton_error"] = f"{type(exc).__name__}: {exc}"[:200]
+            del a, d, k, proposal
+        total = marks["read_ms"] + marks["proposal_ms"] + marks["commit_torch_ms"]
+        what = ("the reference's own functions (unmodified package staged under oracle/_ref) on CUDA tensors, float32 bank, "
+                "functional commit counted; commit_triton_ms is its Triton commit kernel on the same entries")
+    marks = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in marks.items()}
     marks.update({"value": n / (total / 1e3), "unit": "tokens/s",
-                  "sample": f"{n} tokens of one commit epoch, product-key scores in, in-place commit counted; "
-                            "PyTorch CUDA tensor ops of the reference path (port) on the same GPU"})
+                  "sample": f"{n} tokens of one commit epoch, product-key scores in; {what}"})
     return marks
 
 
@@ -887,7 +927,25 @@ def phase_times_pk(runner):
     if op.factored and op.heads > 1:
         touched = touched.view(-1, op.heads, prop[0].shape[-1]) + torch.arange(op.heads, device=touched.device).view(1, -1, 1) * op.slots
     unique = float(torch.unique(touched).numel()) / max(1, touched.numel())
+    phase_times_pk.popularity = slot_popularity(touched)
     return {k: v / len(marks) for k, v in phase.items()}, unique
+
+
+def slot_popularity(slots):
+    """How the write routes of one epoch pile up on slots (the skewed configuration plants a
+    Zipf popularity): entries, unique touched rows and their fraction u, the longest segment one
+    address receives, the share of the entries that go to the 1 / 10 / 100 / 1000 most written
+    slots, and the deciles of the per-slot entry counts over the touched slots."""
+    flat = slots.reshape(-1).long()
+    flat = flat[flat >= 0]
+    counts = torch.bincount(flat).float()
+    counts = counts[counts > 0].sort(descending=True).values
+    entries = float(counts.sum())
+    deciles = torch.quantile(counts, torch.linspace(0.1, 0.9, 9, device=counts.device)).tolist()
+    share = {f"top_{k}": float(counts[:k].sum()) / entries for k in (1, 10, 100, 1000)}
+    return {"entries": int(entries), "unique_rows": int(counts.numel()), "unique_row_fraction": counts.numel() / entries,
+            "longest_segment": int(counts[0]), "share_of_entries": share,
+            "deciles_of_entries_per_touched_slot": [round(d, 2) for d in deciles]}
 
 
 def dense_roofline(w, runner, world, peaks, peak_kind):
@@ -918,6 +976,8 @@ def dense_roofline(w, runner, world, peaks, peak_kind):
            "frac_of_burst_peak": achieved / peaks["bf16_tflops"], "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
            "traffic": load_traffic("score_topk", w), "algorithmic_flops_per_launch": flops, "ms_per_launch": ms,
            "phases": {k: {"ms_per_epoch": v} for k, v in phases.items()}}
+    if hasattr(runner.op, "last_routes"):
+        out["slot_popularity"] = slot_popularity(runner.op.last_routes()[2])
     for name, nbytes in hbm.items():
         if name in phases and phases[name] > 0:
             gbs = nbytes / (phases[name] / 1e3) / 1e9
@@ -953,7 +1013,7 @@ def pk_roofline(w, runner, world, peaks, peak_kind):
             "phases": {k: {"ms_per_epoch": phase[k], "algorithmic_GBs": algo[k] / (phase[k] / 1e3) / 1e9,
                            "frac_of_hbm_peak": algo[k] / (phase[k] / 1e3) / 1e9 / peaks["hbm_gbs"],
                            **(extra if k == "commit" else {})} for k in phase},
-            "unique_row_fraction": unique}
+            "unique_row_fraction": unique, "slot_popularity": getattr(phase_times_pk, "popularity", None)}
 
 
 def pk_sharded_roofline(w, runner, world, peaks, peak_kind):
@@ -1126,7 +1186,7 @@ def main():
     ap.add_argument("--sequences", type=int, default=None, help="override the batch (sequences per step)")
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--cpu-sample-tokens", type=int, default=0, help="0 = 256 (dense) / 8192 (pk)")
-    ap.add_argument("--e2e-steps", type=int, default=1)
+    ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input pass (profiling runs)")
     ap.add_argument("--delta-rows", action="store_true",
