@@ -4,10 +4,12 @@
 // commit.cu, deltas rebuilt from their factors in commit_factored.cu).
 #pragma once
 
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "glsdm.h"
@@ -212,12 +214,10 @@ __device__ __forceinline__ void finish_entry_stage(const Workspace& w, int passe
   write_plan(w.histogram, passes, entries, w.plan);
 }
 
-__global__ void __launch_bounds__(kSortThreads)
-prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes, Workspace w) {
-  __shared__ uint32_t local[kDigits][kRadix];
-  for (int i = threadIdx.x; i < kDigits * kRadix; i += kSortThreads) (&local[0][0])[i] = 0;
-  __syncthreads();
-  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+// Tile `tile` of the caller's keys: order-preserving keys, entry ids, digit counts into `local`.
+__device__ __forceinline__ void prepare_tile(const int64_t* __restrict__ keys, int64_t entries, int passes,
+                                             const Workspace& w, int64_t tile, uint32_t (*local)[kRadix]) {
+  const int64_t base = tile * kTile;
   for (int r = 0; r < kItems; ++r) {
     const int64_t i = base + r * kSortThreads + threadIdx.x;
     if (i < entries) {
@@ -227,6 +227,14 @@ prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes, Wo
       for (int p = 0; p < passes; ++p) atomicAdd(&local[p][digit_of(k, p)], 1u);
     }
   }
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+prepare_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes, Workspace w) {
+  __shared__ uint32_t local[kDigits][kRadix];
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += kSortThreads) (&local[0][0])[i] = 0;
+  __syncthreads();
+  prepare_tile(keys, entries, passes, w, blockIdx.x, local);
   finish_entry_stage(w, passes, entries, local);
 }
 
@@ -570,9 +578,90 @@ inline int run_passes(const Workspace& w, int64_t entries, int passes, const Sor
   return GLSDM_OK;
 }
 
-// Sort (keys[i], i) for i in [0, entries): clear, prepare, passes.
+// The same sort in ONE cooperative launch (a grid small enough to be resident at once, with a
+// grid-wide barrier where a launch boundary would be): clear | prepare | plan (every block
+// computes the same one) | pass, pass, ... Small and medium sorts are bound by dependent
+// launches, not bytes. Blocks walk the tiles in increasing order, so every tile a look-back
+// waits for belongs to a resident block that reaches it no later.
+__global__ void __launch_bounds__(kSortThreads)
+sort_all_kernel(const int64_t* __restrict__ keys, int64_t entries, int passes, Workspace w, SortGather g) {
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+  __shared__ uint32_t local[kDigits][kRadix];
+  __shared__ Plan plan;
+  __shared__ SortScratch scratch;
+  {
+    uint4* zero = static_cast<uint4*>(w.zero_from);
+    const size_t cells = w.zero_bytes / sizeof(uint4);
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < cells;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+      zero[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int i = threadIdx.x; i < kDigits * kRadix; i += blockDim.x) (&local[0][0])[i] = 0;
+  grid.sync();
+  const int64_t tiles = (entries + kTile - 1) / kTile;
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) prepare_tile(keys, entries, passes, w, tile, local);
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kRadix; i += blockDim.x) {
+    const uint32_t c = (&local[0][0])[i];
+    if (c) atomicAdd(w.histogram + i, c);
+  }
+  grid.sync();
+  write_plan(w.histogram, passes, entries, &plan);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int p = 0; p < kDigits; ++p) {
+      w.plan->skip[p] = plan.skip[p];
+      w.plan->source[p] = plan.source[p];
+    }
+    w.plan->final_buffer = plan.final_buffer;
+    w.plan->last_pass = plan.last_pass;
+  }
+  for (int p = 0; p < passes; ++p) {
+    if (plan.skip[p]) continue;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x)
+      radix_pass_tile(w, plan, entries, p, g, tile, scratch);
+    if (static_cast<uint32_t>(p) != plan.last_pass) grid.sync();
+  }
+}
+
+constexpr int64_t kSortAllMaxEntries = int64_t{1} << 20;   // beyond it every pass wants the whole GPU
+
+// Blocks of sort_all_kernel that are resident at once on the current device (two per SM at
+// most), or -1 where a cooperative launch is not possible.
+inline int sort_all_resident() {
+  static thread_local int resident[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return -1;
+  if (resident[device] == 0) {
+    int cooperative = 0, sms = 0, per_sm = 0;
+    if (cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sort_all_kernel, kSortThreads, 0) != cudaSuccess)
+      return -1;
+    resident[device] = cooperative && per_sm > 0 ? sms * (per_sm < 2 ? per_sm : 2) : -1;
+  }
+  return resident[device];
+}
+
+// Sort (keys[i], i) for i in [0, entries): one cooperative launch where that pays and is
+// possible (GLSDM_ORDER_ALL=0 switches it off), else clear, prepare and one launch per pass.
 inline int run_sort(const Workspace& w, const int64_t* keys, int64_t entries, int passes,
                     const SortGather& g, glsdm_stream_t stream) {
+  static const bool one_launch = [] {
+    const char* v = getenv("GLSDM_ORDER_ALL");
+    return v == nullptr || v[0] != '0';
+  }();
+  const int resident = (one_launch && entries <= kSortAllMaxEntries) ? sort_all_resident() : -1;
+  if (resident > 0) {
+    const int grid = w.tiles < resident ? (w.tiles < 1 ? 1 : w.tiles) : resident;
+    Workspace ws = w;
+    SortGather gs = g;
+    void* args[] = {&keys, &entries, &passes, &ws, &gs};
+    GLSDM_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(sort_all_kernel), dim3(grid), dim3(kSortThreads),
+                                              args, 0, stream),
+                  "commit sort launch");
+    count_launches(1);
+    return GLSDM_OK;
+  }
   if (int s = clear_sort_state(w, 0, stream)) return s;
   prepare_kernel<<<w.tiles, kSortThreads, 0, stream>>>(keys, entries, passes, w);
   GLSDM_CUDA_OK(cudaGetLastError(), "commit prepare launch");
