@@ -45,6 +45,24 @@ NOMINAL_HBM_GBS = 8000.0
 NOMINAL_BF16_TFLOPS = 2250.0
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keep standard output for the ONE JSON line: libraries loaded later (NCCL prints its
+    version there) get standard error instead."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(text):
+    sys.stdout.flush()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, (text + "\n").encode())
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -369,12 +387,12 @@ def reference_arm(args, w, rank):
     if w.per_request_banks:
         cpu = per_request_cpu_port(w, seconds=10.0)
         ms = cpu.pop("ms_per_step")
-        print(json.dumps({
+        emit(json.dumps({
             "impl": "reference", "metric": "memory-op tokens/s", "value": cpu["value"], "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": per_request_config(w), "cpu_baseline": cpu,
-            "e2e": {"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+            "e2e": {"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
     threads = os.cpu_count() or 1
     tokens = args.cpu_sample_tokens or (256 if args.routing == "dense" else 8192)
@@ -394,7 +412,7 @@ def reference_arm(args, w, rank):
                          "sample": (reference_sample_text if kind == "reference" else cpu_sample_text)(w, args.routing, n, sec)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 # ---- per-request banks (c1 / c2) through the reference-shaped API ------------------------------------
@@ -561,7 +579,7 @@ def stack_reference_arm(args, w, rank):
                 first = time.perf_counter() - t0
     sec = statistics.median(times or [first])
     value = ids.numel() / sec
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": "stack forward tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": len(times), "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 weights, f32 banks", "data": "synthetic",
@@ -569,7 +587,7 @@ def stack_reference_arm(args, w, rank):
                                "top-16, 512-token chunks), forward with every chunk committed", "batch": "1 x 1024 (reduced)"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "reference",
                          "sample": f"1 x 1024 tokens, the unmodified reference model on its own torch memory path, {sec:.2f} s per step"},
-        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 def stack_arm(args, w, rank):
@@ -654,7 +672,7 @@ def stack_arm(args, w, rank):
     total = sum(algo.values())
     gbs = total / (op_ms / 1e3) / 1e9
     tokens = B * T
-    print(json.dumps({
+    emit(json.dumps({
         "metric": "stack forward tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 weights, f32 banks and memory arithmetic", "data": "synthetic",
@@ -671,7 +689,7 @@ def stack_arm(args, w, rank):
         "cpu_baseline": None,
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "h2d_bytes_per_step": host_ids.numel() * 8, "d2h_bytes_per_step": last.numel() * 4},
-        "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+        "gpu_launches": int(launches), "clocks": clocks}))
 
 
 def per_request_arm(args, w, rank):
@@ -736,7 +754,7 @@ def per_request_arm(args, w, rank):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": back.numel() * 4},
         "gpu_launches": int(launches), "clocks": clocks,
     }
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 # ---- correctness of the multi-GPU path, recorded with every number ---------------------------------
@@ -1176,7 +1194,7 @@ def ours(args, w, rank, world, local, dist):
     }
     if extra is not None:
         line["product_key_scores"] = extra
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def main():
@@ -1203,6 +1221,7 @@ def main():
                          "unmodified, over this package instead of the memory API alone")
     ap.add_argument("--no-parity", action="store_true", help="skip the small checked epoch that precedes the timing")
     args = ap.parse_args()
+    claim_stdout()
     w = workloads.WORKLOADS[args.workload]
     if args.sequences or args.seq_len:
         w = w.scaled(args.sequences, args.seq_len)
