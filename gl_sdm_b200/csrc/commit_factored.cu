@@ -1064,7 +1064,15 @@ extern "C" int glsdm_commit_factored_phased(const glsdm_bank* bank, const int32_
   a.bank_rows = static_cast<int64_t>(v.heads) * v.part_stride_rows;
   a.dim = v.dim;
   a.device_status = device_status;
-  if (overlap) {
+  // Single-writer rows on the caller's stream, the shared addresses' rows (other rows) beside
+  // them on the side stream: in the one-call form that stream has just sorted them; when only
+  // the apply phase was asked for it is forked here.
+  if (overlap || (once && once_bulk())) {
+    if (side == nullptr) {
+      if (int s = side_lane(&side)) return s;
+      GLSDM_CUDA_OK(cudaEventRecord(side->fork, stream), "factored commit fork");
+      GLSDM_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0), "factored commit fork wait");
+    }
     const bool f32 = bank->dtype == GLSDM_F32;
     int status;
     switch (v.dim) {
