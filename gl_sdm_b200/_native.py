@@ -46,6 +46,8 @@ SIGNATURES = {
     "glsdm_pk_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _i64,
                               _i64, _i32, _i32, _p, _p, _p, _p, _p]),
     "glsdm_read_backward": (_i, [_BANK, _p, _p, _p, _i, _p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
+    "glsdm_read_backward_version": (_i, [_BANK, _p, _p, _p, _i, _p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p,
+                                         _p, _p, _p, _p]),
     "glsdm_gather_rows": (_i, [_p, _i, _i64, _i32, _p, _i64, _p, _p, _p]),
     "glsdm_token_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _p]),
     "glsdm_write_error": (_i, [_p, _p, _i, _p, _p, _i64, _i32, _p, _p, _p]),
@@ -529,19 +531,10 @@ def overlay_read(values, index, weights, rows_per_bank, logs):
     require_cuda(values, index, weights)
     if index.dtype not in (torch.int64, torch.int32) or weights.dtype != torch.float32:
         raise ValueError("routes are int32/int64 indices with float32 weights")
-    if len(logs) > MAX_UNDO_LOGS:
-        raise ValueError(f"at most {MAX_UNDO_LOGS} undo logs per read")
-    for a, r in logs:
-        require_cuda(a, r)
-        if a.dtype != torch.int64 or r.dtype != values.dtype or r.shape[-1] != values.shape[-1]:
-            raise ValueError("the undo log does not match the bank")
+    n, addresses, log_rows, entries = _log_arrays(values, logs)
     bank = bank_of(values)
     width = index.shape[-1]
     rows = index.numel() // width
-    n = len(logs)
-    addresses = (ctypes.c_void_p * max(n, 1))(*[a.data_ptr() for a, _ in logs])
-    log_rows = (ctypes.c_void_p * max(n, 1))(*[r.data_ptr() for _, r in logs])
-    entries = (ctypes.c_int64 * max(n, 1))(*[a.numel() for a, _ in logs])
     out = torch.empty((*index.shape[:-1], values.shape[-1]), dtype=torch.float32, device=values.device)
     _check(library().glsdm_overlay_read(ctypes.byref(bank), _ptr(index), int(index.dtype == torch.int64),
                                         _ptr(weights), rows, rows_per_bank, width, n, addresses, log_rows, entries,
@@ -646,19 +639,37 @@ def pk_gemm_select(queries, codebooks, width, index_dtype=torch.int64):
     return out_index, out_weights
 
 
-def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half):
+def _log_arrays(values, logs):
+    """ctypes arrays (addresses, rows, entries) of undo logs [(addresses, rows), ...]."""
+    if len(logs) > MAX_UNDO_LOGS:
+        raise ValueError(f"at most {MAX_UNDO_LOGS} undo logs per read")
+    for a, r in logs:
+        require_cuda(a, r)
+        if a.dtype != torch.int64 or r.dtype != values.dtype or r.shape[-1] != values.shape[-1]:
+            raise ValueError("the undo log does not match the bank")
+    n = len(logs)
+    addresses = (ctypes.c_void_p * max(n, 1))(*[a.data_ptr() for a, _ in logs])
+    rows = (ctypes.c_void_p * max(n, 1))(*[r.data_ptr() for _, r in logs])
+    entries = (ctypes.c_int64 * max(n, 1))(*[a.numel() for a, _ in logs])
+    return n, addresses, rows, entries
+
+
+def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half, logs=()):
     """Backward of the routed read: (grad_scores [..., 2*half], addresses [rows*k] int64,
-    grad_rows [rows*k, dim]) - the bank gradient stays compact, one row per route."""
+    grad_rows [rows*k, dim]) - the bank gradient stays compact, one row per route. ``logs``
+    = [(undo_addresses, undo_rows), ...] of the copy-free commits applied to ``values`` since
+    the version that was read (oldest first); empty when ``values`` still is that version."""
     require_cuda(values, grad_out, grad_weights, index, weights)
     bank = bank_of(values)
     width = index.shape[-1]
     rows = index.numel() // width
     dim = values.shape[-1]
+    n, log_addresses, log_rows, log_entries = _log_arrays(values, logs)
     grad_scores = torch.empty((*index.shape[:-1], 2 * half), dtype=torch.float32, device=values.device)
     grad_rows = torch.empty((rows * width, dim), dtype=torch.float32, device=values.device)
     addresses = torch.empty(rows * width, dtype=torch.int64, device=values.device)
-    _check(library().glsdm_read_backward(ctypes.byref(bank), _ptr(grad_out), _ptr(grad_weights), _ptr(index),
-                                         int(index.dtype == torch.int64),
-                                         _ptr(weights), rows, rows_per_bank, width, half, _ptr(grad_scores),
-                                         _ptr(grad_rows), _ptr(addresses), _stream(values.device)))
+    _check(library().glsdm_read_backward_version(
+        ctypes.byref(bank), _ptr(grad_out), _ptr(grad_weights), _ptr(index), int(index.dtype == torch.int64),
+        _ptr(weights), rows, rows_per_bank, width, half, n, log_addresses, log_rows, log_entries,
+        _ptr(grad_scores), _ptr(grad_rows), _ptr(addresses), _stream(values.device)))
     return grad_scores, addresses, grad_rows

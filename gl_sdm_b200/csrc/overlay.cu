@@ -15,29 +15,11 @@
 
 #include "common.cuh"
 #include "glsdm.h"
+#include "overlay.cuh"
 #include "route.cuh"
 
 namespace glsdm {
 namespace {
-
-constexpr int kMaxLogs = GLSDM_MAX_UNDO_LOGS;
-
-struct UndoChain {
-  int count;
-  const int64_t* addresses[kMaxLogs];  // sorted flat addresses of one commit (runs of equal values)
-  const void* rows[kMaxLogs];          // [entries, dim]; the first position of a run holds the row
-  int64_t entries[kMaxLogs];
-};
-
-// First position whose address is >= key.
-__device__ __forceinline__ int64_t lower_bound(const int64_t* __restrict__ sorted, int64_t n, int64_t key) {
-  int64_t lo = 0, hi = n;
-  while (lo < hi) {
-    const int64_t mid = (lo + hi) >> 1;
-    if (sorted[mid] < key) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
 
 // The weighted gather of route.cuh's gather_units with each route's row given by pointer
 // (resolved through the logs) instead of by slot; same grouping, same order of additions, so
@@ -102,14 +84,7 @@ overlay_read_kernel(BankView bank, const void* __restrict__ index, int i64,
     } else {
       weight = weights[at];
       const int64_t flat = part * bank.slots + s;
-      const T* src = static_cast<const T*>(bank.values) + flat * dim;
-      for (int l = 0; l < chain.count; ++l) {
-        const int64_t pos = lower_bound(chain.addresses[l], chain.entries[l], flat);
-        if (pos < chain.entries[l] && chain.addresses[l][pos] == flat) {
-          src = static_cast<const T*>(chain.rows[l]) + pos * dim;
-          break;
-        }
-      }
+      const T* src = version_row<T>(chain, flat, dim, static_cast<const T*>(bank.values) + flat * dim);
       row_ptr = reinterpret_cast<uint64_t>(src);
     }
   }
@@ -156,26 +131,13 @@ extern "C" int glsdm_overlay_read(const glsdm_bank* bank, const void* index, int
   if (bank->dtype != GLSDM_F32 && bank->dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
   if (index == nullptr || weights == nullptr || out_read == nullptr || rows < 0 || rows_per_bank < 1)
     return GLSDM_ERR_ARGUMENT;
-  if (width < 1 || n_logs < 0) return GLSDM_ERR_ARGUMENT;
+  if (width < 1) return GLSDM_ERR_ARGUMENT;
   if (bank->banks < 1 || (bank->banks > 1 && rows > bank->banks * rows_per_bank)) return GLSDM_ERR_ARGUMENT;
   if (width > 32) return GLSDM_ERR_UNSUPPORTED;
-  if (n_logs > kMaxLogs) return GLSDM_ERR_LIMIT;
   if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
-  if (n_logs > 0 && (log_addresses == nullptr || log_rows == nullptr || log_entries == nullptr))
-    return GLSDM_ERR_ARGUMENT;
   UndoChain chain;
-  chain.count = 0;
   bool rows_aligned = true;
-  for (int l = 0; l < n_logs; ++l) {
-    if (log_entries[l] < 0) return GLSDM_ERR_ARGUMENT;
-    if (log_entries[l] == 0) continue;
-    if (log_addresses[l] == nullptr || log_rows[l] == nullptr) return GLSDM_ERR_ARGUMENT;
-    chain.addresses[chain.count] = log_addresses[l];
-    chain.rows[chain.count] = log_rows[l];
-    chain.entries[chain.count] = log_entries[l];
-    rows_aligned = rows_aligned && (reinterpret_cast<uintptr_t>(log_rows[l]) & 15u) == 0;
-    ++chain.count;
-  }
+  if (int s = make_chain(n_logs, log_addresses, log_rows, log_entries, &chain, &rows_aligned)) return s;
   const BankView v = make_view(*bank);
   const int grid = blocks_for(rows, kWarpsPerBlock);
   const bool out_aligned = (reinterpret_cast<uintptr_t>(out_read) & 15u) == 0;

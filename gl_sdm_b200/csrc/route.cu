@@ -1,6 +1,7 @@
 // Routing and snapshot-read kernels (one warp per (request, token, head) row) and their
 // C entry points: glsdm_pk_select, glsdm_snapshot_read, glsdm_pk_select_read,
 // glsdm_pk_propose.
+#include "overlay.cuh"
 #include "route.cuh"
 
 // Resident blocks per SM the selection kernels are compiled for: with 4 (a 64-register budget)
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 read_backward_kernel(BankView bank, const float* __restrict__ grad_out, const float* __restrict__ grad_weights,
                      const void* __restrict__ index, int i64, const float* __restrict__ weights, int64_t rows, int64_t rows_per_bank, int width, int half,
                      float* __restrict__ grad_scores, float* __restrict__ grad_rows,
-                     int64_t* __restrict__ out_addresses) {
+                     int64_t* __restrict__ out_addresses, UndoChain chain) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
   if (row >= rows) return;
@@ -323,17 +324,19 @@ read_backward_kernel(BankView bank, const float* __restrict__ grad_out, const fl
   const float* __restrict__ g = grad_out + row * dim;
   int64_t slot = 0;
   float w = 0.f;
+  uint64_t row_ptr = 0;   // the row as the version that was read held it
   if (lane < width) {
     const int64_t at = row * width + lane;
     slot = i64 ? static_cast<const int64_t*>(index)[at] : static_cast<int64_t>(static_cast<const int32_t*>(index)[at]);
     w = weights[at];
-    out_addresses[at] = part * bank.slots + slot;
+    const int64_t flat = part * bank.slots + slot;
+    out_addresses[at] = flat;
+    row_ptr = reinterpret_cast<uint64_t>(version_row<T>(chain, flat, dim, base + slot * dim));
   }
   float gw = 0.f;
   for (int k = 0; k < width; ++k) {
-    const int64_t a = __shfl_sync(kFullMask, slot, k);
     const float wk = __shfl_sync(kFullMask, w, k);
-    const T* vrow = base + a * dim;
+    const T* vrow = reinterpret_cast<const T*>(shfl_u64(row_ptr, k));
     float* grow = grad_rows + (row * width + k) * dim;
     float partial = 0.f;
     for (int d = lane; d < dim; d += 32) {
@@ -611,11 +614,12 @@ extern "C" int glsdm_pk_combine(const float* left_score, const int32_t* left_ind
   return GLSDM_OK;
 }
 
-extern "C" int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
-                                   const void* index, int index_i64,
-                                   const float* weights, int64_t rows, int64_t rows_per_bank, int32_t width,
-                                   int32_t half, float* grad_scores, float* grad_rows, int64_t* out_addresses,
-                                   glsdm_stream_t stream) {
+extern "C" int glsdm_read_backward_version(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
+                                           const void* index, int index_i64, const float* weights, int64_t rows,
+                                           int64_t rows_per_bank, int32_t width, int32_t half, int32_t n_logs,
+                                           const int64_t* const* log_addresses, const void* const* log_rows,
+                                           const int64_t* log_entries, float* grad_scores, float* grad_rows,
+                                           int64_t* out_addresses, glsdm_stream_t stream) {
   if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
   if (int s = check_bank(bank)) return s;
   if (grad_out == nullptr || index == nullptr || weights == nullptr || grad_scores == nullptr ||
@@ -626,18 +630,29 @@ extern "C" int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out
   if (width > 32) return GLSDM_ERR_UNSUPPORTED;
   if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
   if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
-  if (rows == 0) return GLSDM_OK;
+  UndoChain chain;
+  if (int s = make_chain(n_logs, log_addresses, log_rows, log_entries, &chain, nullptr)) return s;
   const BankView v = make_view(*bank);
   const int grid = blocks_for(rows, kWarpsPerBlock);
   if (bank->dtype == GLSDM_F32)
     read_backward_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
         v, grad_out, grad_weights, index, index_i64, weights, rows, rows_per_bank, width, half, grad_scores, grad_rows,
-        out_addresses);
+        out_addresses, chain);
   else
     read_backward_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
         v, grad_out, grad_weights, index, index_i64, weights, rows, rows_per_bank, width, half, grad_scores, grad_rows,
-        out_addresses);
+        out_addresses, chain);
   GLSDM_CUDA_OK(cudaGetLastError(), "read_backward launch");
   count_launches(1);
   return GLSDM_OK;
+}
+
+extern "C" int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
+                                   const void* index, int index_i64,
+                                   const float* weights, int64_t rows, int64_t rows_per_bank, int32_t width,
+                                   int32_t half, float* grad_scores, float* grad_rows, int64_t* out_addresses,
+                                   glsdm_stream_t stream) {
+  return glsdm_read_backward_version(bank, grad_out, grad_weights, index, index_i64, weights, rows, rows_per_bank,
+                                     width, half, 0, nullptr, nullptr, nullptr, grad_scores, grad_rows,
+                                     out_addresses, stream);
 }

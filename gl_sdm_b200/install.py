@@ -22,8 +22,15 @@ _NAMES = {
 }
 
 
-def install():
-    """Make ``import gl_sdm.memory`` resolve to gl_sdm_b200.memory. Returns the replaced modules."""
+def install(copy_free_commits=None):
+    """Make ``import gl_sdm.memory`` resolve to gl_sdm_b200.memory. Returns the replaced modules.
+
+    ``copy_free_commits`` (True / False; None leaves the setting alone) chooses whether the
+    commits the reference's layers issue (layers/stack.py:65, chunk.py:95, token.py:62,68) copy
+    the bank as the reference does or update it in place with undo logs, see
+    ``memory.transactions.copy_free_commits``."""
+    if copy_free_commits is not None:
+        transactions.copy_free_commits(copy_free_commits)
     previous = {name: sys.modules.get(name) for name in _NAMES}
     sys.modules.update(_NAMES)
     parent = sys.modules.get("gl_sdm")

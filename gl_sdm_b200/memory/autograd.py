@@ -10,6 +10,7 @@ the commit uses, so gradients are reproducible bit for bit.
 import torch
 
 from .. import _native
+from . import state
 
 
 def _dense_bank_gradient(shape, device, addresses, rows):
@@ -22,28 +23,55 @@ def _dense_bank_gradient(shape, device, addresses, rows):
     return zero
 
 
+def version_operand(bank, node):
+    """What a backward reads the rows of an older bank version from: (tensor, undo logs).
+
+    ``node`` is the chain node (state.tail_of) the forward saw. If copy-free commits have
+    since updated the tensor in place, their logs lead back to that version; a chain longer
+    than one kernel call takes is resolved by rebuilding the version once (kept on the node).
+    Any other in-place change of the tensor is an error, as it is for tensors autograd saves."""
+    logs, last = node.later()
+    if bank._version != last.accounted:
+        raise RuntimeError("the memory bank a differentiable read used was modified in place by something other "
+                           "than a copy-free commit")
+    if len(logs) <= _native.MAX_UNDO_LOGS:
+        return bank, [(log.addresses, log.rows) for log in logs]
+    if node.rebuilt is None:
+        rebuilt = bank.clone()
+        for log in reversed(logs):         # newest commit first, so the oldest row wins
+            _native.undo_apply(rebuilt, log.addresses, log.rows)
+        node.rebuilt = rebuilt
+    return node.rebuilt, []
+
+
 class RoutedRead(torch.autograd.Function):
-    """(readings, index, weights) = routed read of factor scores [B, T, H, 2*half]."""
+    """(readings, index, weights) = routed read of factor scores [B, T, H, 2*half].
+
+    The bank is not handed to autograd's saved tensors: a copy-free commit may update it in
+    place before the backward runs, and the backward then reads the version the forward saw
+    through the undo logs (``version_operand``)."""
 
     @staticmethod
     def forward(ctx, memory, scores, width):
         B, T, H, L = scores.shape
         scores = scores.detach().float().contiguous()
         readings, index, weights = _native.pk_select_read(memory.detach(), scores, width, rows_per_bank=T * H)
-        ctx.save_for_backward(memory.detach(), index, weights)
+        ctx.save_for_backward(index, weights)
+        ctx.bank, ctx.node = memory.detach(), state.tail_of(memory)
         ctx.geometry = (T * H, L // 2)
         ctx.mark_non_differentiable(index)
         return readings, index, weights
 
     @staticmethod
     def backward(ctx, grad_readings, _grad_index, grad_weights):
-        memory, index, weights = ctx.saved_tensors
+        index, weights = ctx.saved_tensors
+        memory, logs = version_operand(ctx.bank, ctx.node)
         rows_per_bank, half = ctx.geometry
         if grad_readings is None:
             grad_readings = torch.zeros((*index.shape[:-1], memory.shape[-1]), device=memory.device)
         grad_weights = None if grad_weights is None else grad_weights.float().contiguous()
         grad_scores, addresses, rows = _native.read_backward(memory, grad_readings.float().contiguous(), grad_weights,
-                                                             index, weights, rows_per_bank, half)
+                                                             index, weights, rows_per_bank, half, logs)
         grad_memory = (_dense_bank_gradient(memory.shape, memory.device, addresses, rows).to(memory.dtype)
                        if ctx.needs_input_grad[0] else None)
         return grad_memory, grad_scores if ctx.needs_input_grad[1] else None, None
@@ -81,6 +109,31 @@ class Commit(torch.autograd.Function):
         if ctx.needs_input_grad[2]:
             grad_deltas = _native.gather_rows(incoming.float().view(-1, incoming.shape[-1]), addresses)
         return incoming if ctx.needs_input_grad[0] else None, None, grad_deltas, None, None
+
+
+class OverlayCommit(torch.autograd.Function):
+    """The same commit applied to the bank tensor IN PLACE (no per-commit copy, which the
+    reference pays at gl_sdm/memory/transactions.py:96), differentiable like ``Commit``: the
+    gradient passes through to the previous version unchanged and every delta receives the
+    gradient row of its address. The undo log the kernel writes is appended to ``made``; the
+    caller links it into the tensor's chain so that backwards of earlier reads still find the
+    rows they read (OPTIMIZATION_PLAN.md, "carry gradients back through updates")."""
+
+    @staticmethod
+    def forward(ctx, values, addresses, deltas, keys, key_bits, made):
+        ctx.mark_dirty(values)
+        ctx.save_for_backward(addresses)
+        made.append(_native.commit_undo(values.detach(), addresses, deltas.detach(), keys, key_bits=key_bits))
+        return values
+
+    @staticmethod
+    def backward(ctx, incoming):
+        (addresses,) = ctx.saved_tensors
+        incoming = incoming.contiguous()
+        grad_deltas = None
+        if ctx.needs_input_grad[2]:
+            grad_deltas = _native.gather_rows(incoming.float().view(-1, incoming.shape[-1]), addresses)
+        return incoming if ctx.needs_input_grad[0] else None, None, grad_deltas, None, None, None
 
 
 class TokenRead(torch.autograd.Function):

@@ -16,11 +16,21 @@ class UndoLog:
     """Rows one copy-free commit overwrote: ``addresses`` [entries] int64 sorted (runs of equal
     addresses), ``rows`` [entries, dim] with the old row at the first position of every run.
     ``next`` is the log of the following copy-free commit on the same storage, ``broken`` is
-    set when the storage was later changed without a log (a donated commit)."""
-    __slots__ = ("addresses", "rows", "next", "broken")
+    set when the next change of the storage was made without a log (a donated commit)."""
+    __slots__ = ("addresses", "rows", "next", "broken", "accounted", "rebuilt", "__weakref__")
 
     def __init__(self, addresses, rows):
         self.addresses, self.rows, self.next, self.broken = addresses, rows, None, False
+        self.accounted = None   # the bank tensor's autograd version once this commit was applied
+        self.rebuilt = None     # the version this commit produced, materialised for a long chain
+
+    def later(self):
+        """Logs of the commits applied after this one, oldest first, and the last of them
+        (this one if there is none)."""
+        if self.broken:
+            raise RuntimeError("this snapshot was invalidated by an in-place (donated) commit of a later version")
+        logs = self.next.chain() if self.next is not None else []
+        return logs, (logs[-1] if logs else self)
 
     def chain(self):
         """This log and every later one, oldest commit first."""
@@ -33,6 +43,20 @@ class UndoLog:
         return out
 
 
+def tail_of(values):
+    """The newest node of the undo-log chain of a bank tensor, kept on the tensor object
+    itself: the log of the last copy-free commit, or a node without rows that marks "no such
+    commit yet". A differentiable read holds the node it saw; whatever hangs off it when the
+    backward runs are the commits that have since overwritten rows of the version it read.
+    Nodes nobody holds any more are freed with their rows."""
+    node = getattr(values, "_glsdm_tail", None)
+    if node is None:
+        node = UndoLog(None, None)
+        node.accounted = values._version
+        values._glsdm_tail = node
+    return node
+
+
 class MemoryView:
     """An immutable bank version: values [requests, heads, slots, dim].
 
@@ -43,7 +67,7 @@ class MemoryView:
     version on first use (one bank copy plus the touched rows), while
     ``gl_sdm_b200.memory.overlay.read`` reads it without any copy.
     """
-    __slots__ = ("_storage", "version", "lineage", "_undo", "_made_by")
+    __slots__ = ("_storage", "version", "lineage", "_undo")
 
     def __init__(self, values, version=0, lineage=None):
         bad_shape = values.ndim != 4 or min(values.shape) < 1
@@ -54,7 +78,6 @@ class MemoryView:
         set_(self, "version", version)
         set_(self, "lineage", object() if lineage is None else lineage)
         set_(self, "_undo", None)      # first log between this version and the storage's content
-        set_(self, "_made_by", None)   # the log of the copy-free commit that produced this view
 
     def __setattr__(self, name, value):
         raise FrozenInstanceError(f"cannot assign to field {name!r}")
@@ -74,6 +97,9 @@ class MemoryView:
     def values(self):
         if self._undo is None:
             return self._storage
+        if self._storage.requires_grad and torch.is_grad_enabled():
+            raise RuntimeError("a snapshot behind copy-free commits cannot be rebuilt differentiably: "
+                               "read the newest view, or rebuild under torch.no_grad()")
         from .. import _native
         rebuilt = self._storage.clone()
         for log in reversed(self._undo.chain()):   # newest commit first, so the oldest row wins

@@ -10,7 +10,7 @@ import torch
 
 from .. import _native
 from . import autograd, oracle_hook
-from .state import MemoryView, WriteProposal, WriteBuffer
+from .state import MemoryView, UndoLog, WriteProposal, WriteBuffer, tail_of
 
 _BACKENDS = {"torch", "urm"}
 
@@ -82,7 +82,20 @@ def _concat(tensors):
     return tensors[0] if len(tensors) == 1 else torch.cat(tensors)
 
 
-def commit(view, buffer, reference=False, backend="torch", donate=False, key_bits=0):
+_default_donate = False
+
+
+def copy_free_commits(enabled):
+    """Choose what ``commit`` does when its caller does not say (``donate=None``, which is what
+    the reference's layers pass): False copies the bank per commit as the reference does,
+    True commits in place with undo logs (``donate="overlay"``). Returns the previous choice."""
+    global _default_donate
+    previous = _default_donate == "overlay"
+    _default_donate = "overlay" if enabled else False
+    return previous
+
+
+def commit(view, buffer, reference=False, backend="torch", donate=None, key_bits=0):
     """Apply a write buffer: stable sort by key, per-address fp32 sums, one write per row.
 
     Returns a new view (version + 1, same lineage). ``donate`` chooses what happens to the
@@ -90,12 +103,16 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
       False      the bank is copied, the input view's tensor stays bit-for-bit unchanged
                  (the reference's behaviour, gl_sdm/memory/transactions.py:96);
       True       update in place and hand the same storage to the new view; the old view must
-                 not be read afterwards;
+                 not be read afterwards (not differentiable);
       "overlay"  update in place AND keep the old view valid: the commit records the rows it
                  overwrites (an undo log of the touched rows only) and the old view reads
                  through it (see ``MemoryView`` and ``memory.overlay``). The sort keys of such
                  a commit must be monotone in the address, as the reference's keys are: the
                  log is searched by bisection (a log that is not sets a device status bit).
+                 Differentiable: gradients flow to the deltas and through to the previous
+                 version, and backwards of reads made before the commit resolve the rows they
+                 read through the logs, so a training step needs no bank copy per commit;
+      None       (default) False, or "overlay" after ``copy_free_commits(True)``.
     ``key_bits`` optionally bounds the sort keys.
     """
     _check_backend(backend)
@@ -106,6 +123,8 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
         raise ValueError("cannot mix keyed and unkeyed proposals")
     if reference:
         return oracle_hook.get("commit")(view, buffer)
+    if donate is None:
+        donate = _default_donate
     if donate not in (False, True, "overlay"):
         raise ValueError('donate must be False, True or "overlay"')
     if donate and view.stale:
@@ -115,21 +134,26 @@ def commit(view, buffer, reference=False, backend="torch", donate=False, key_bit
     idx = _concat([p.addresses.reshape(-1) for p in buffer.proposals]).long().contiguous()
     delta = _concat([p.deltas for p in buffer.proposals]).float().contiguous()
     keys = _concat([p.sort_keys.reshape(-1) for p in buffer.proposals]).long().contiguous() if all(keyed) else None
-    if autograd.needs_grad(values, delta):
+    differentiable = autograd.needs_grad(values, delta)
+    if donate == "overlay":
+        if differentiable:
+            made = []
+            values = autograd.OverlayCommit.apply(values, idx, delta, keys, key_bits, made)
+            log = UndoLog(*made[0])
+        else:
+            log = UndoLog(*_native.commit_undo(values, idx, delta, keys, key_bits=key_bits))
+        log.accounted = values._version
+        tail_of(values).next = log         # backwards of earlier differentiable reads continue here
+        values._glsdm_tail = log
+        object.__setattr__(view, "_undo", log)   # the old view reads through this commit and later ones
+        return MemoryView(values, view.version + 1, view.lineage)
+    if differentiable:
         if donate:
             raise ValueError("a donated (in-place) commit cannot be differentiated")
         updated = autograd.Commit.apply(values, idx, delta, keys, key_bits)
         return MemoryView(updated, view.version + 1, view.lineage)
-    if donate == "overlay":
-        from .state import UndoLog
-        log = UndoLog(*_native.commit_undo(values, idx, delta, keys, key_bits=key_bits))
-        newer = MemoryView(values, view.version + 1, view.lineage)
-        object.__setattr__(newer, "_made_by", log)
-        if view._made_by is not None:
-            view._made_by.next = log       # older snapshots continue through this commit
-        object.__setattr__(view, "_undo", log)
-        return newer
-    if donate and view._made_by is not None:
-        view._made_by.broken = True        # older overlay snapshots can no longer be rebuilt
+    if donate:
+        tail_of(values).broken = True      # older snapshots (and reads awaiting a backward) end here
+        values._glsdm_tail = None
     updated = _native.commit_rows(values, idx, delta, keys, out=values if donate else None, key_bits=key_bits)
     return MemoryView(updated, view.version + 1, view.lineage)

@@ -143,6 +143,20 @@ int glsdm_read_backward(const glsdm_bank* bank, const float* grad_out, const flo
                         int32_t half, float* grad_scores, float* grad_rows, int64_t* out_addresses,
                         glsdm_stream_t stream);
 
+/* The same backward for a read of an OLDER bank version whose storage copy-free commits have
+ * since updated in place (the reference plans gradients "back through updates" of compact
+ * overlays, projects/gl-sdm/OPTIMIZATION_PLAN.md, "Represent commits as compact overlays";
+ * the per-commit clone this replaces is gl_sdm/memory/transactions.py:96). Each route's row
+ * is resolved as glsdm_overlay_read resolves it: from the first of the n_logs undo logs
+ * (oldest commit first, host arrays of device pointers / sizes, n_logs <= GLSDM_MAX_UNDO_LOGS)
+ * that holds its address, else from the bank. With n_logs = 0 it is glsdm_read_backward. */
+int glsdm_read_backward_version(const glsdm_bank* bank, const float* grad_out, const float* grad_weights,
+                                const void* index, int index_i64, const float* weights, int64_t rows,
+                                int64_t rows_per_bank, int32_t width, int32_t half, int32_t n_logs,
+                                const int64_t* const* log_addresses, const void* const* log_rows,
+                                const int64_t* log_entries, float* grad_scores, float* grad_rows,
+                                int64_t* out_addresses, glsdm_stream_t stream);
+
 /* Row gather out[n, :] = flat[addresses[n], :] in the bank's dtype, reference
  * gl_sdm/memory/routing.py:37-42 (gather_rows), gl_sdm/memory/transactions.py:19-25
  * (selected) and gl_sdm/memory/backends/primitives.py:14-20 (_gather). */

@@ -131,13 +131,43 @@ def memory_api_standins():
         out.copy_(new)
         return out
 
-    def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half):
+    def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
+        # the layout of the CUDA call: sorted addresses, the old row at the head of every run
+        order = torch.argsort(addresses if keys is None else keys, stable=True)
+        undo_addresses = addresses[order]
+        flat = values.view(-1, values.shape[-1])
+        undo_rows = torch.zeros(addresses.numel(), values.shape[-1], dtype=values.dtype)
+        head = torch.ones_like(undo_addresses, dtype=torch.bool)
+        head[1:] = undo_addresses[1:] != undo_addresses[:-1]
+        undo_rows[head] = flat[undo_addresses[head]]
+        values.copy_(port.commit(values, addresses, deltas, keys))
+        return undo_addresses, undo_rows
+
+    def undo_apply(values, undo_addresses, undo_rows):
+        head = torch.ones_like(undo_addresses, dtype=torch.bool)
+        head[1:] = undo_addresses[1:] != undo_addresses[:-1]
+        values.view(-1, values.shape[-1])[undo_addresses[head]] = undo_rows[head]
+        return values
+
+    def version_rows(values, addresses, logs):
+        """Rows of the version that preceded ``logs`` (oldest commit first)."""
+        rows = values.flatten(0, 2)[addresses].float()
+        found = torch.zeros(addresses.shape, dtype=torch.bool)
+        for undo_addresses, undo_rows in logs:
+            pos = torch.searchsorted(undo_addresses, addresses.reshape(-1)).reshape(addresses.shape)
+            pos = pos.clamp(max=undo_addresses.numel() - 1)
+            hit = (undo_addresses[pos] == addresses) & ~found
+            rows[hit] = undo_rows[pos[hit]].float()
+            found |= hit
+        return rows
+
+    def read_backward(values, grad_out, grad_weights, index, weights, rows_per_bank, half, logs=()):
         lead, width, dim = index.shape[:-1], index.shape[-1], values.shape[-1]
         if index.ndim == 4:
             addresses = port.flat_rows(values, index.long())
         else:
             raise ValueError("stand-in expects [B, T, H, K] routes")
-        rows = values.flatten(0, 2)[addresses].float()
+        rows = version_rows(values, addresses, logs)
         grad_w = (rows * grad_out.unsqueeze(-2)).sum(-1)
         if grad_weights is not None:
             grad_w = grad_w + grad_weights
@@ -150,4 +180,4 @@ def memory_api_standins():
         return grad_scores, addresses.reshape(-1), grad_rows
 
     return dict(require_cuda=require_cuda, require_device=require_cuda, pk_select_read=pk_select_read, gather_rows=gather_rows,
-                commit_rows=commit_rows, read_backward=read_backward)
+                commit_rows=commit_rows, read_backward=read_backward, commit_undo=commit_undo, undo_apply=undo_apply)

@@ -327,3 +327,48 @@ def audited_free_run(cfg, device, batch, length, redraw=None, noise_tol=1e-4):
     if report["first_split_call"] is None:
         close(got, want, "prefill logits", 5e-4, 3e-3)
     return report
+
+
+def copy_free_training_matches(cfg, device, batch, length, strict=False):
+    """The same training-mode forward + backward of the stack bound to this package, once with
+    the reference's per-commit bank copy (gl_sdm/memory/transactions.py:96) and once with
+    copy-free commits: logits and every gradient agree (``strict``: bit for bit, for runs whose
+    dense surround is deterministic; otherwise to 1e-6 / 1e-5, the embedding and attention
+    backwards of the library use atomics)."""
+    _, _, other, model = seeded_pair(cfg, device, "shim")
+    x, targets = tokens(cfg, batch, length, device), tokens(cfg, batch, length, device, seed=7)
+    with other:
+        transactions = other.module("gl_sdm.memory.transactions")
+
+    def run(copy_free):
+        model.zero_grad(set_to_none=True)
+        if device != "cpu":
+            torch.cuda.reset_peak_memory_stats()
+        previous = transactions.copy_free_commits(copy_free)
+        try:
+            with other:
+                hidden, _, _ = model.hidden(x)
+                logits = model.head(hidden)
+                loss = torch.nn.functional.cross_entropy(logits.reshape(-1, cfg["vocab_size"]), targets.flatten())
+                loss.backward()
+        finally:
+            transactions.copy_free_commits(previous)
+        peak = torch.cuda.max_memory_allocated() if device != "cpu" else 0
+        return logits.detach(), {n: p.grad.clone() for n, p in model.named_parameters()}, peak
+
+    want, want_grads, copied_peak = run(False)
+    got, got_grads, free_peak = run(True)
+    exact = 0
+    if strict:
+        assert torch.equal(got, want)
+    else:
+        close(got, want, "logits with copy-free commits", 1e-6, 1e-5)
+    for name, expected in want_grads.items():
+        if strict:
+            assert torch.equal(got_grads[name], expected), name
+        else:
+            close(got_grads[name], expected, f"gradient {name} with copy-free commits", 1e-6, 1e-5)
+        exact += int(torch.equal(got_grads[name], expected))
+    assert want_grads["bank.memory"].abs().sum() > 0
+    return {"bit_equal_gradients": exact, "gradients": len(want_grads), "peak_bytes_copying": copied_peak,
+            "peak_bytes_copy_free": free_peak}

@@ -72,3 +72,9 @@ def test_backend_seam_runs_the_stack(standins):
         checks.prefill_matches(cfg, "cpu", batch=2, length=40, kind="seam")
         assert reads.call_count == 2 * 2 * 3 and commits.call_count == 2
         checks.gradients_match(cfg, "cpu", batch=2, length=40, kind="seam")
+
+
+def test_copy_free_commits_train_the_stack_identically(standins):
+    out = checks.copy_free_training_matches(checks.ref_package.stack_config(**SMALL), "cpu", batch=2, length=40,
+                                            strict=True)
+    assert out["bit_equal_gradients"] == out["gradients"]
