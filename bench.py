@@ -672,6 +672,29 @@ def stack_arm(args, w, rank):
     total = sum(algo.values())
     gbs = total / (op_ms / 1e3) / 1e9
     tokens = B * T
+
+    # the same forward with GlobalLayer.propose served by the fused write proposal (one kernel
+    # instead of routed read + row gather + the delta arithmetic in tensor ops)
+    from gl_sdm_b200.layers import install_fused_proposals
+    plain = forward(ids).float()
+    undo = install_fused_proposals(importlib.import_module("gl_sdm.layers.global_layer"))
+    try:
+        for _ in range(max(1, args.warmup)):
+            fused_out = forward(ids).float()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        f0.record()
+        for _ in range(args.steps):
+            forward(ids)
+        f1.record()
+        torch.cuda.synchronize(dev)
+        fused_ms = f0.elapsed_time(f1) / args.steps
+    finally:
+        undo()
+    fused = {"value": tokens / (fused_ms / 1e3), "unit": "tokens/s", "ms_per_step": fused_ms,
+             "what": "gl_sdm_b200.install(fused_proposals=True): GlobalLayer.propose on glsdm_pk_propose",
+             "hidden_relative_l2_vs_unfused": ((fused_out - plain).norm() / plain.norm().clamp_min(1e-12)).item()}
+    _native.raise_on_device_status(dev)
     emit(json.dumps({
         "metric": "stack forward tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -682,6 +705,7 @@ def stack_arm(args, w, rank):
                    "l2": "per-request banks of 256 MB in all and 4.2 GB of factor scores per layer call: larger than L2"},
         "memory_operator": {"ms_per_step": op_ms, "share_of_forward": op_ms / ms, "tokens_per_s": tokens / (op_ms / 1e3),
                             "ms_by_call": inside, "calls": calls},
+        "fused_proposals": fused,
         "roofline": {"bound": "hbm", "kernel": "memory operator inside the stack (pk_select_read, gather_rows, commit sort + "
                                                 "reduce, whole-bank copy of the functional commit)",
                      "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],

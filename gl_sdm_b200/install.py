@@ -22,8 +22,12 @@ _NAMES = {
 }
 
 
-def install(copy_free_commits=None):
+def install(copy_free_commits=None, fused_proposals=False):
     """Make ``import gl_sdm.memory`` resolve to gl_sdm_b200.memory. Returns the replaced modules.
+
+    ``fused_proposals`` additionally replaces the reference's ``GlobalLayer.propose``
+    (layers/global_layer.py:33-54) by ``gl_sdm_b200.layers.propose``: forward-only calls then
+    build their write proposal with one kernel; it imports ``gl_sdm.layers.global_layer``.
 
     ``copy_free_commits`` (True / False; None leaves the setting alone) chooses whether the
     commits the reference's layers issue (layers/stack.py:65, chunk.py:95, token.py:62,68) copy
@@ -36,6 +40,10 @@ def install(copy_free_commits=None):
     parent = sys.modules.get("gl_sdm")
     if parent is not None:
         parent.memory = memory
+    if fused_proposals:
+        import importlib
+        from .layers import install_fused_proposals
+        install_fused_proposals(importlib.import_module("gl_sdm.layers.global_layer"))
     return previous
 
 

@@ -131,6 +131,12 @@ def memory_api_standins():
         out.copy_(new)
         return out
 
+    def pk_propose(values, scores, target, beta, log_decay, mass, tokens, width, chunk_offset, chunk_size,
+                   num_layers, layer_index, out=None):
+        B, T, H, _ = scores.shape
+        return port.propose(values, scores, width, target.float().view(B, T, H, -1), beta.view(B, T, H),
+                            log_decay.view(B, T, H), mass, chunk_offset, layer_index, chunk_size, num_layers)
+
     def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
         # the layout of the CUDA call: sorted addresses, the old row at the head of every run
         order = torch.argsort(addresses if keys is None else keys, stable=True)
@@ -180,4 +186,5 @@ def memory_api_standins():
         return grad_scores, addresses.reshape(-1), grad_rows
 
     return dict(require_cuda=require_cuda, require_device=require_cuda, pk_select_read=pk_select_read, gather_rows=gather_rows,
-                commit_rows=commit_rows, read_backward=read_backward, commit_undo=commit_undo, undo_apply=undo_apply)
+                commit_rows=commit_rows, read_backward=read_backward, commit_undo=commit_undo, undo_apply=undo_apply,
+                pk_propose=pk_propose)

@@ -9,11 +9,11 @@ and the plan to replace it, OPTIMIZATION_PLAN.md "Represent commits as compact o
 import torch
 
 from gl_sdm_b200.memory import routing, transactions
-from gl_sdm_b200.memory.state import MemoryBank, WriteProposal
+from gl_sdm_b200.memory.state import MemoryBank, MemoryView, WriteProposal
 
 
 def training_step(device, copy_free, commits=3, batch=2, tokens=8, heads=2, half=8, dim=32, width=4, seed=0,
-                  read_old_view_last=True):
+                  storage=torch.float32):
     """Returns (loss, final bank, {name: gradient})."""
     gen = torch.Generator().manual_seed(seed)
     bank = MemoryBank(heads, half * half, dim)
@@ -24,6 +24,8 @@ def training_step(device, copy_free, commits=3, batch=2, tokens=8, heads=2, half
     targets = torch.randn(commits, batch, tokens, heads, dim, generator=gen).to(device).requires_grad_()
     hidden = torch.randn(batch, tokens, heads, dim, generator=gen).to(device)
     view = bank.snapshot(batch)
+    if storage != torch.float32:           # a bf16 request bank derived from the fp32 initialiser
+        view = MemoryView(bank.memory.unsqueeze(0).expand(batch, -1, -1, -1).to(storage))
     previous = transactions.copy_free_commits(copy_free)
     try:
         loss = hidden.new_zeros(())
@@ -36,7 +38,7 @@ def training_step(device, copy_free, commits=3, batch=2, tokens=8, heads=2, half
             rows = routing.gather_rows(view.values, index)
             addresses = routing.absolute_addresses(view.values, index)
             error = targets[c] - prediction
-            delta = weights.unsqueeze(-1) * error.unsqueeze(-2) - 0.125 * rows
+            delta = weights.unsqueeze(-1) * error.unsqueeze(-2) - 0.125 * rows.float()
             positions = torch.arange(tokens, device=device).view(1, tokens, 1, 1)
             keys = addresses * tokens + positions
             proposal = WriteProposal(view.version, addresses.flatten(), delta.flatten(0, 3), view.lineage, keys.flatten())

@@ -3,10 +3,11 @@
 Test infrastructure. The reference resolves ``gl_sdm.memory`` and its backends through
 ``sys.modules`` - partly at import time (layers/stack.py:8, layers/global_layer.py:5-6),
 partly inside functions (model.py:33-34,58; memory/routing.py:47; memory/transactions.py:82)
-- so one process can hold the same unmodified source bound three ways:
+- so one process can hold the same unmodified source bound several ways:
 
   "reference"  the reference's own memory package (its torch path is the oracle);
   "shim"       gl_sdm_b200.install: the whole memory package replaced (package seam);
+  "fused"      the same, plus GlobalLayer.propose replaced by the fused write proposal;
   "seam"       the reference's own memory package with only its two native backend modules,
                backends.urm and backends.commit, replaced (backend seam, config "urm").
 
@@ -69,7 +70,7 @@ def load(kind):
         sys.path.insert(0, REF)
     binding = Binding(kind)
     with binding:
-        if kind == "shim":
+        if kind in ("shim", "fused"):
             from gl_sdm_b200 import install
             install.install()
         elif kind == "seam":
@@ -80,9 +81,12 @@ def load(kind):
             raise ValueError(kind)
         importlib.import_module("gl_sdm.model")
         importlib.import_module("gl_sdm.layers.stack")
+        if kind == "fused":
+            from gl_sdm_b200.layers import install_fused_proposals
+            install_fused_proposals(importlib.import_module("gl_sdm.layers.global_layer"))
         memory = importlib.import_module("gl_sdm.memory")
         origin = os.path.dirname(os.path.abspath(memory.__file__))
-        if kind == "shim":
+        if kind in ("shim", "fused"):
             assert origin.startswith(os.path.join(ROOT, "gl_sdm_b200")), origin
         else:
             assert origin.startswith(REF), origin

@@ -18,6 +18,12 @@ def test_copy_free_step_matches_copying_step():
     _native.raise_on_device_status("cuda")
 
 
+def test_bf16_request_banks():
+    checks.assert_same_step("cuda", commits=4, batch=2, tokens=64, heads=4, half=32, dim=128, width=8,
+                            storage=torch.bfloat16, seed=11)
+    _native.raise_on_device_status("cuda")
+
+
 def test_wide_rows_and_long_chain():
     # more commits than one kernel call takes logs: the oldest reads rebuild their version once
     checks.assert_same_step("cuda", commits=_native.MAX_UNDO_LOGS + 3, batch=1, tokens=32, heads=2, half=16, dim=256,

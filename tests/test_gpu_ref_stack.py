@@ -143,3 +143,29 @@ def test_backend_seam_five_dimensional_scores():
     mine = ours.routed_read(block, memory, scores, 8, physical)
     assert mine[0].shape == (2, 3, 700, 3, 64) and torch.equal(mine[1], want[1])
     torch.testing.assert_close(mine[0], want[0], atol=1e-6, rtol=1e-5)
+
+
+def test_fused_proposals_one_chunk_and_fast_clock():
+    """GlobalLayer.propose served by the fused write proposal (gl_sdm_b200.layers): one chunk at
+    c2 widths against the reference at its fp32 bounds, then the 16-token clock (pending
+    proposals across calls, several commits) with continuation, reset and causality."""
+    out = checks.prefill_matches(ref_package.stack_config(), DEV, batch=2, length=512, redraw=0.02, kind="fused")
+    assert out["commits"] == 1
+    clocked = checks.continuation_reset_causality(ref_package.stack_config(**FAST_CLOCK), DEV, batch=2, length=65,
+                                                  kind="fused")
+    print("fused proposals, one chunk:", out, "| 16-token chunks:", clocked)
+
+
+def test_fused_proposals_equal_the_layer_method_call_by_call():
+    """The same layer, the same inputs: the fused proposal against the reference method bound
+    to this package (addresses and keys identical, delta rows to 1e-6 / 1e-5)."""
+    _, _, binding, model = checks.seeded_pair(ref_package.stack_config(num_hidden_layers=2), DEV, "fused")
+    with binding, torch.inference_mode():
+        layer = next(b for b in model.blocks if hasattr(b, "propose"))
+        cache = model.bank.new_cache(2)
+        x = torch.randn(2, 96, 512, device=DEV)
+        got = layer.propose(x, cache.view, 40, 1, 512, 2)
+        want = layer._glsdm_reference_propose(x, cache.view, 40, 1, 512, 2)
+    assert torch.equal(got.addresses, want.addresses) and torch.equal(got.sort_keys, want.sort_keys)
+    torch.testing.assert_close(got.deltas, want.deltas, atol=1e-6, rtol=1e-5)
+    assert got.base_version == want.base_version and got.lineage is want.lineage

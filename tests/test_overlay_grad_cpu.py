@@ -19,6 +19,10 @@ def test_copy_free_step_matches_copying_step(standins):
     checks.assert_same_step("cpu")
 
 
+def test_bf16_request_banks(standins):
+    checks.assert_same_step("cpu", storage=torch.bfloat16)
+
+
 def test_chain_longer_than_one_call_takes(standins, monkeypatch):
     monkeypatch.setattr(_native, "MAX_UNDO_LOGS", 2)
     checks.assert_same_step("cpu", commits=5)

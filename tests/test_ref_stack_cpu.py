@@ -78,3 +78,18 @@ def test_copy_free_commits_train_the_stack_identically(standins):
     out = checks.copy_free_training_matches(checks.ref_package.stack_config(**SMALL), "cpu", batch=2, length=40,
                                             strict=True)
     assert out["bit_equal_gradients"] == out["gradients"]
+
+
+def test_fused_proposals_serve_the_stack(standins, monkeypatch):
+    from gl_sdm_b200 import _native
+    calls = []
+    fused = _native.pk_propose
+    monkeypatch.setattr(_native, "pk_propose", lambda *a, **k: calls.append(k["layer_index"]) or fused(*a, **k))
+    cfg = checks.ref_package.stack_config(**SMALL)
+    out = checks.prefill_matches(cfg, "cpu", batch=2, length=40, kind="fused")
+    assert out["commits"] == 2
+    assert calls == [1, 3] * 3               # both global layers, three chunk pieces (16 + 16 + 8 tokens)
+    calls.clear()
+    checks.continuation_reset_causality(cfg, "cpu", batch=2, length=37, kind="fused")
+    checks.gradients_match(cfg, "cpu", batch=2, length=40, kind="fused")   # training keeps the reference method
+    assert not calls or max(calls) >= 0
