@@ -25,6 +25,48 @@ def _forward_only(layer, x, snapshot):
                 or any(p.requires_grad for p in layer.attn.parameters()))
 
 
+class _Arena:
+    """One allocation for the proposals of all global layers of one stack call against one
+    snapshot: the commit then finds them side by side and concatenates nothing (the stack's
+    functional commit otherwise copies every delta row once more, gl_sdm/memory/transactions.py:80)."""
+
+    def __init__(self, capacity, dim, device):
+        self.addresses = torch.empty(capacity, dtype=torch.int64, device=device)
+        self.deltas = torch.empty((capacity, dim), dtype=torch.float32, device=device)
+        self.keys = torch.empty(capacity, dtype=torch.int64, device=device)
+        self.capacity, self.used, self.last_layer, self.calls = capacity, 0, -1, 0
+
+    def take(self, entries):
+        lo, hi = self.used, self.used + entries
+        self.used = hi
+        return self.addresses[lo:hi], self.deltas[lo:hi], self.keys[lo:hi]
+
+
+# global layers per stack call of a model with that many blocks: the most seen so far
+_layers_per_call = {}
+
+
+def _buffers(snapshot, entries, dim, device, layer_idx, num_layers):
+    """Where this proposal goes: the next piece of the snapshot's arena when the number of
+    global layers is known (from an earlier call) and the piece fits, else nothing (the
+    kernel wrapper allocates, the commit concatenates)."""
+    if not hasattr(snapshot, "_arena"):
+        return None
+    arena = snapshot._arena
+    fresh = arena is None or layer_idx <= arena.last_layer        # a new stack call begins
+    if fresh:
+        count = _layers_per_call.get(num_layers)
+        arena = _Arena(entries * count if count else 0, dim, device)
+        object.__setattr__(snapshot, "_arena", arena)
+    arena.last_layer = layer_idx
+    arena.calls += 1
+    if arena.calls > _layers_per_call.get(num_layers, 0):
+        _layers_per_call[num_layers] = arena.calls
+    if arena.used + entries > arena.capacity:
+        return None
+    return arena.take(entries)
+
+
 def propose(self, x, snapshot, offset, layer_idx, chunk_size, num_layers, physical=None):
     """Same arguments and result as the reference method: a ``WriteProposal`` of
     [batch*token*head*writes] addresses, delta rows and (address, position, layer) keys
@@ -43,10 +85,11 @@ def propose(self, x, snapshot, offset, layer_idx, chunk_size, num_layers, physic
     log_decay = -F.softplus(router.decay(dense).float() - 4)
     values = snapshot.values
     _native.require_cuda(values)
+    entries = B * T * router.heads * _native.routes_out(router.num_writes, router.half)
     addresses, deltas, keys = _native.pk_propose(
         values, scores.contiguous(), target.contiguous(), beta.contiguous(), log_decay.contiguous(), None,
         tokens=T, width=router.num_writes, chunk_offset=offset, chunk_size=chunk_size, num_layers=num_layers,
-        layer_index=layer_idx)
+        layer_index=layer_idx, out=_buffers(snapshot, entries, values.shape[-1], values.device, layer_idx, num_layers))
     return WriteProposal(snapshot.version, addresses, deltas, snapshot.lineage, keys)
 
 

@@ -67,7 +67,7 @@ class MemoryView:
     version on first use (one bank copy plus the touched rows), while
     ``gl_sdm_b200.memory.overlay.read`` reads it without any copy.
     """
-    __slots__ = ("_storage", "version", "lineage", "_undo")
+    __slots__ = ("_storage", "version", "lineage", "_undo", "_arena")
 
     def __init__(self, values, version=0, lineage=None):
         bad_shape = values.ndim != 4 or min(values.shape) < 1
@@ -78,6 +78,7 @@ class MemoryView:
         set_(self, "version", version)
         set_(self, "lineage", object() if lineage is None else lineage)
         set_(self, "_undo", None)      # first log between this version and the storage's content
+        set_(self, "_arena", None)     # scratch of the proposals being collected against this view
 
     def __setattr__(self, name, value):
         raise FrozenInstanceError(f"cannot assign to field {name!r}")

@@ -78,8 +78,28 @@ def merge(view, proposals):
     return WriteBuffer(view.version, proposals, view.lineage)
 
 
+def _adjacent(tensors):
+    """True when the tensors are consecutive contiguous pieces of one allocation (proposals
+    written side by side into one buffer, see gl_sdm_b200.layers): no copy is needed then."""
+    first = tensors[0]
+    at = first.storage_offset()
+    base = first.untyped_storage().data_ptr()
+    for t in tensors:
+        if (t.dtype != first.dtype or t.shape[1:] != first.shape[1:] or not t.is_contiguous()
+                or t.untyped_storage().data_ptr() != base or t.storage_offset() != at):
+            return False
+        at += t.numel()
+    return True
+
+
 def _concat(tensors):
-    return tensors[0] if len(tensors) == 1 else torch.cat(tensors)
+    if len(tensors) == 1:
+        return tensors[0]
+    if _adjacent(tensors):
+        first = tensors[0]
+        rows = sum(t.shape[0] for t in tensors)
+        return torch.as_strided(first, (rows, *first.shape[1:]), first.stride())
+    return torch.cat(tensors)
 
 
 _default_donate = False

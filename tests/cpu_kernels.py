@@ -134,8 +134,13 @@ def memory_api_standins():
     def pk_propose(values, scores, target, beta, log_decay, mass, tokens, width, chunk_offset, chunk_size,
                    num_layers, layer_index, out=None):
         B, T, H, _ = scores.shape
-        return port.propose(values, scores, width, target.float().view(B, T, H, -1), beta.view(B, T, H),
+        made = port.propose(values, scores, width, target.float().view(B, T, H, -1), beta.view(B, T, H),
                             log_decay.view(B, T, H), mass, chunk_offset, layer_index, chunk_size, num_layers)
+        if out is None:
+            return made
+        for buffer, tensor in zip(out, made):
+            buffer.copy_(tensor.view_as(buffer))
+        return out
 
     def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
         # the layout of the CUDA call: sorted addresses, the old row at the head of every run

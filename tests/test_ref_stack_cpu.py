@@ -90,6 +90,15 @@ def test_fused_proposals_serve_the_stack(standins, monkeypatch):
     assert out["commits"] == 2
     assert calls == [1, 3] * 3               # both global layers, three chunk pieces (16 + 16 + 8 tokens)
     calls.clear()
+    # from the second stack call on, the proposals of one call sit side by side in one buffer
+    # and the commit concatenates without a copy
+    from gl_sdm_b200.memory import transactions
+    copies = []
+    joined = transactions._concat
+    monkeypatch.setattr(transactions, "_concat", lambda ts: copies.append(transactions._adjacent(ts)) or joined(ts))
+    checks.prefill_matches(cfg, "cpu", batch=2, length=32, kind="fused")
+    assert copies and all(copies)
+    calls.clear()
     checks.continuation_reset_causality(cfg, "cpu", batch=2, length=37, kind="fused")
     checks.gradients_match(cfg, "cpu", batch=2, length=40, kind="fused")   # training keeps the reference method
     assert not calls or max(calls) >= 0
