@@ -451,6 +451,34 @@ def api_step(w, values, inputs, memory):
     return readings, view
 
 
+def api_step_fused(w, values, inputs, memory):
+    """The same step with every layer's write side on the fused proposal kernel
+    (glsdm_pk_propose, what gl_sdm_b200.layers.propose runs after the layer's projections): the
+    proposals of a chunk are written side by side into one buffer, so the commit concatenates
+    nothing. Reads and commits are the calls of api_step."""
+    from gl_sdm_b200 import _native
+    view = memory.MemoryView(values)
+    L, C = w.global_layers, w.chunk
+    readings = None
+    for layers in inputs:
+        entries = layers[0]["k_scores"].numel() // layers[0]["k_scores"].shape[-1] * w.width
+        dev = values.device
+        addresses = torch.empty(L * entries, dtype=torch.int64, device=dev)
+        deltas = torch.empty((L * entries, w.dim), dtype=torch.float32, device=dev)
+        keys = torch.empty(L * entries, dtype=torch.int64, device=dev)
+        proposals = []
+        for layer, x in enumerate(layers):
+            readings, _, _ = memory.routing.torch_routed_read(view.values, x["q_scores"], w.width)
+            piece = slice(layer * entries, (layer + 1) * entries)
+            out = (addresses[piece], deltas[piece], keys[piece])
+            _native.pk_propose(view.values, x["k_scores"], x["target"], x["beta"], x["log_decay"], None,
+                               tokens=x["k_scores"].shape[1], width=w.width, chunk_offset=0, chunk_size=C,
+                               num_layers=L, layer_index=layer, out=out)
+            proposals.append(memory.WriteProposal(view.version, *out[:2], view.lineage, out[2]))
+        view = memory.commit(view, memory.merge(view, proposals))
+    return readings, view
+
+
 class PortMemory:
     """The CPU port behind the same five names, so api_step can time it unchanged."""
 
@@ -758,6 +786,26 @@ def per_request_arm(args, w, rank):
     t1.record()
     torch.cuda.synchronize(dev)
     e2e_ms = t0.elapsed_time(t1)
+    # the same step with the write side fused (one kernel per layer instead of routed read +
+    # row gather + tensor ops), checked against the unfused step's bank
+    _, want_view = api_step(w, values, inputs, memory)
+    for _ in range(max(1, args.warmup)):
+        _, got_view = api_step_fused(w, values, inputs, memory)
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    f0.record()
+    for _ in range(args.steps):
+        api_step_fused(w, values, inputs, memory)
+    f1.record()
+    torch.cuda.synchronize(dev)
+    fused_ms = f0.elapsed_time(f1) / args.steps
+    scale = want_view.values.abs().max().clamp_min(1e-30)
+    fused = {"value": w.tokens_per_step / (fused_ms / 1e3), "unit": "tokens/s", "ms_per_step": fused_ms,
+             "what": "write side of every layer on glsdm_pk_propose (gl_sdm_b200.layers.propose), proposals of a "
+                     "chunk side by side in one buffer",
+             "bank_max_rel_err_vs_unfused": ((got_view.values - want_view.values).abs().max() / scale).item()}
+    del want_view, got_view
+    _native.raise_on_device_status(dev)
     algo = workloads.algorithmic_bytes(w, w.tokens_per_step, 1.0)
     # the functional commit writes a new bank per epoch: one read and one write of every bank
     algo["bank_copy"] = w.epochs * 2 * values.numel() * values.element_size()
@@ -774,6 +822,7 @@ def per_request_arm(args, w, rank):
                      "peak_kind": f"of {peak_kind}", "traffic": None, "algorithmic_bytes_per_step": total,
                      "algorithmic_bytes_by_stage": {k: int(v) for k, v in algo.items()}},
         "cpu_baseline": cpu,
+        "fused_proposals": {**fused, "frac_of_hbm_peak": total / (fused_ms / 1e3) / 1e9 / peaks["hbm_gbs"]},
         "e2e": {"value": w.tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "steps": 1,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": back.numel() * 4},
         "gpu_launches": int(launches), "clocks": clocks,
