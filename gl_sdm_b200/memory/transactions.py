@@ -82,6 +82,8 @@ def _adjacent(tensors):
     """True when the tensors are consecutive contiguous pieces of one allocation (proposals
     written side by side into one buffer, see gl_sdm_b200.layers): no copy is needed then."""
     first = tensors[0]
+    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+        return False                      # a view over the pieces would cut their graphs
     at = first.storage_offset()
     base = first.untyped_storage().data_ptr()
     for t in tensors:

@@ -216,3 +216,28 @@ def test_token_clock_backward_wiring_against_reference_gradients(monkeypatch):
     grads = torch.autograd.grad((p.deltas * cot_delta).sum(), [leaves[k] for k in names])
     for k, g in zip(names, grads):
         np.testing.assert_allclose(g.numpy(), gold[f"propose_grad_{k}"], rtol=1e-4, atol=1e-5, err_msg=k)
+
+
+def test_concatenation_of_side_by_side_proposals_copies_nothing():
+    """Proposals written into consecutive pieces of one buffer (gl_sdm_b200.layers) reach the
+    commit as one tensor over the same memory; anything else is concatenated as before."""
+    from gl_sdm_b200.memory import transactions
+    buffer = torch.arange(24.0).view(12, 2)
+    pieces = [buffer[0:3], buffer[3:8], buffer[8:12]]
+    joined = transactions._concat(pieces)
+    assert joined.data_ptr() == buffer.data_ptr() and torch.equal(joined, buffer)
+    inner = transactions._concat([buffer[3:8], buffer[8:12]])
+    assert inner.data_ptr() == buffer[3:].data_ptr() and torch.equal(inner, buffer[3:])
+    for other in ([buffer[0:3], buffer[4:8]],                 # a gap
+                  [buffer[3:8], buffer[0:3]],                 # out of order
+                  [buffer[0:3], buffer[3:8].clone()],         # another allocation
+                  [buffer[0:3], buffer[3:8].double()]):       # another type
+        assert not transactions._adjacent(other)
+    assert torch.equal(transactions._concat([buffer[3:8], buffer[0:3]]), torch.cat([buffer[3:8], buffer[0:3]]))
+    leaf = torch.arange(24.0).view(12, 2).requires_grad_()
+    tracked = [leaf[0:3], leaf[3:12]]
+    assert not transactions._adjacent(tracked)                # their graphs must survive
+    transactions._concat(tracked).sum().backward()
+    assert torch.equal(leaf.grad, torch.ones(12, 2))
+    with torch.no_grad():
+        assert transactions._adjacent(tracked)
