@@ -46,6 +46,8 @@ SIGNATURES = {
     "glsdm_pk_propose": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _i64, _i64, _i64, _i32, _i32, _i64,
                               _i64, _i32, _i32, _p, _p, _p, _p, _p]),
     "glsdm_read_backward": (_i, [_BANK, _p, _p, _p, _i, _p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
+    "glsdm_pk_propose_backward": (_i, [_BANK, _p, _p, _i, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p,
+                                       _p, _p, _p, _p, _p, _p]),
     "glsdm_read_backward_version": (_i, [_BANK, _p, _p, _p, _i, _p, _i64, _i64, _i32, _i32, _i32, _p, _p, _p,
                                          _p, _p, _p, _p]),
     "glsdm_gather_rows": (_i, [_p, _i, _i64, _i32, _p, _i64, _p, _p, _p]),
@@ -300,6 +302,35 @@ def pk_propose(values, scores, target, beta, log_decay, mass, tokens, width, chu
                                       _ptr(addresses), _ptr(deltas), _ptr(keys),
                                       _ptr(status_word(values.device)), _stream(values.device)))
     return addresses, deltas, keys
+
+
+def pk_propose_backward(values, scores, target, beta, log_decay, mass, addresses, grad_deltas, tokens, width, logs=()):
+    """Backward of ``pk_propose``: (grad_scores [..., 2*half], grad_target [rows, dim] fp32, grad_beta
+    [rows], grad_log_decay [rows], grad_rows [rows*k, dim]); the compact bank gradient belongs to
+    ``addresses``. ``logs`` as for ``read_backward``."""
+    require_cuda(values, scores, target, beta, log_decay, mass, addresses, grad_deltas)
+    half = scores.shape[-1] // 2
+    bank = bank_of(values)
+    k = routes_out(width, half)
+    rows = scores.numel() // (2 * half)
+    dim = values.shape[-1]
+    if addresses.dtype != torch.int64 or addresses.numel() != rows * k:
+        raise ValueError("addresses must be the int64 routes the forward returned")
+    if grad_deltas.dtype != torch.float32 or grad_deltas.numel() != rows * k * dim:
+        raise ValueError("grad_deltas must be float32 [rows*k, dim]")
+    n, log_addresses, log_rows, log_entries = _log_arrays(values, logs)
+    dev = values.device
+    grad_scores = torch.empty(scores.shape, dtype=torch.float32, device=dev)
+    grad_target = torch.empty((rows, dim), dtype=torch.float32, device=dev)
+    grad_beta = torch.empty(rows, dtype=torch.float32, device=dev)
+    grad_log_decay = torch.empty(rows, dtype=torch.float32, device=dev)
+    grad_rows = torch.empty((rows * k, dim), dtype=torch.float32, device=dev)
+    _check(library().glsdm_pk_propose_backward(
+        ctypes.byref(bank), _ptr(scores), _ptr(target), _dtype_code(target), _ptr(beta), _ptr(log_decay), _ptr(mass),
+        _ptr(addresses), _ptr(grad_deltas), rows, tokens * values.shape[1], half, width, n, log_addresses, log_rows,
+        log_entries, _ptr(grad_scores), _ptr(grad_target), _ptr(grad_beta), _ptr(grad_log_decay), _ptr(grad_rows),
+        _stream(dev)))
+    return grad_scores, grad_target, grad_beta, grad_log_decay, grad_rows
 
 
 def gather_rows(flat, addresses):

@@ -301,6 +301,30 @@ pk_combine_kernel(const float* __restrict__ left_score, const int32_t* __restric
   store_routes(out_index, i64 != 0, out_weights, row, kout, lane, slot, weight);
 }
 
+// Softmax backward of one row's routes, scattered to the factor scores: gs_k = w_k * (gw_k -
+// sum_j w_j gw_j) is added at left_k and at half + right_k. Routes of the row that share a factor
+// index are summed in route order by one lane, so the result does not depend on scheduling; the
+// row of 2 * half gradients is written whole (zeros elsewhere).
+__device__ __forceinline__ void scatter_score_gradients(float gw, float w, int64_t slot, int width, int half,
+                                                        float* __restrict__ srow, int lane) {
+  const float mean = warp_sum(lane < width ? w * gw : 0.f);
+  const float gs = lane < width ? w * (gw - mean) : 0.f;
+  for (int c = lane; c < 2 * half; c += 32) srow[c] = 0.f;
+  __syncwarp();
+  const int left = static_cast<int>(slot / half), right = static_cast<int>(slot % half);
+  for (int f = 0; f < 2; ++f) {
+    const int mine = lane < width ? (f == 0 ? left : right) : -1 - lane;   // unused lanes match nobody
+    const unsigned peers = __match_any_sync(kFullMask, mine);
+    // every lane walks all routes (the shuffle needs the whole warp) and keeps its peers' terms
+    float sum = 0.f;
+    for (int k = 0; k < width; ++k) {
+      const float term = __shfl_sync(kFullMask, gs, k);
+      if ((peers >> k) & 1u) sum += term;
+    }
+    if (lane < width && (peers & ((1u << lane) - 1u)) == 0) srow[f * half + mine] = sum;
+  }
+}
+
 // Backward of the routed read (reference: autograd through gl_sdm/memory/routing.py:19-28;
 // native counterparts gl_sdm/memory/backends/token.py:69-82,134-144). One warp per row.
 //   gw_k   = <g, row_k>                       (gradient of the softmax weights)
@@ -349,23 +373,133 @@ read_backward_kernel(BankView bank, const float* __restrict__ grad_out, const fl
   }
   // the weights are an output too (the write proposal uses them): add their own gradient
   if (grad_weights != nullptr && lane < width) gw += grad_weights[row * width + lane];
-  const float mean = warp_sum(lane < width ? w * gw : 0.f);
-  const float gs = lane < width ? w * (gw - mean) : 0.f;
-  float* __restrict__ srow = grad_scores + row * 2 * half;
-  for (int c = lane; c < 2 * half; c += 32) srow[c] = 0.f;
-  __syncwarp();
-  const int left = static_cast<int>(slot / half), right = static_cast<int>(slot % half);
-  for (int f = 0; f < 2; ++f) {
-    const int mine = lane < width ? (f == 0 ? left : right) : -1 - lane;   // unused lanes match nobody
-    const unsigned peers = __match_any_sync(kFullMask, mine);
-    // every lane walks all routes (the shuffle needs the whole warp) and keeps its peers' terms
-    float sum = 0.f;
-    for (int k = 0; k < width; ++k) {
-      const float term = __shfl_sync(kFullMask, gs, k);
-      if ((peers >> k) & 1u) sum += term;
-    }
-    if (lane < width && (peers & ((1u << lane) - 1u)) == 0) srow[f * half + mine] = sum;
+  scatter_score_gradients(gw, w, slot, width, half, grad_scores + row * 2 * half, lane);
+}
+
+// Backward of the fused write proposal (glsdm_pk_propose): reference autograd through
+// gl_sdm/layers/global_layer.py:41-51 and gl_sdm/runtime/dense.py:11-14. One warp per row; G_k is
+// the gradient arriving at delta row k.
+//   delta_k = m * ((decay - 1) * row_k + w_k * err),  err = beta * (target - decay * pred),
+//   pred = sum_j w_j row_j,  w = softmax of the selected sums
+//   g_err    = m * sum_k w_k G_k            g_target = beta * g_err
+//   g_beta   = <g_err, target - decay * pred>
+//   g_pred   = -beta * decay * g_err
+//   g_decay  = m * sum_k <G_k, row_k> - beta * <g_err, pred>;   g_log_decay = decay * g_decay
+//   g_w_k    = m * <G_k, err> + <g_pred, row_k>     (then the softmax backward, scattered to the factors)
+//   g_row_k  = m * (decay - 1) * G_k + w_k * g_pred (compact bank gradient, one row per route)
+// The weights are recomputed from the scores and the routes the forward chose; the rows are
+// those of the version the forward read (undo chain). Rows of up to 256 values.
+template <typename T, typename TT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+pk_propose_backward_kernel(BankView bank, UndoChain chain, const float* __restrict__ scores,
+                           const TT* __restrict__ target, const float* __restrict__ beta,
+                           const float* __restrict__ log_decay, const float* __restrict__ mass,
+                           const int64_t* __restrict__ addresses, const float* __restrict__ grad_deltas,
+                           int64_t rows, int64_t rows_per_bank, int half, int width,
+                           float* __restrict__ grad_scores, float* __restrict__ grad_target,
+                           float* __restrict__ grad_beta, float* __restrict__ grad_log_decay,
+                           float* __restrict__ grad_rows) {
+  constexpr int kCols = 8;   // columns per lane: rows of at most 256 values
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+  if (row >= rows) return;
+  const int dim = bank.dim;
+  const int64_t part = partition_of(bank, row, rows_per_bank, nullptr);
+  const T* base = static_cast<const T*>(bank.values) + part * bank.part_stride_rows * dim;
+  const float* __restrict__ srow = scores + row * 2 * half;
+  int64_t slot = 0;
+  float sum = -INFINITY;
+  uint64_t row_ptr = 0;
+  if (lane < width) {
+    const int64_t flat = addresses[row * width + lane];
+    slot = flat - part * bank.slots;
+    sum = __fadd_rn(srow[slot / half], srow[half + slot % half]);
+    row_ptr = reinterpret_cast<uint64_t>(version_row<T>(chain, flat, dim, base + slot * dim));
   }
+  float top = sum;
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFullMask, top, o));
+  const float e = lane < width ? expf(sum - top) : 0.f;
+  const float w = e / warp_sum(e);
+
+  const float decay = expf(log_decay[row]);
+  const float b = beta[row];
+  const float m = mass != nullptr ? mass[row / bank.heads] : 1.0f;
+  float pred[kCols], resid[kCols], gerr[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) pred[c] = gerr[c] = 0.f;
+  for (int k = 0; k < width; ++k) {
+    const T* vrow = reinterpret_cast<const T*>(shfl_u64(row_ptr, k));
+    const float wk = __shfl_sync(kFullMask, w, k);
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int d = c * 32 + lane;
+      if (d < dim) pred[c] = fmaf(wk, Unit<T>::scalar(vrow + d), pred[c]);
+    }
+  }
+  const TT* __restrict__ trow = target + row * dim;
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) {
+    const int d = c * 32 + lane;
+    resid[c] = d < dim ? Unit<TT>::scalar(trow + d) - decay * pred[c] : 0.f;
+  }
+  const float* __restrict__ grow = grad_deltas + row * width * dim;
+  float with_err = 0.f;      // lane k: <G_k, err>
+  float with_rows = 0.f;     // sum_k <G_k, row_k>
+  for (int k = 0; k < width; ++k) {
+    const T* vrow = reinterpret_cast<const T*>(shfl_u64(row_ptr, k));
+    const float wk = __shfl_sync(kFullMask, w, k);
+    float p_err = 0.f, p_rows = 0.f;
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int d = c * 32 + lane;
+      if (d < dim) {
+        const float g = grow[k * dim + d];
+        gerr[c] = fmaf(wk, g, gerr[c]);
+        p_err = fmaf(g, b * resid[c], p_err);
+        p_rows = fmaf(g, Unit<T>::scalar(vrow + d), p_rows);
+      }
+    }
+    const float t_err = warp_sum(p_err);
+    with_rows += warp_sum(p_rows);
+    if (lane == k) with_err = t_err;
+  }
+  float p_beta = 0.f, p_pred = 0.f;
+  float gpred[kCols];
+  float* __restrict__ gt = grad_target + row * dim;
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) {
+    const int d = c * 32 + lane;
+    gerr[c] *= m;
+    gpred[c] = -b * decay * gerr[c];
+    p_beta = fmaf(gerr[c], resid[c], p_beta);
+    p_pred = fmaf(gerr[c], pred[c], p_pred);
+    if (d < dim) gt[d] = b * gerr[c];
+  }
+  const float g_beta = warp_sum(p_beta);
+  const float g_decay = m * with_rows - b * warp_sum(p_pred);
+  if (lane == 0) {
+    grad_beta[row] = g_beta;
+    grad_log_decay[row] = g_decay * decay;
+  }
+  const float keep = m * (decay - 1.0f);
+  float gw = 0.f;
+  for (int k = 0; k < width; ++k) {
+    const T* vrow = reinterpret_cast<const T*>(shfl_u64(row_ptr, k));
+    const float wk = __shfl_sync(kFullMask, w, k);
+    float* __restrict__ out = grad_rows + (row * width + k) * dim;
+    float p = 0.f;
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int d = c * 32 + lane;
+      if (d < dim) {
+        p = fmaf(gpred[c], Unit<T>::scalar(vrow + d), p);
+        out[d] = fmaf(keep, grow[k * dim + d], wk * gpred[c]);
+      }
+    }
+    const float t = warp_sum(p);
+    if (lane == k) gw = m * with_err + t;
+  }
+  scatter_score_gradients(gw, w, slot, width, half, grad_scores + row * 2 * half, lane);
 }
 
 int route_shape(int32_t half, int32_t width, int* kf, int* kout) {
@@ -540,6 +674,49 @@ extern "C" int glsdm_pk_propose(const glsdm_bank* bank, const float* scores, con
   }
 #undef GLSDM_PROPOSE
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_propose launch");
+  count_launches(1);
+  return GLSDM_OK;
+}
+
+extern "C" int glsdm_pk_propose_backward(const glsdm_bank* bank, const float* scores, const void* target,
+                                         int target_dtype, const float* beta, const float* log_decay,
+                                         const float* mass, const int64_t* addresses, const float* grad_deltas,
+                                         int64_t rows, int64_t rows_per_bank, int32_t half, int32_t width,
+                                         int32_t n_logs, const int64_t* const* log_addresses,
+                                         const void* const* log_rows, const int64_t* log_entries,
+                                         float* grad_scores, float* grad_target, float* grad_beta,
+                                         float* grad_log_decay, float* grad_rows, glsdm_stream_t stream) {
+  if (rows == 0) return GLSDM_OK;   // nothing to do: pointers of empty arrays may be null
+  if (int s = check_bank(bank)) return s;
+  int kf, kout;
+  if (int s = route_shape(half, width, &kf, &kout)) return s;
+  if (scores == nullptr || target == nullptr || beta == nullptr || log_decay == nullptr || addresses == nullptr ||
+      grad_deltas == nullptr || grad_scores == nullptr || grad_target == nullptr || grad_beta == nullptr ||
+      grad_log_decay == nullptr || grad_rows == nullptr)
+    return GLSDM_ERR_ARGUMENT;
+  if (rows < 0 || rows_per_bank < 1) return GLSDM_ERR_ARGUMENT;
+  if (int s = check_rows(bank, rows, rows_per_bank)) return s;
+  if (static_cast<int64_t>(half) * half != bank->slots) return GLSDM_ERR_ARGUMENT;
+  if (bank->slot_lo != 0 || bank->slot_hi != bank->slots) return GLSDM_ERR_UNSUPPORTED;
+  if (bank->dim > 256) return GLSDM_ERR_UNSUPPORTED;
+  if (target_dtype != GLSDM_F32 && target_dtype != GLSDM_BF16) return GLSDM_ERR_ARGUMENT;
+  UndoChain chain;
+  if (int s = make_chain(n_logs, log_addresses, log_rows, log_entries, &chain, nullptr)) return s;
+  const BankView v = make_view(*bank);
+  const int grid = blocks_for(rows, kWarpsPerBlock);
+#define GLSDM_PROPOSE_BACKWARD(T, TT)                                                                       \
+  pk_propose_backward_kernel<T, TT><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                              \
+      v, chain, scores, static_cast<const TT*>(target), beta, log_decay, mass, addresses, grad_deltas, rows, \
+      rows_per_bank, half, kout, grad_scores, grad_target, grad_beta, grad_log_decay, grad_rows)
+  if (bank->dtype == GLSDM_F32) {
+    if (target_dtype == GLSDM_F32) GLSDM_PROPOSE_BACKWARD(float, float);
+    else GLSDM_PROPOSE_BACKWARD(float, __nv_bfloat16);
+  } else {
+    if (target_dtype == GLSDM_F32) GLSDM_PROPOSE_BACKWARD(__nv_bfloat16, float);
+    else GLSDM_PROPOSE_BACKWARD(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef GLSDM_PROPOSE_BACKWARD
+  GLSDM_CUDA_OK(cudaGetLastError(), "pk_propose_backward launch");
   count_launches(1);
   return GLSDM_OK;
 }

@@ -5,24 +5,17 @@ the prediction, gathers the selected rows, forms the delta rows with tensor arit
 (gl_sdm/runtime/dense.py:11-14) and builds the canonical sort keys: three operator calls and
 about a dozen elementwise passes over [batch, token, head, route, dim]. ``propose`` below is a
 drop-in for that method: the projections stay the layer's own modules (same parameters, same
-checkpoint), everything after them is ``glsdm_pk_propose``. It serves forward-only calls
-(prefill, decode, evaluation); when a gradient is needed, or the layer asks for the
-reference path, it hands the call to the method it replaced.
+checkpoint), everything after them is ``glsdm_pk_propose``, and under autograd its backward
+is ``glsdm_pk_propose_backward``: none of the [batch, token, head, route, dim] intermediates
+of the tensor-op expression is computed or kept for the backward. A layer that asks for the
+reference path gets the method this one replaced.
 """
 import torch
 import torch.nn.functional as F
 
 from .. import _native
+from ..memory import autograd
 from ..memory.state import WriteProposal
-
-
-def _forward_only(layer, x, snapshot):
-    if layer.attn.reference:
-        return False
-    if not torch.is_grad_enabled():
-        return True
-    return not (x.requires_grad or snapshot.values.requires_grad
-                or any(p.requires_grad for p in layer.attn.parameters()))
 
 
 class _Arena:
@@ -67,14 +60,25 @@ def _buffers(snapshot, entries, dim, device, layer_idx, num_layers):
     return arena.take(entries)
 
 
+def _needs_grad(layer, x, snapshot):
+    if not torch.is_grad_enabled():
+        return False
+    return (x.requires_grad or snapshot.values.requires_grad
+            or any(p.requires_grad for p in layer.attn.parameters()) or any(p.requires_grad for p in layer.norm1.parameters()))
+
+
 def propose(self, x, snapshot, offset, layer_idx, chunk_size, num_layers, physical=None):
     """Same arguments and result as the reference method: a ``WriteProposal`` of
     [batch*token*head*writes] addresses, delta rows and (address, position, layer) keys
-    against ``snapshot``. ``physical`` (the reference's padded bank) is not needed."""
-    if not _forward_only(self, x, snapshot):
+    against ``snapshot``. ``physical`` (the reference's padded bank) is not needed.
+    Differentiable (``autograd.FusedProposal``) for rows of up to 256 values; wider rows under
+    autograd, and layers that ask for the reference path, go to the replaced method."""
+    router = self.attn
+    values = snapshot.values
+    training = _needs_grad(self, x, snapshot)
+    if router.reference or (training and values.shape[-1] > 256):
         return self._glsdm_reference_propose(x, snapshot, offset, layer_idx, chunk_size, num_layers, physical)
     B, T, _ = x.shape
-    router = self.attn
     z = self.norm1(x)
     scores = router.k(z.to(router.k.weight.dtype)).float().view(B, T, router.heads, -1)
     dense = z.to(router.v.weight.dtype)
@@ -83,13 +87,17 @@ def propose(self, x, snapshot, offset, layer_idx, chunk_size, num_layers, physic
         target = target.float()
     beta = router.beta(dense).float().sigmoid()
     log_decay = -F.softplus(router.decay(dense).float() - 4)
-    values = snapshot.values
     _native.require_cuda(values)
-    entries = B * T * router.heads * _native.routes_out(router.num_writes, router.half)
-    addresses, deltas, keys = _native.pk_propose(
-        values, scores.contiguous(), target.contiguous(), beta.contiguous(), log_decay.contiguous(), None,
-        tokens=T, width=router.num_writes, chunk_offset=offset, chunk_size=chunk_size, num_layers=num_layers,
-        layer_index=layer_idx, out=_buffers(snapshot, entries, values.shape[-1], values.device, layer_idx, num_layers))
+    geometry = dict(tokens=T, width=router.num_writes, chunk_offset=offset, chunk_size=chunk_size,
+                    num_layers=num_layers, layer_index=layer_idx)
+    if training:
+        addresses, deltas, keys = autograd.FusedProposal.apply(values, scores, target, beta, log_decay,
+                                                               tuple(geometry.values()))
+    else:
+        entries = B * T * router.heads * _native.routes_out(router.num_writes, router.half)
+        addresses, deltas, keys = _native.pk_propose(
+            values, scores.contiguous(), target.contiguous(), beta.contiguous(), log_decay.contiguous(), None,
+            out=_buffers(snapshot, entries, values.shape[-1], values.device, layer_idx, num_layers), **geometry)
     return WriteProposal(snapshot.version, addresses, deltas, snapshot.lineage, keys)
 
 

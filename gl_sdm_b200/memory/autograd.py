@@ -136,6 +136,47 @@ class OverlayCommit(torch.autograd.Function):
         return incoming if ctx.needs_input_grad[0] else None, None, grad_deltas, None, None, None
 
 
+class FusedProposal(torch.autograd.Function):
+    """(addresses, deltas, keys) of the fused write proposal, differentiable in the bank, the
+    write scores, the target, beta and the log-decay (reference: autograd through
+    gl_sdm/layers/global_layer.py:41-51 and gl_sdm/runtime/dense.py:11-14). Forward and backward
+    are one kernel each; nothing of size [rows, routes, dim] is kept between them except the
+    delta rows themselves. Like ``RoutedRead`` the backward reads the rows of the bank version
+    the forward saw through the undo logs of later copy-free commits."""
+
+    @staticmethod
+    def forward(ctx, values, scores, target, beta, log_decay, geometry):
+        tokens, width, chunk_offset, chunk_size, num_layers, layer_index = geometry
+        scores = scores.detach().float().contiguous()
+        target = target.detach().contiguous()
+        beta, log_decay = beta.detach().float().contiguous(), log_decay.detach().float().contiguous()
+        addresses, deltas, keys = _native.pk_propose(values.detach(), scores, target, beta, log_decay, None,
+                                                     tokens=tokens, width=width, chunk_offset=chunk_offset,
+                                                     chunk_size=chunk_size, num_layers=num_layers, layer_index=layer_index)
+        ctx.save_for_backward(scores, target, beta, log_decay, addresses)
+        ctx.bank, ctx.node = values.detach(), state.tail_of(values)
+        ctx.geometry = (tokens, width)
+        ctx.mark_non_differentiable(addresses, keys)
+        return addresses, deltas, keys
+
+    @staticmethod
+    def backward(ctx, _grad_addresses, grad_deltas, _grad_keys):
+        scores, target, beta, log_decay, addresses = ctx.saved_tensors
+        memory, logs = version_operand(ctx.bank, ctx.node)
+        tokens, width = ctx.geometry
+        if grad_deltas is None:
+            return None, None, None, None, None, None
+        grad_scores, grad_target, grad_beta, grad_log_decay, grad_rows = _native.pk_propose_backward(
+            memory, scores, target, beta, log_decay, None, addresses, grad_deltas.float().contiguous(), tokens, width, logs)
+        need = ctx.needs_input_grad
+        grad_memory = (_dense_bank_gradient(memory.shape, memory.device, addresses, grad_rows).to(memory.dtype)
+                       if need[0] else None)
+        return (grad_memory, grad_scores if need[1] else None,
+                grad_target.view(target.shape).to(target.dtype) if need[2] else None,
+                grad_beta.view(beta.shape) if need[3] else None,
+                grad_log_decay.view(log_decay.shape) if need[4] else None, None)
+
+
 class TokenRead(torch.autograd.Function):
     """Token-clock weighted read of supplied routes [A, H, K] -> [A, H, D].
 

@@ -157,6 +157,28 @@ int glsdm_read_backward_version(const glsdm_bank* bank, const float* grad_out, c
                                 const int64_t* log_entries, float* grad_scores, float* grad_rows,
                                 int64_t* out_addresses, glsdm_stream_t stream);
 
+/* Backward of glsdm_pk_propose: reference autograd through gl_sdm/layers/global_layer.py:41-51
+ * and gl_sdm/runtime/dense.py:11-14 (proposal_delta), i.e. through the write route's softmax
+ * weights, the prediction read, the row gather and the delta expression, in one kernel.
+ *   scores / target / beta / log_decay / mass   the forward's operands
+ *   addresses    [rows*out_k] int64 as the forward returned them (the routes it chose)
+ *   grad_deltas  [rows*out_k, dim] fp32, the gradient arriving at the delta rows
+ *   log_*        undo logs of the copy-free commits applied to the bank since the forward
+ *                (oldest first, as for glsdm_read_backward_version); n_logs = 0 if none
+ *   grad_scores  [rows, 2*half] fp32 written whole; grad_target [rows, dim] fp32;
+ *   grad_beta / grad_log_decay [rows] fp32 (beta as passed, i.e. after the sigmoid)
+ *   grad_rows    [rows*out_k, dim] fp32 compact bank gradient, one row per route at
+ *                addresses[i]: fold it into a bank with glsdm_commit
+ * Rows of at most 256 values (GLSDM_ERR_UNSUPPORTED beyond); no gradient for mass. */
+int glsdm_pk_propose_backward(const glsdm_bank* bank, const float* scores, const void* target,
+                              int target_dtype, const float* beta, const float* log_decay,
+                              const float* mass, const int64_t* addresses, const float* grad_deltas,
+                              int64_t rows, int64_t rows_per_bank, int32_t half, int32_t width,
+                              int32_t n_logs, const int64_t* const* log_addresses,
+                              const void* const* log_rows, const int64_t* log_entries,
+                              float* grad_scores, float* grad_target, float* grad_beta,
+                              float* grad_log_decay, float* grad_rows, glsdm_stream_t stream);
+
 /* Row gather out[n, :] = flat[addresses[n], :] in the bank's dtype, reference
  * gl_sdm/memory/routing.py:37-42 (gather_rows), gl_sdm/memory/transactions.py:19-25
  * (selected) and gl_sdm/memory/backends/primitives.py:14-20 (_gather). */

@@ -142,6 +142,31 @@ def memory_api_standins():
             buffer.copy_(tensor.view_as(buffer))
         return out
 
+    def pk_propose_backward(values, scores, target, beta, log_decay, mass, addresses, grad_deltas, tokens, width,
+                            logs=()):
+        # autograd through the port's expression, on the rows of the version that was read
+        B, T, H, _ = scores.shape
+        dim = values.shape[-1]
+        old = values.detach().clone()
+        for undo_addresses, undo_rows in reversed(list(logs)):
+            undo_apply(old, undo_addresses, undo_rows)
+        bank = old.float().requires_grad_()
+        leaves = [scores.detach().clone().requires_grad_(), target.detach().float().view(B, T, H, dim).requires_grad_(),
+                  beta.detach().view(B, T, H).clone().requires_grad_(), log_decay.detach().view(B, T, H).clone().requires_grad_()]
+        with torch.enable_grad():
+            made_addresses, deltas, _ = port.propose(bank, leaves[0], width, leaves[1], leaves[2], leaves[3], mass, 0, 0, 1, 1)
+            assert torch.equal(made_addresses, addresses)
+            rows = bank.flatten(0, 2)[addresses]              # for the compact bank gradient
+            grads = torch.autograd.grad(deltas, [bank] + leaves, grad_deltas.view_as(deltas))
+        grad_rows = grads[0].flatten(0, 2)[addresses]
+        # one row per route: a bank row written by several routes must not be counted several times
+        order = torch.argsort(addresses, stable=True)
+        first = torch.ones_like(addresses, dtype=torch.bool)
+        first[order[1:]] = addresses[order[1:]] != addresses[order[:-1]]
+        grad_rows = grad_rows * first.unsqueeze(-1)
+        del rows
+        return grads[1], grads[2].reshape(-1, dim), grads[3].reshape(-1), grads[4].reshape(-1), grad_rows
+
     def commit_undo(values, addresses, deltas, keys=None, key_bits=0):
         # the layout of the CUDA call: sorted addresses, the old row at the head of every run
         order = torch.argsort(addresses if keys is None else keys, stable=True)
@@ -192,4 +217,4 @@ def memory_api_standins():
 
     return dict(require_cuda=require_cuda, require_device=require_cuda, pk_select_read=pk_select_read, gather_rows=gather_rows,
                 commit_rows=commit_rows, read_backward=read_backward, commit_undo=commit_undo, undo_apply=undo_apply,
-                pk_propose=pk_propose)
+                pk_propose=pk_propose, pk_propose_backward=pk_propose_backward)

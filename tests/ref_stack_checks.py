@@ -329,13 +329,13 @@ def audited_free_run(cfg, device, batch, length, redraw=None, noise_tol=1e-4):
     return report
 
 
-def copy_free_training_matches(cfg, device, batch, length, strict=False):
+def copy_free_training_matches(cfg, device, batch, length, strict=False, kind="shim"):
     """The same training-mode forward + backward of the stack bound to this package, once with
     the reference's per-commit bank copy (gl_sdm/memory/transactions.py:96) and once with
     copy-free commits: logits and every gradient agree (``strict``: bit for bit, for runs whose
     dense surround is deterministic; otherwise to 1e-6 / 1e-5, the embedding and attention
     backwards of the library use atomics)."""
-    _, _, other, model = seeded_pair(cfg, device, "shim")
+    _, _, other, model = seeded_pair(cfg, device, kind)
     x, targets = tokens(cfg, batch, length, device), tokens(cfg, batch, length, device, seed=7)
     with other:
         transactions = other.module("gl_sdm.memory.transactions")

@@ -169,3 +169,43 @@ def test_fused_proposals_equal_the_layer_method_call_by_call():
     assert torch.equal(got.addresses, want.addresses) and torch.equal(got.sort_keys, want.sort_keys)
     torch.testing.assert_close(got.deltas, want.deltas, atol=1e-6, rtol=1e-5)
     assert got.base_version == want.base_version and got.lineage is want.lineage
+
+
+def test_fused_proposal_gradients_equal_autograd_through_the_layer_method():
+    """Training: the fused proposal's backward kernel against autograd through the method it
+    replaces, same layer, same inputs, a random gradient arriving at the delta rows - for the
+    hidden state, every parameter of the write side and the bank."""
+    _, _, binding, model = checks.seeded_pair(ref_package.stack_config(num_hidden_layers=2), DEV, "fused")
+    torch.manual_seed(3)
+    with binding:
+        layer = next(b for b in model.blocks if hasattr(b, "propose"))
+        x = torch.randn(2, 96, 512, device=DEV, requires_grad=True)
+        incoming = None
+        results = []
+        for method in (layer.propose, layer._glsdm_reference_propose):
+            model.zero_grad(set_to_none=True)
+            x.grad = None
+            cache = model.bank.new_cache(2)
+            proposal = method(x, cache.view, 40, 1, 512, 2)
+            if incoming is None:
+                incoming = torch.randn_like(proposal.deltas)
+            (proposal.deltas * incoming).sum().backward()
+            grads = {"x": x.grad.clone(), "bank": model.bank.memory.grad.clone()}
+            grads.update({n: p.grad.clone() for n, p in layer.named_parameters() if p.grad is not None})
+            results.append((proposal, grads))
+    (got, got_grads), (want, want_grads) = results
+    assert torch.equal(got.addresses, want.addresses)
+    assert set(got_grads) == set(want_grads) and {"attn.k.weight", "attn.v.weight", "attn.beta.weight",
+                                                  "attn.decay.weight", "norm1.weight"} <= set(got_grads)
+    for name, expected in want_grads.items():
+        scale = expected.abs().max().item()
+        torch.testing.assert_close(got_grads[name], expected, atol=2e-5 * max(scale, 1e-6), rtol=2e-4,
+                                   msg=lambda detail, name=name: f"gradient {name}\n{detail}")
+
+
+def test_stack_gradients_with_fused_proposals_and_copy_free_commits():
+    out = checks.gradients_match(ref_package.stack_config(**FAST_CLOCK), DEV, batch=2, length=65, kind="fused")
+    cfg = ref_package.stack_config(num_hidden_layers=4, gl_slots=4096, gl_chunk_size=128, gl_local_window=64,
+                                   vocab_size=4096)
+    free = checks.copy_free_training_matches(cfg, DEV, batch=2, length=512, kind="fused")
+    print("fused proposals, fp32 gradients:", out, "| with copy-free commits:", free)
