@@ -618,6 +618,53 @@ def stack_reference_arm(args, w, rank):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def stack_training_step(model, dev, args):
+    """--train: forward + backward of the same model (cross-entropy on random targets, 8 x 2048
+    token ids, every parameter and the learned bank receive gradients), with the reference's
+    own GlobalLayer.propose and with the fused one (forward glsdm_pk_propose, backward
+    glsdm_pk_propose_backward). Milliseconds per step and the peak of allocated device memory."""
+    import importlib
+    from gl_sdm_b200.layers import install_fused_proposals
+    B, T = 8, 2048
+    gen = torch.Generator().manual_seed(11)
+    ids = torch.randint(STACK_CONFIG["vocab_size"], (B, T), generator=gen).to(dev)
+    targets = torch.randint(STACK_CONFIG["vocab_size"], (B, T), generator=gen).to(dev)
+    model.train()
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        hidden, _, _ = model.hidden(ids)
+        logits = model.head(hidden)
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.flatten())
+        loss.backward()
+        return loss
+
+    def measure():
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize(dev)
+        torch.cuda.reset_peak_memory_stats(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            loss = step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / args.steps
+        return {"ms_per_step": ms, "tokens_per_s": B * T / (ms / 1e3),
+                "peak_allocated_GB": torch.cuda.max_memory_allocated(dev) / 1e9, "loss": loss.item()}
+
+    out = {"batch": f"{B} x {T}", "reference_propose": measure()}
+    undo = install_fused_proposals(importlib.import_module("gl_sdm.layers.global_layer"))
+    try:
+        out["fused_propose"] = measure()
+    finally:
+        undo()
+        model.eval()
+        model.zero_grad(set_to_none=True)
+    return out
+
+
 def stack_arm(args, w, rank):
     """--workload c2 --stack: the reference's own model, unmodified, on the CUDA operator.
     A step = Model.hidden over 8 x 4096 token ids with a fresh request cache (16 layers, 8
@@ -723,6 +770,8 @@ def stack_arm(args, w, rank):
              "what": "gl_sdm_b200.install(fused_proposals=True): GlobalLayer.propose on glsdm_pk_propose",
              "hidden_relative_l2_vs_unfused": ((fused_out - plain).norm() / plain.norm().clamp_min(1e-12)).item()}
     _native.raise_on_device_status(dev)
+    del plain, fused_out
+    training = stack_training_step(model, dev, args) if args.train else None
     emit(json.dumps({
         "metric": "stack forward tokens/s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -734,6 +783,7 @@ def stack_arm(args, w, rank):
         "memory_operator": {"ms_per_step": op_ms, "share_of_forward": op_ms / ms, "tokens_per_s": tokens / (op_ms / 1e3),
                             "ms_by_call": inside, "calls": calls},
         "fused_proposals": fused,
+        "training_step": training,
         "roofline": {"bound": "hbm", "kernel": "memory operator inside the stack (pk_select_read, gather_rows, commit sort + "
                                                 "reduce, whole-bank copy of the functional commit)",
                      "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
@@ -1292,6 +1342,8 @@ def main():
     ap.add_argument("--stack", action="store_true",
                     help="with --workload c2: drive the reference's own 16-layer model (staged under oracle/_ref), "
                          "unmodified, over this package instead of the memory API alone")
+    ap.add_argument("--train", action="store_true",
+                    help="with --stack: also time a forward + backward step (8 x 2048 tokens)")
     ap.add_argument("--no-parity", action="store_true", help="skip the small checked epoch that precedes the timing")
     args = ap.parse_args()
     claim_stdout()
