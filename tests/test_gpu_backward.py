@@ -89,3 +89,53 @@ def test_token_clock_gradients_match_reference_autograd(native):
     only_bank = read(view, t["requests"], t["indices"], t["weights"])
     (g,) = torch.autograd.grad((only_bank * cot_read.to(DEV)).sum(), (leaves["memory"],))
     np.testing.assert_allclose(g.cpu().numpy(), gold["read_grad_memory"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("half,width,dim,bank_dtype,target_dtype,commits", [
+    (32, 8, 64, torch.float32, torch.float32, 0),
+    (16, 4, 48, torch.float32, torch.float32, 0),          # rows that do not fill the lanes
+    (64, 32, 256, torch.bfloat16, torch.bfloat16, 0),      # widest rows, most routes
+    (32, 16, 128, torch.float32, torch.bfloat16, 2),       # the bank has moved on: rows through undo logs
+])
+def test_fused_proposal_backward_matches_autograd_of_the_expression(native, half, width, dim, bank_dtype,
+                                                                    target_dtype, commits):
+    """glsdm_pk_propose_backward against float32 autograd through the port's statement of
+    gl_sdm/layers/global_layer.py:41-51 + gl_sdm/runtime/dense.py:11-14 on the same routes."""
+    from gl_sdm_b200.memory import autograd as ours
+    torch.manual_seed(half * 131 + dim)
+    B, T, H = 2, 24, 3
+    bank = (torch.randn(B, H, half * half, dim, device=DEV) * 0.5).to(bank_dtype)
+    kept = bank.clone()
+    scores = torch.randn(B, T, H, 2 * half, device=DEV)
+    target = torch.randn(B, T, H, dim, device=DEV).to(target_dtype)
+    beta = torch.rand(B, T, H, device=DEV) * 0.8 + 0.1
+    log_decay = -torch.rand(B, T, H, device=DEV) * 0.3
+    leaves = [t.clone().requires_grad_() for t in (bank, scores, target, beta, log_decay)]
+    addresses, deltas, keys = ours.FusedProposal.apply(*leaves, (T, width, 5, 64, 3, 1))
+    incoming = torch.randn_like(deltas)
+    for _ in range(commits):                                  # copy-free commits between forward and backward
+        n = 2048
+        hit = torch.randint(bank.numel() // dim, (n,), device=DEV)
+        log = native.commit_undo(leaves[0].detach(), hit, torch.randn(n, dim, device=DEV))
+        from gl_sdm_b200.memory.state import UndoLog, tail_of
+        node = UndoLog(*log)
+        node.accounted = leaves[0]._version
+        tail_of(leaves[0]).next = node
+        leaves[0]._glsdm_tail = node
+    got = torch.autograd.grad(deltas, leaves, incoming)
+    if commits:
+        assert not torch.equal(leaves[0].detach(), kept)
+
+    exact = [kept.float().requires_grad_(), scores.clone().requires_grad_(), target.float().requires_grad_(),
+             beta.clone().requires_grad_(), log_decay.clone().requires_grad_()]
+    want_addresses, want_deltas, want_keys = port.propose(exact[0], exact[1], width, exact[2], exact[3], exact[4], None,
+                                                          5, 1, 64, 3)
+    assert torch.equal(addresses, want_addresses) and torch.equal(keys, want_keys)
+    torch.testing.assert_close(deltas, want_deltas, atol=1e-5, rtol=1e-5 if bank_dtype == torch.float32 else 1e-4)
+    want = torch.autograd.grad(want_deltas, exact, incoming)
+    for name, g, w in zip(("bank", "scores", "target", "beta", "log_decay"), got, want):
+        scale = w.abs().max().item()
+        loose = 2e-2 if name in ("bank", "target") and g.dtype == torch.bfloat16 else 1e-4
+        torch.testing.assert_close(g.float(), w, atol=loose * scale, rtol=loose,
+                                   msg=lambda detail, name=name: f"gradient {name}\n{detail}")
+    native.raise_on_device_status(DEV)
