@@ -413,8 +413,13 @@ pk_propose_backward_kernel(BankView bank, UndoChain chain, const float* __restri
   if (lane < width) {
     const int64_t flat = addresses[row * width + lane];
     slot = flat - part * bank.slots;
-    sum = __fadd_rn(srow[slot / half], srow[half + slot % half]);
-    row_ptr = reinterpret_cast<uint64_t>(version_row<T>(chain, flat, dim, base + slot * dim));
+    if (slot < 0 || slot >= bank.slots) {
+      slot = 0;                                  // not a route of this row's bank: weight 0, no access outside it
+      row_ptr = reinterpret_cast<uint64_t>(base);
+    } else {
+      sum = __fadd_rn(srow[slot / half], srow[half + slot % half]);
+      row_ptr = reinterpret_cast<uint64_t>(version_row<T>(chain, flat, dim, base + slot * dim));
+    }
   }
   float top = sum;
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFullMask, top, o));

@@ -69,7 +69,19 @@ def test_rows_beyond_the_banks_are_rejected_before_any_launch(native):
                                    null) == 1
     assert lib.glsdm_overlay_read(ctypes.byref(two), fake, 1, fake, bad, 5, 2, 0, null, null, null, fake, null,
                                   null) == 1
-    del ok, one
+    assert lib.glsdm_read_backward_version(ctypes.byref(two), fake, null, fake, 1, fake, bad, 5, 2, 4, 0, null, null,
+                                           null, fake, fake, fake, null) == 1
+    backward = lambda bank, rows, logs: lib.glsdm_pk_propose_backward(                     # noqa: E731
+        ctypes.byref(bank), fake, fake, 0, fake, fake, null, fake, fake, rows, 5, 4, 2, logs, null, null, null,
+        fake, fake, fake, fake, fake, null)
+    assert backward(two, bad, 0) == 1
+    assert backward(two, ok, 1) == 1                      # logs announced, none given
+    assert backward(two, ok, native.MAX_UNDO_LOGS + 1) == lib.glsdm_read_backward_version(
+        ctypes.byref(two), fake, null, fake, 1, fake, ok, 5, 2, 4, native.MAX_UNDO_LOGS + 1, null, null, null,
+        fake, fake, fake, null) != 0
+    wide = native.Bank(4096, 0, 1, 1, 16, 512, 0, 16)     # rows of 512 values: the backward kernel holds 256
+    assert backward(wide, 5, 0) == 2
+    del one
 
 
 def test_score_topk_plans_cover_every_block_and_tile_once():
