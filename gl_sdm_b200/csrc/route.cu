@@ -389,7 +389,7 @@ read_backward_kernel(BankView bank, const float* __restrict__ grad_out, const fl
 //   g_row_k  = m * (decay - 1) * G_k + w_k * g_pred (compact bank gradient, one row per route)
 // The weights are recomputed from the scores and the routes the forward chose; the rows are
 // those of the version the forward read (undo chain). Rows of up to 256 values.
-template <typename T, typename TT>
+template <typename T, typename TT, int kCols>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 pk_propose_backward_kernel(BankView bank, UndoChain chain, const float* __restrict__ scores,
                            const TT* __restrict__ target, const float* __restrict__ beta,
@@ -399,7 +399,7 @@ pk_propose_backward_kernel(BankView bank, UndoChain chain, const float* __restri
                            float* __restrict__ grad_scores, float* __restrict__ grad_target,
                            float* __restrict__ grad_beta, float* __restrict__ grad_log_decay,
                            float* __restrict__ grad_rows) {
-  constexpr int kCols = 8;   // columns per lane: rows of at most 256 values
+  // kCols columns per lane: rows of at most 32 * kCols values (2, 4 or 8: up to 256)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
   if (row >= rows) return;
@@ -465,9 +465,10 @@ pk_propose_backward_kernel(BankView bank, UndoChain chain, const float* __restri
       }
     }
     const float t_err = warp_sum(p_err);
-    with_rows += warp_sum(p_rows);
+    with_rows += p_rows;                 // this lane's columns; summed over the lanes once, below
     if (lane == k) with_err = t_err;
   }
+  with_rows = warp_sum(with_rows);
   float p_beta = 0.f, p_pred = 0.f;
   float gpred[kCols];
   float* __restrict__ gt = grad_target + row * dim;
@@ -709,10 +710,16 @@ extern "C" int glsdm_pk_propose_backward(const glsdm_bank* bank, const float* sc
   if (int s = make_chain(n_logs, log_addresses, log_rows, log_entries, &chain, nullptr)) return s;
   const BankView v = make_view(*bank);
   const int grid = blocks_for(rows, kWarpsPerBlock);
-#define GLSDM_PROPOSE_BACKWARD(T, TT)                                                                       \
-  pk_propose_backward_kernel<T, TT><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                              \
+#define GLSDM_PROPOSE_BACKWARD_COLS(T, TT, COLS)                                                            \
+  pk_propose_backward_kernel<T, TT, COLS><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                        \
       v, chain, scores, static_cast<const TT*>(target), beta, log_decay, mass, addresses, grad_deltas, rows, \
       rows_per_bank, half, kout, grad_scores, grad_target, grad_beta, grad_log_decay, grad_rows)
+#define GLSDM_PROPOSE_BACKWARD(T, TT)                                 \
+  do {                                                                \
+    if (v.dim <= 64) GLSDM_PROPOSE_BACKWARD_COLS(T, TT, 2);           \
+    else if (v.dim <= 128) GLSDM_PROPOSE_BACKWARD_COLS(T, TT, 4);     \
+    else GLSDM_PROPOSE_BACKWARD_COLS(T, TT, 8);                       \
+  } while (0)
   if (bank->dtype == GLSDM_F32) {
     if (target_dtype == GLSDM_F32) GLSDM_PROPOSE_BACKWARD(float, float);
     else GLSDM_PROPOSE_BACKWARD(float, __nv_bfloat16);
@@ -721,6 +728,7 @@ extern "C" int glsdm_pk_propose_backward(const glsdm_bank* bank, const float* sc
     else GLSDM_PROPOSE_BACKWARD(__nv_bfloat16, __nv_bfloat16);
   }
 #undef GLSDM_PROPOSE_BACKWARD
+#undef GLSDM_PROPOSE_BACKWARD_COLS
   GLSDM_CUDA_OK(cudaGetLastError(), "pk_propose_backward launch");
   count_launches(1);
   return GLSDM_OK;
