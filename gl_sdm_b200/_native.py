@@ -76,6 +76,7 @@ SIGNATURES = {
     "glsdm_commit_factored_mode": (_i, [_i]),
     "glsdm_score_topk_plan": (_i, [_i64, _i64, _i32, _i32, _i32, _p]),
     "glsdm_score_topk_pitched": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
+    "glsdm_score_topk_bounded": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _p, _sz, _p, _p]),
     "glsdm_pk_combine": (_i, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge_strided": (_i, [_p, _p, _i32, _i64, _i64, _i32, _p, _i, _p, _p]),
@@ -610,9 +611,11 @@ def topk_merge_packed(packed, parts, rows, width, out):
     return index, weights
 
 
-def score_topk(queries, keys, width, col_base=0, out=None):
-    """Dense-key routing of one shard: best `width` (score, slot) per query row, best first."""
-    require_cuda(queries, keys)
+def score_topk(queries, keys, width, col_base=0, out=None, row_floor=None):
+    """Dense-key routing of one shard: best `width` (score, slot) per query row, best first.
+    ``row_floor`` [rows] float32: a score each row's width-th best over the WHOLE bank is known
+    to reach; candidates below it are dropped (lists may come back short, padded with slot -1)."""
+    require_cuda(queries, keys, row_floor)
     if queries.dtype != torch.bfloat16 or keys.dtype != torch.bfloat16:
         raise ValueError("queries and keys must be bfloat16")
     rows, dk = queries.shape
@@ -628,9 +631,11 @@ def score_topk(queries, keys, width, col_base=0, out=None):
         require_cuda(score, slot)
         if score.numel() != rows * width or slot.numel() != rows * width or score.dtype != torch.float32 or slot.dtype != torch.int32:
             raise ValueError("preallocated candidate buffers have the wrong size or type")
-    _check(lib.glsdm_score_topk(_ptr(queries), _ptr(keys), rows, slots, dk, width, col_base, _ptr(score),
-                                _ptr(slot), _ptr(work), work.numel(), _ptr(status_word(queries.device)),
-                                _stream(queries.device)))
+    if row_floor is not None and (row_floor.dtype != torch.float32 or row_floor.numel() != rows):
+        raise ValueError("row_floor must be float32 with one value per query row")
+    _check(lib.glsdm_score_topk_bounded(_ptr(queries), dk, _ptr(keys), dk, rows, slots, dk, width, col_base,
+                                        _ptr(row_floor), _ptr(score), _ptr(slot), _ptr(work), work.numel(),
+                                        _ptr(status_word(queries.device)), _stream(queries.device)))
     return score, slot
 
 

@@ -569,6 +569,15 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
                                         int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
                                         int64_t col_base, float* out_score, int32_t* out_slot, void* workspace,
                                         size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream) {
+  return glsdm_score_topk_bounded(queries, query_pitch, keys, key_pitch, rows, slots, dk, width, col_base, nullptr,
+                                  out_score, out_slot, workspace, workspace_bytes, device_status, stream);
+}
+
+extern "C" int glsdm_score_topk_bounded(const void* queries, int64_t query_pitch, const void* keys,
+                                        int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                                        int64_t col_base, const float* row_floor, float* out_score,
+                                        int32_t* out_slot, void* workspace, size_t workspace_bytes,
+                                        uint32_t* device_status, glsdm_stream_t stream) {
   if (query_pitch < dk || key_pitch < dk || (query_pitch % 8) || (key_pitch % 8)) return GLSDM_ERR_ARGUMENT;
   if (queries == nullptr || keys == nullptr || out_score == nullptr || out_slot == nullptr) return GLSDM_ERR_ARGUMENT;
   if (rows < 0 || slots < 1 || width < 1 || col_base < 0) return GLSDM_ERR_ARGUMENT;
@@ -590,6 +599,7 @@ extern "C" int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch
   p.tiles_total = pl.tiles_total;
   p.unit_pairs = pl.unit_pairs;
   p.device_status = device_status;
+  p.row_floor = row_floor;
   p.tail_blocks = pl.tail_blocks;
   p.tail_splits = pl.tail_splits;
   p.tail_tiles_per_split = pl.tail_tiles_per_split;

@@ -40,6 +40,7 @@ struct Params {
   float* out_score;     // [splits][rows][width] (or the final output when splits == 1)
   int32_t* out_slot;
   uint32_t* device_status;
+  const float* row_floor;   // [rows] a score every row's K-th best is known to reach, or null
   // Tail (wide-tile kernel only): the row blocks left over after the last full wave of CTAs
   // have their slot range cut in tail_splits parts, so the last wave is short instead of
   // mostly idle. Their partial lists go to tail_score/tail_slot [part][tail row][width].

@@ -263,7 +263,16 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t head = 0, units_done = 0;
     bool ok = true;
     for (int r = 0; r < 32; ++r) lists[r * 32 + lane] = 0;
-    floor_s[lane] = -INFINITY;
+    // A caller may know a score that the K-th best of a row is sure to reach (row_floor): the
+    // row's floor starts there instead of at -inf, and candidates below it are never queued.
+    auto seed_for = [&](int unit_index) -> float {
+      if (p.row_floor == nullptr || unit_index >= units) return -INFINITY;
+      const UnitSpan s = unit_span(p, unit_index);
+      const int64_t r = static_cast<int64_t>(s.block) * kBlockRows + iw * 32 + lane;
+      return r < p.rows ? p.row_floor[r] : -INFINITY;
+    };
+    float seed = seed_for(first_unit);
+    floor_s[lane] = seed;
     __syncwarp();
     for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
       const UnitSpan span = unit_span(p, unit);
@@ -294,13 +303,14 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           uint64_t* row_list = lists + row * 32;
           const uint64_t cur = row_list[lane];
           const int pos = __popc(__ballot_sync(kFullMask, cur > key));
+          const float row_seed = __shfl_sync(kFullMask, seed, row);
           if (pos < K) {
             const uint64_t up = __shfl_up_sync(kFullMask, cur, 1);
             const uint64_t ne = lane < pos ? cur : (lane == pos ? key : up);
             row_list[lane] = ne;
             if (lane == K - 1)
               *reinterpret_cast<volatile float*>(&floor_s[row]) =
-                  ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+                  ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : row_seed;
           }
         };
         // Entries of four different rows are independent: their list loads, ballots and
@@ -334,12 +344,13 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint64_t up = __shfl_up_sync(kFullMask, cur[i], 1);
+            const float row_seed = __shfl_sync(kFullMask, seed, row[i]);
             if (pos[i] < K) {
               const uint64_t ne = lane < pos[i] ? cur[i] : (lane == pos[i] ? key[i] : up);
               lists[row[i] * 32 + lane] = ne;
               if (lane == K - 1)
                 *reinterpret_cast<volatile float*>(&floor_s[row[i]]) =
-                    ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : -INFINITY;
+                    ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : row_seed;
             }
           }
         }
@@ -372,7 +383,8 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         lists[r * 32 + lane] = 0;
       }
-      floor_s[lane] = -INFINITY;
+      seed = seed_for(unit + unit_stride);
+      floor_s[lane] = seed;
       __threadfence_block();
       __syncwarp();
       ++units_done;

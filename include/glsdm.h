@@ -410,6 +410,19 @@ int glsdm_score_topk_pitched(const void* queries, int64_t query_pitch, const voi
                              int64_t col_base, float* out_score, int32_t* out_slot, void* workspace,
                              size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
 
+/* The same routing with a lower bound per row: row_floor [rows] fp32 (or NULL) holds, for every
+ * query row, a score that the row's width-th best score OVER ALL SLOTS OF THE BANK is known to
+ * reach - e.g. the width-th best another shard has already found. Candidates below it are
+ * never kept, so a shard whose slots cannot compete does little list work; a row's list may
+ * then come back shorter than width (padded with (-inf, slot -1)), which the candidate merge
+ * accepts. Scores equal to the bound are kept, so ties are decided as without it. With the
+ * true bound the merged routes are identical to those of the unbounded call. */
+int glsdm_score_topk_bounded(const void* queries, int64_t query_pitch, const void* keys,
+                             int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                             int64_t col_base, const float* row_floor, float* out_score,
+                             int32_t* out_slot, void* workspace, size_t workspace_bytes,
+                             uint32_t* device_status, glsdm_stream_t stream);
+
 /* Product-key routing from per-factor candidate lists: second stage of
  * gl_sdm/memory/routing.py:19-26 (candidate sums, selection, canonical order, softmax). The
  * lists [rows, min(width, half)] (score, factor index; best first) are what two

@@ -212,3 +212,34 @@ def test_tail_split_units_agree_with_the_uniform_plan(native):
     order_w, order_g = torch.sort(want_slot, dim=-1), torch.sort(got_slot, dim=-1)
     assert torch.equal(order_w.values, order_g.values)
     assert torch.equal(torch.gather(want_score, -1, order_w.indices), torch.gather(got_score, -1, order_g.indices))
+
+
+@pytest.mark.parametrize("rows,slots,width", [(300, 4096, 8), (5000, 1 << 18, 32), ((148 + 20) * 128 - 37, 1 << 19, 32)])
+def test_bounded_routing_keeps_exactly_what_reaches_the_bound(native, rows, slots, width):
+    """glsdm_score_topk_bounded on one shard with the K-th best score of ANOTHER shard as the
+    row bound: every list is the unbounded list cut at the bound (scores equal to the bound
+    stay), padded with (-inf, slot -1); merged with the other shard's list the routes are
+    those of the unbounded pair. A bound above every score empties the row."""
+    g = torch.Generator(device=DEV).manual_seed(rows + width)
+    q = torch.randn(rows, 128, generator=g, device=DEV).bfloat16()
+    k = torch.randn(2 * slots, 128, generator=g, device=DEV)
+    k = (k / k.norm(dim=1, keepdim=True)).bfloat16()
+    k[slots:slots + 64] = k[:64]                                       # bit-equal scores across the shards
+    here, there = k[:slots].contiguous(), k[slots:].contiguous()
+    free_score, free_slot = native.score_topk(q, here, width, col_base=0)
+    peer_score, peer_slot = native.score_topk(q, there, width, col_base=slots)
+    bound = peer_score[:, width - 1].contiguous()
+    bound[::7] = float("inf")                                          # rows this shard cannot contribute to
+    bound[3::7] = float("-inf")                                        # rows without any knowledge
+    got_score, got_slot = native.score_topk(q, here, width, col_base=0, row_floor=bound)
+    native.raise_on_device_status(DEV)
+    keep = free_score >= bound.unsqueeze(1)
+    assert torch.equal(got_slot >= 0, keep)
+    assert torch.equal(got_slot[keep], free_slot[keep]) and torch.equal(got_score[keep], free_score[keep])
+    assert (got_score[~keep] == float("-inf")).all() and (got_slot[~keep] == -1).all()
+    assert not keep[::7].any() and keep[3::7].all()
+    usable = torch.ones(rows, dtype=torch.bool, device=DEV)
+    usable[::7] = False                                                # their bound was not a true one
+    want = native.topk_merge(torch.stack([free_score, peer_score]), torch.stack([free_slot, peer_slot]))
+    got = native.topk_merge(torch.stack([got_score, peer_score]), torch.stack([got_slot, peer_slot]))
+    assert torch.equal(got[0][usable], want[0][usable]) and torch.equal(got[1][usable], want[1][usable])
