@@ -77,6 +77,8 @@ SIGNATURES = {
     "glsdm_score_topk_plan": (_i, [_i64, _i64, _i32, _i32, _i32, _p]),
     "glsdm_score_topk_pitched": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _sz, _p, _p]),
     "glsdm_score_topk_bounded": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _p, _p, _p, _sz, _p, _p]),
+    "glsdm_score_topk_shared": (_i, [_p, _i64, _p, _i64, _i64, _i64, _i32, _i32, _i64, _p, _i64, _p, _i32, _p, _i32, _p, _p,
+                                     _p, _sz, _p, _p]),
     "glsdm_pk_combine": (_i, [_p, _p, _p, _p, _i64, _i32, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge": (_i, [_p, _p, _i32, _i64, _i32, _p, _i, _p, _p]),
     "glsdm_topk_merge_strided": (_i, [_p, _p, _i32, _i64, _i64, _i32, _p, _i, _p, _p]),
@@ -611,11 +613,14 @@ def topk_merge_packed(packed, parts, rows, width, out):
     return index, weights
 
 
-def score_topk(queries, keys, width, col_base=0, out=None, row_floor=None):
+def score_topk(queries, keys, width, col_base=0, out=None, row_floor=None, floor_in=None, floor_out=(), row_shift=0):
     """Dense-key routing of one shard: best `width` (score, slot) per query row, best first.
     ``row_floor`` [rows] float32: a score each row's width-th best over the WHOLE bank is known
-    to reach; candidates below it are dropped (lists may come back short, padded with slot -1)."""
-    require_cuda(queries, keys, row_floor)
+    to reach; candidates below it are dropped (lists may come back short, padded with slot -1).
+    ``floor_in`` [sources, rows] float32 (this GPU) / ``floor_out`` (device addresses of this
+    shard's [rows] float32 row in each peer's floor_in) / ``row_shift``: bounds exchanged with
+    the other shards while the kernels run, see glsdm_score_topk_shared."""
+    require_cuda(queries, keys, row_floor, floor_in)
     if queries.dtype != torch.bfloat16 or keys.dtype != torch.bfloat16:
         raise ValueError("queries and keys must be bfloat16")
     rows, dk = queries.shape
@@ -633,9 +638,16 @@ def score_topk(queries, keys, width, col_base=0, out=None, row_floor=None):
             raise ValueError("preallocated candidate buffers have the wrong size or type")
     if row_floor is not None and (row_floor.dtype != torch.float32 or row_floor.numel() != rows):
         raise ValueError("row_floor must be float32 with one value per query row")
-    _check(lib.glsdm_score_topk_bounded(_ptr(queries), dk, _ptr(keys), dk, rows, slots, dk, width, col_base,
-                                        _ptr(row_floor), _ptr(score), _ptr(slot), _ptr(work), work.numel(),
-                                        _ptr(status_word(queries.device)), _stream(queries.device)))
+    sources = 0
+    if floor_in is not None:
+        if floor_in.dtype != torch.float32 or floor_in.ndim != 2 or floor_in.shape[1] != rows:
+            raise ValueError("floor_in must be float32 [sources, rows]")
+        sources = floor_in.shape[0]
+    peers = (ctypes.c_void_p * max(len(floor_out), 1))(*[int(a) for a in floor_out])
+    _check(lib.glsdm_score_topk_shared(_ptr(queries), dk, _ptr(keys), dk, rows, slots, dk, width, col_base,
+                                       _ptr(row_floor), row_shift, _ptr(floor_in), sources, peers, len(floor_out),
+                                       _ptr(score), _ptr(slot), _ptr(work), work.numel(),
+                                       _ptr(status_word(queries.device)), _stream(queries.device)))
     return score, slot
 
 

@@ -578,6 +578,22 @@ extern "C" int glsdm_score_topk_bounded(const void* queries, int64_t query_pitch
                                         int64_t col_base, const float* row_floor, float* out_score,
                                         int32_t* out_slot, void* workspace, size_t workspace_bytes,
                                         uint32_t* device_status, glsdm_stream_t stream) {
+  return glsdm_score_topk_shared(queries, query_pitch, keys, key_pitch, rows, slots, dk, width, col_base, row_floor,
+                                 0, nullptr, 0, nullptr, 0, out_score, out_slot, workspace, workspace_bytes,
+                                 device_status, stream);
+}
+
+extern "C" int glsdm_score_topk_shared(const void* queries, int64_t query_pitch, const void* keys,
+                                       int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                                       int64_t col_base, const float* row_floor, int64_t row_shift,
+                                       const float* floor_in, int32_t floor_sources, float* const* floor_out,
+                                       int32_t floor_peers, float* out_score, int32_t* out_slot, void* workspace,
+                                       size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream) {
+  if (floor_sources < 0 || floor_peers < 0 || row_shift < 0 || (rows > 0 && row_shift >= rows)) return GLSDM_ERR_ARGUMENT;
+  if (floor_peers > kMaxFloorPeers) return GLSDM_ERR_LIMIT;
+  if ((floor_sources > 0 && floor_in == nullptr) || (floor_peers > 0 && floor_out == nullptr)) return GLSDM_ERR_ARGUMENT;
+  for (int i = 0; i < floor_peers; ++i)
+    if (floor_out[i] == nullptr) return GLSDM_ERR_ARGUMENT;
   if (query_pitch < dk || key_pitch < dk || (query_pitch % 8) || (key_pitch % 8)) return GLSDM_ERR_ARGUMENT;
   if (queries == nullptr || keys == nullptr || out_score == nullptr || out_slot == nullptr) return GLSDM_ERR_ARGUMENT;
   if (rows < 0 || slots < 1 || width < 1 || col_base < 0) return GLSDM_ERR_ARGUMENT;
@@ -600,6 +616,11 @@ extern "C" int glsdm_score_topk_bounded(const void* queries, int64_t query_pitch
   p.unit_pairs = pl.unit_pairs;
   p.device_status = device_status;
   p.row_floor = row_floor;
+  p.floor_in = floor_in;
+  p.floor_sources = floor_sources;
+  p.floor_peers = floor_peers;
+  p.row_shift = row_shift;
+  for (int i = 0; i < kMaxFloorPeers; ++i) p.floor_out[i] = i < floor_peers ? floor_out[i] : nullptr;
   p.tail_blocks = pl.tail_blocks;
   p.tail_splits = pl.tail_splits;
   p.tail_tiles_per_split = pl.tail_tiles_per_split;

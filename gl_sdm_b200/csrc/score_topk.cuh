@@ -27,6 +27,8 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr unsigned kIdleNanoseconds = 1000;      // an idle inserter sleeps this long between looks at its queue
 constexpr uint32_t kIdleLimit = 1u << 22;        // idle looks before an inserter gives up (about four seconds)
 
+constexpr int kMaxFloorPeers = 7;
+
 struct Params {
   int64_t rows;
   int64_t slots;
@@ -41,6 +43,18 @@ struct Params {
   int32_t* out_slot;
   uint32_t* device_status;
   const float* row_floor;   // [rows] a score every row's K-th best is known to reach, or null
+  // Bounds exchanged with the other shards WHILE they scan (all optional). floor_in
+  // [floor_sources][rows]: what the peers have reached so far, written by their kernels into
+  // this GPU's memory; read when a unit starts. floor_out[i] [rows]: this shard's place in peer
+  // i's floor_in; when a unit ends, the K-th best score of each of its rows is stored there
+  // (plain stores, nobody waits for anybody: a bound that has not arrived yet is only a
+  // missed saving). Rows are addressed as (row + row_shift) % rows, so that shards which walk
+  // the rows in different orders (rotated copies of the queries) agree on their names.
+  const float* floor_in;
+  int floor_sources;
+  float* floor_out[kMaxFloorPeers];
+  int floor_peers;
+  int64_t row_shift;
   // Tail (wide-tile kernel only): the row blocks left over after the last full wave of CTAs
   // have their slot range cut in tail_splits parts, so the last wave is short instead of
   // mostly idle. Their partial lists go to tail_score/tail_slot [part][tail row][width].

@@ -266,10 +266,15 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // A caller may know a score that the K-th best of a row is sure to reach (row_floor): the
     // row's floor starts there instead of at -inf, and candidates below it are never queued.
     auto seed_for = [&](int unit_index) -> float {
-      if (p.row_floor == nullptr || unit_index >= units) return -INFINITY;
+      if ((p.row_floor == nullptr && p.floor_sources == 0) || unit_index >= units) return -INFINITY;
       const UnitSpan s = unit_span(p, unit_index);
       const int64_t r = static_cast<int64_t>(s.block) * kBlockRows + iw * 32 + lane;
-      return r < p.rows ? p.row_floor[r] : -INFINITY;
+      if (r >= p.rows) return -INFINITY;
+      float bound = p.row_floor != nullptr ? p.row_floor[r] : -INFINITY;
+      const int64_t name = (r + p.row_shift) % p.rows;
+      for (int src = 0; src < p.floor_sources; ++src)    // peers write these while we run: read past L1
+        bound = fmaxf(bound, __ldcg(p.floor_in + static_cast<int64_t>(src) * p.rows + name));
+      return bound;
     };
     float seed = seed_for(first_unit);
     floor_s[lane] = seed;
@@ -363,9 +368,14 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (!ok) break;
       __syncwarp();
+      float reached = -INFINITY;   // lane r: the K-th best score row r ended with (-inf: fewer than K qualified)
       for (int r = 0; r < 32; ++r) {
         const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + r;
         const uint64_t e = lists[r * 32 + lane];
+        if (p.floor_peers > 0) {
+          const uint64_t last = shfl_u64(e, K - 1);
+          if (lane == r && last != 0) reached = from_orderable_bits(static_cast<uint32_t>(last >> 32));
+        }
         if (row < p.rows && lane < K) {
           const float score = e ? from_orderable_bits(static_cast<uint32_t>(e >> 32)) : -INFINITY;
           const int32_t slot = e ? static_cast<int32_t>(p.col_base + static_cast<int64_t>(e & 0xffffffull)) : -1;
@@ -382,6 +392,15 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
         lists[r * 32 + lane] = 0;
+      }
+      if (p.floor_peers > 0 && reached > -INFINITY) {
+        // The K-th best over a part of the bank never exceeds the K-th best over all of it: a
+        // valid bound for every other shard, whichever part of the slot range this unit covered.
+        const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + lane;
+        if (row < p.rows) {
+          const int64_t name = (row + p.row_shift) % p.rows;
+          for (int peer = 0; peer < p.floor_peers; ++peer) p.floor_out[peer][name] = reached;
+        }
       }
       seed = seed_for(unit + unit_stride);
       floor_s[lane] = seed;

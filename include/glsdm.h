@@ -423,6 +423,29 @@ int glsdm_score_topk_bounded(const void* queries, int64_t query_pitch, const voi
                              int32_t* out_slot, void* workspace, size_t workspace_bytes,
                              uint32_t* device_status, glsdm_stream_t stream);
 
+/* The same with the bounds exchanged between the shards of a slot-sharded bank WHILE their
+ * kernels run (no counterpart in the reference, which is single-GPU). Every shard scores the
+ * same query rows; a streaming top-k spends about width * (1 + ln(slots / width)) list
+ * insertions per row before its threshold is tight, whatever the shard size, so R shards pay
+ * that R times - unless a shard that reaches a row later starts from what the others found.
+ *   floor_in    [floor_sources][rows] fp32 in THIS GPU's memory, -inf where nothing is known:
+ *               peers store into it while this call runs; a unit reads its rows when it starts
+ *   floor_out   HOST array of floor_peers device pointers (<= 7), each [rows] fp32: this
+ *               shard's row in a peer's floor_in (peer memory, plain stores); when a unit ends,
+ *               the width-th best score of each of its rows is stored there
+ *   row_shift   rows are named (row + row_shift) % rows in floor_in / floor_out: give each
+ *               shard a rotated copy of the queries so that they walk the rows in different
+ *               orders and most rows are first finished by somebody else
+ * Nobody waits for anybody: a bound that has not arrived is a missed saving, nothing more, and
+ * a stale bound of the SAME call is still a bound. The caller must make sure that nothing of
+ * an earlier call (other queries) is left in floor_in when this call starts, on every shard. */
+int glsdm_score_topk_shared(const void* queries, int64_t query_pitch, const void* keys,
+                            int64_t key_pitch, int64_t rows, int64_t slots, int32_t dk, int32_t width,
+                            int64_t col_base, const float* row_floor, int64_t row_shift,
+                            const float* floor_in, int32_t floor_sources, float* const* floor_out,
+                            int32_t floor_peers, float* out_score, int32_t* out_slot, void* workspace,
+                            size_t workspace_bytes, uint32_t* device_status, glsdm_stream_t stream);
+
 /* Product-key routing from per-factor candidate lists: second stage of
  * gl_sdm/memory/routing.py:19-26 (candidate sums, selection, canonical order, softmax). The
  * lists [rows, min(width, half)] (score, factor index; best first) are what two

@@ -243,3 +243,35 @@ def test_bounded_routing_keeps_exactly_what_reaches_the_bound(native, rows, slot
     want = native.topk_merge(torch.stack([free_score, peer_score]), torch.stack([free_slot, peer_slot]))
     got = native.topk_merge(torch.stack([got_score, peer_score]), torch.stack([got_slot, peer_slot]))
     assert torch.equal(got[0][usable], want[0][usable]) and torch.equal(got[1][usable], want[1][usable])
+
+
+def test_bounds_pushed_by_one_shard_are_read_by_the_next(native):
+    """glsdm_score_topk_shared, two shards of one bank on one GPU, one after the other: the
+    first stores the K-th best score of every row in the second's floor_in; the second, which
+    walks a rotated copy of the rows, keeps exactly the candidates that reach those bounds, and
+    the merged routes are those of two unbounded shards."""
+    rows, slots, width, shift = 5000, 1 << 18, 32, 128 * 17
+    g = torch.Generator(device=DEV).manual_seed(5)
+    q = torch.randn(rows, 128, generator=g, device=DEV).bfloat16()
+    k = torch.randn(2 * slots, 128, generator=g, device=DEV)
+    k = (k / k.norm(dim=1, keepdim=True)).bfloat16()
+    first, second = k[:slots].contiguous(), k[slots:].contiguous()
+    inbox = torch.full((1, rows), float("-inf"), device=DEV)
+    a_score, a_slot = native.score_topk(q, first, width, col_base=0, floor_out=[inbox[0].data_ptr()])
+    # 40 row blocks on 148 SMs: the slot range is cut in parts, and a part's K-th best is what gets stored
+    assert (inbox[0] <= a_score[:, width - 1]).all() and (inbox[0] > float("-inf")).all()
+    free_score, free_slot = native.score_topk(q, second, width, col_base=slots)
+    turned = torch.roll(q, -shift, 0).contiguous()             # logical row l is row (l + shift) % rows
+    outbox = torch.full((rows,), float("-inf"), device=DEV)
+    b_score, b_slot = native.score_topk(turned, second, width, col_base=slots, floor_in=inbox,
+                                        floor_out=[outbox.data_ptr()], row_shift=shift)
+    b_score, b_slot = torch.roll(b_score, shift, 0), torch.roll(b_slot, shift, 0)
+    native.raise_on_device_status(DEV)
+    keep = free_score >= inbox[0].unsqueeze(1)
+    assert torch.equal(b_slot >= 0, keep) and torch.equal(b_slot[keep], free_slot[keep])
+    assert (outbox <= free_score[:, width - 1]).all()
+    assert (outbox[~keep[:, width - 1]] == float("-inf")).all()   # fewer than K reached the bound: nothing to tell
+    want = native.topk_merge(torch.stack([a_score, free_score]), torch.stack([a_slot, free_slot]))
+    got = native.topk_merge(torch.stack([a_score, b_score]), torch.stack([a_slot, b_slot]))
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    assert 0.02 < keep.float().mean().item() < 0.99            # the bounds did prune
