@@ -38,6 +38,19 @@ def shard_range(slots, rank, world):
     return rank * per, (rank + 1) * per
 
 
+def _symmetric_memory(numel, device, dist, group):
+    """float32 [numel] that every rank of the group can address, and its address on each rank
+    (torch.distributed symmetric memory: one allocation per rank, mapped into all of them). The
+    NVLink multicast mapping is not requested: only plain peer stores go there."""
+    import os
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm
+    world = dist.group.WORLD if group is None else group
+    tensor = symm.empty(numel, dtype=torch.float32, device=device)
+    handle = symm.rendezvous(tensor, world)
+    return tensor, [int(p) for p in handle.buffer_ptrs]
+
+
 class SingleProcess:
     """The collectives of a world of one rank (a single GPU running the sharded code path)."""
 
@@ -103,6 +116,7 @@ class ShardedBankOperator:
         # proposal + commit with materialised deltas. Both give bit-identical banks.
         self.factored = factored
         self._buf = {}
+        self._floor_state, self._floor_calls = None, 0
         self.marks = None   # set to a list to collect (stage name, CUDA event) pairs for profiling
 
     def _mark(self, name):
@@ -149,8 +163,8 @@ class ShardedBankOperator:
         # this rank's candidates: scores then slots in one buffer, so that one all-gather moves both
         mine = self._buffer("cand", 2 * rows * K, torch.int32)
         self._mark("score_topk")
-        k.score_topk(everyone.view(rows, dk), self.keys, K, col_base=self.slot_lo,
-                     out=(mine[:rows * K].view(torch.float32).view(rows, K), mine[rows * K:].view(rows, K)))
+        self._score_all_rows(everyone.view(rows, dk), mine[:rows * K].view(torch.float32).view(rows, K),
+                             mine[rows * K:].view(rows, K))
         self._mark("merge")
         region = n * K
         if R == 1:
@@ -172,6 +186,74 @@ class ShardedBankOperator:
         # per rank block: [slots of the query rows | slots of the write rows | weights, same order]
         return dict(routes=routes, stride=4 * region, read_weights_at=2 * region, write_index_at=region,
                     write_weights_at=3 * region)
+
+    def _score_all_rows(self, queries, scores, slots):
+        """Partial top-k of ALL rows on this rank's keys, the ranks telling each other what they
+        have reached while their kernels run (glsdm_score_topk_shared). A streaming top-k spends
+        about K * (1 + ln(n / K)) list insertions per row before its threshold is tight, whatever
+        the shard size, so R shards pay that R times. Here every rank walks the rows from a
+        different starting point (a rotated copy of the queries): after the first R-th of its
+        rows, whatever row a rank begins has usually been finished by another rank, whose K-th
+        best score - the K-th best over a part of the bank, so never above the true one - arrives
+        through peer memory and lets this rank drop nearly all of its candidates at once. Nobody
+        waits; without peer memory (or alone) this is the plain kernel."""
+        k, R, K = self.k, self.world, self.width
+        rows = queries.shape[0]
+        inbox = self._floor_inbox(rows) if R > 1 else None
+        if inbox is None:
+            k.score_topk(queries, self.keys, K, col_base=self.slot_lo, out=(scores, slots))
+            return
+        boxes, peers = inbox
+        call = self._floor_calls
+        self._floor_calls += 1
+        # The other half was written during the previous call. Every peer finished that call
+        # before it entered the collective this rank has just completed (the all-gather of the
+        # queries), and none starts the next one before this rank enters the next all-gather:
+        # clearing here can neither lose a bound of this call nor leave one of an older call.
+        boxes[(call + 1) % 2].fill_(float("-inf"))
+        mine_at = ((call % 2) * R + self.rank) * rows * 4
+        shift = (rows // R // 128) * 128 * self.rank
+        if shift:
+            turned = self._buffer("queries_turned", queries.numel(), queries.dtype).view_as(queries)
+            turned.copy_(torch.roll(queries, -shift, 0))
+            out_scores = self._buffer("cand_turned_scores", scores.numel(), scores.dtype).view_as(scores)
+            out_slots = self._buffer("cand_turned_slots", slots.numel(), slots.dtype).view_as(slots)
+        else:
+            turned, out_scores, out_slots = queries, scores, slots
+        k.score_topk(turned, self.keys, K, col_base=self.slot_lo, out=(out_scores, out_slots),
+                     floor_in=boxes[call % 2], floor_out=[p + mine_at for i, p in enumerate(peers) if i != self.rank],
+                     row_shift=shift)
+        if shift:
+            scores.copy_(torch.roll(out_scores, shift, 0))
+            slots.copy_(torch.roll(out_slots, shift, 0))
+
+    def _floor_inbox(self, rows):
+        """([2, R, rows] float32 in memory the peers can store into, [its address on every rank]),
+        or None where peer memory is not to be had (then the ranks simply do not share bounds)."""
+        if self._floor_state is not None and self._floor_state[0] == rows:
+            return self._floor_state[1]
+        self._floor_state = (rows, None)
+        if self.world - 1 > 7:
+            return None
+        numel = 2 * self.world * rows
+        try:
+            if hasattr(self.dist, "peer_memory"):              # ranks that share one process and GPU (tests)
+                boxes, peers = self.dist.peer_memory(numel, self.shard.device, self.group)
+            else:
+                boxes, peers = _symmetric_memory(numel, self.shard.device, self.dist, self.group)
+        except Exception as error:                             # noqa: BLE001 - any failure only costs the saving
+            import sys
+            print(f"gl_sdm_b200: no peer memory for shared routing bounds ({type(error).__name__}: {error})", file=sys.stderr)
+            return None
+        boxes = boxes[:numel].view(2, self.world, rows)
+        boxes.fill_(float("-inf"))
+        self._floor_calls = 0
+        # nobody may store into a box that its owner has not cleared yet
+        token = torch.zeros(1, device=self.shard.device)
+        everyone = torch.empty(self.world, device=self.shard.device)
+        self.dist.all_gather_into_tensor(everyone, token, group=self.group)
+        self._floor_state = (rows, (boxes, peers))
+        return self._floor_state[1]
 
     # -- read, proposal, commit --------------------------------------------------------------------
 

@@ -80,3 +80,12 @@ class _RankDist:
         n = out.numel() // self.w.world
         out.view(self.w.world, n).copy_(torch.stack([p.reshape(self.w.world, n)[self.rank] for p in pieces]))
         self.w.barrier.wait()
+
+    def peer_memory(self, numel, device, group=None):
+        """float32 [numel] of this rank and the addresses of every rank's: the virtual ranks share
+        one process and one GPU, so plain allocations are each other's "peer memory"."""
+        mine = torch.empty(numel, dtype=torch.float32, device=device)
+        pieces = self._exchange(mine)
+        self.w.barrier.wait()
+        self.w.local.__dict__.setdefault("kept", []).append(pieces)      # the peers' tensors must outlive their users
+        return mine, [p.data_ptr() for p in pieces]
