@@ -167,3 +167,43 @@ def test_benchmark_parity_epoch(native, world, routing):
     print(parity)
     assert parity["ok"] and parity["wrong"] == 0 and parity["ranks_agree_on_routes"]
     assert parity["near_tie_exempt"] <= (4 if routing == "dense" else 0)
+
+
+def test_ranks_share_routing_bounds_without_changing_the_routes(native):
+    """Dense keys, 4 virtual ranks, enough rows for every rank to walk them from its own starting
+    point: the K-th best scores the ranks store into each other's memory while scoring let the
+    later ones drop candidates (their lists come back padded), and the merged routes, readings
+    and banks are those of one unsharded rank."""
+    from gl_sdm_b200.sharded import ShardedBankOperator
+    world = 4
+    bank, keys, x, K, T = _dense_inputs(world, seed=57, slots=1 << 16, T=256)
+    dx = {k: v.to(DEV) for k, v in x.items()}
+    per = x["q"].shape[0] // world
+
+    def epoch(op, mine):
+        out = op.epoch_dense(*[dx[k][mine].contiguous() for k in ("q", "kq", "target", "beta", "log_decay")]).clone()
+        return out, [t.clone() for t in op.last_routes()]
+
+    def body(rank, dist):
+        torch.cuda.set_device(0)
+        op = ShardedBankOperator(bank.to(DEV).clone(), K, K, dist, chunk_size=T, keys=keys.to(DEV))
+        results = [epoch(op, slice(rank * per, (rank + 1) * per)) for _ in range(3)]   # both halves of the inboxes, twice
+        rows = world * 2 * per * T
+        padded = int((op._buf["cand"][rows * K:2 * rows * K] < 0).sum())
+        assert op._floor_state[1] is not None and op._floor_calls == 3
+        return results, op.gather_bank(), padded
+
+    shared = ThreadWorld(world).run(body)
+    alone = ShardedBankOperator(bank.to(DEV).clone(), K, K, None, chunk_size=T, keys=keys.to(DEV))
+    want = [epoch(alone, slice(None)) for _ in range(3)]
+    native.raise_on_device_status(DEV)
+    assert sum(padded for _, _, padded in shared) > 0
+    for e in range(3):
+        want_reads, want_routes = want[e]
+        for rank, (results, _, _) in enumerate(shared):
+            got_reads, got_routes = results[e]
+            for got, expected in zip(got_routes, want_routes):
+                assert torch.equal(got, expected)                       # every rank holds all routes
+            torch.testing.assert_close(got_reads, want_reads[rank * per:(rank + 1) * per], atol=1e-6, rtol=1e-5)
+    for _, after, _ in shared:
+        torch.testing.assert_close(after, alone.gather_bank(), atol=1e-6, rtol=1e-5)
