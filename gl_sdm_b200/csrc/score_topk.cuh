@@ -25,6 +25,7 @@ constexpr int64_t kMaxSlotsPerCall = 1 << 24;    // a queue entry carries a 24-b
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr unsigned kIdleNanoseconds = 1000;      // an idle inserter sleeps this long between looks at its queue
+constexpr uint32_t kFloorRefresh = 16;           // idle looks between two exchanges of bounds with the peers (a power of two)
 constexpr uint32_t kIdleLimit = 1u << 22;        // idle looks before an inserter gives up (about four seconds)
 
 constexpr int kMaxFloorPeers = 7;

@@ -279,6 +279,31 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     float seed = seed_for(first_unit);
     floor_s[lane] = seed;
     __syncwarp();
+    // While a unit runs, the shards that scan the same rows at the same time (their first waves
+    // overlap) keep each other informed: every so many idle looks this warp stores the K-th best
+    // score its 32 rows have reached so far where it rose, and raises its floors to what the
+    // peers have stored. A bound above the row's own K-th entry simply closes the row earlier.
+    const bool sharing = p.floor_peers > 0 || p.floor_sources > 0;
+    float told = -INFINITY;    // lane r: the last bound stored for row r of this unit
+    uint32_t batches = 0;
+    auto refresh_bounds = [&](int block) {
+      const int64_t row = static_cast<int64_t>(block) * kBlockRows + iw * 32 + lane;
+      if (row >= p.rows) return;
+      const int64_t name = (row + p.row_shift) % p.rows;
+      const uint64_t last = lists[lane * 32 + K - 1];
+      const float mine = last ? from_orderable_bits(static_cast<uint32_t>(last >> 32)) : -INFINITY;
+      if (mine > told) {
+        told = mine;
+        for (int peer = 0; peer < p.floor_peers; ++peer) p.floor_out[peer][name] = mine;
+      }
+      float bound = seed;
+      for (int src = 0; src < p.floor_sources; ++src)
+        bound = fmaxf(bound, __ldcg(p.floor_in + static_cast<int64_t>(src) * p.rows + name));
+      if (bound > seed) {
+        seed = bound;
+        if (bound > mine) *reinterpret_cast<volatile float*>(&floor_s[lane]) = bound;
+      }
+    };
     for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
       const UnitSpan span = unit_span(p, unit);
       const int pair = span.block;
@@ -293,6 +318,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // two scanner warps feed a queue: the two column halves of this lane quarter
           if (finished == 2u * (units_done + 1u) && tail == head) break;
           if (++idle >= kIdleLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
+          if (sharing && (idle & (kFloorRefresh - 1)) == 0) refresh_bounds(pair);
           // Nothing queued: most of a unit is like this. Polling flat out would spend issue
           // slots and, on a power-capped part, clock rate that the tensor pipe can use
           // (measured: 1166 -> 1197 TFLOP/s sustained on 65,536 rows x 16.7M slots).
@@ -315,7 +341,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             row_list[lane] = ne;
             if (lane == K - 1)
               *reinterpret_cast<volatile float*>(&floor_s[row]) =
-                  ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : row_seed;
+                  ne ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed) : row_seed;
           }
         };
         // Entries of four different rows are independent: their list loads, ballots and
@@ -355,7 +381,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               lists[row[i] * 32 + lane] = ne;
               if (lane == K - 1)
                 *reinterpret_cast<volatile float*>(&floor_s[row[i]]) =
-                    ne ? from_orderable_bits(static_cast<uint32_t>(ne >> 32)) : row_seed;
+                    ne ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed) : row_seed;
             }
           }
         }
@@ -365,6 +391,8 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         __syncwarp();
         head += count;
         if (lane == 0) *reinterpret_cast<volatile uint32_t*>(&q->head) = head;
+        // the start of a unit is all insertions and no idle look: exchange there too
+        if (sharing && (++batches & (kFloorRefresh - 1)) == 0) refresh_bounds(pair);
       }
       if (!ok) break;
       __syncwarp();
@@ -393,7 +421,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         lists[r * 32 + lane] = 0;
       }
-      if (p.floor_peers > 0 && reached > -INFINITY) {
+      if (p.floor_peers > 0 && reached > told) {
         // The K-th best over a part of the bank never exceeds the K-th best over all of it: a
         // valid bound for every other shard, whichever part of the slot range this unit covered.
         const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + lane;
@@ -402,6 +430,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int peer = 0; peer < p.floor_peers; ++peer) p.floor_out[peer][name] = reached;
         }
       }
+      told = -INFINITY;
       seed = seed_for(unit + unit_stride);
       floor_s[lane] = seed;
       __threadfence_block();
