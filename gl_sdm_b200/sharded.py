@@ -48,6 +48,9 @@ def _symmetric_memory(numel, device, dist, group):
     world = dist.group.WORLD if group is None else group
     tensor = symm.empty(numel, dtype=torch.float32, device=device)
     handle = symm.rendezvous(tensor, world)
+    if getattr(handle, "multicast_ptr", 0):
+        import sys
+        print("gl_sdm_b200: the symmetric-memory inbox also got an NVLink multicast mapping (unused here)", file=sys.stderr)
     return tensor, [int(p) for p in handle.buffer_ptrs]
 
 
