@@ -548,6 +548,20 @@ extern "C" int glsdm_score_topk_plan(int64_t rows, int64_t slots, int32_t width,
   return GLSDM_OK;
 }
 
+// GLSDM_FLOOR_REFRESH: looks at the queue between two exchanges of bounds inside a unit (a power
+// of two; 0 = only when a unit starts and ends).
+static uint32_t floor_refresh_mask() {
+  static const uint32_t mask = [] {
+    const char* v = std::getenv("GLSDM_FLOOR_REFRESH");
+    const long n = (v == nullptr || v[0] == '\0') ? static_cast<long>(kFloorRefresh) : std::atol(v);
+    if (n <= 0) return 0xffffffffu;
+    uint32_t pow2 = 1;
+    while (pow2 < static_cast<uint32_t>(n) && pow2 < (1u << 30)) pow2 <<= 1;
+    return pow2 - 1u;
+  }();
+  return mask;
+}
+
 extern "C" size_t glsdm_score_topk_workspace_bytes(int64_t rows, int64_t slots, int32_t dk, int32_t width) {
   (void)dk;
   if (rows < 1 || slots < 1 || width < 1) return 0;
@@ -620,6 +634,7 @@ extern "C" int glsdm_score_topk_shared(const void* queries, int64_t query_pitch,
   p.floor_sources = floor_sources;
   p.floor_peers = floor_peers;
   p.row_shift = row_shift;
+  p.floor_refresh_mask = floor_refresh_mask();
   for (int i = 0; i < kMaxFloorPeers; ++i) p.floor_out[i] = i < floor_peers ? floor_out[i] : nullptr;
   p.tail_blocks = pl.tail_blocks;
   p.tail_splits = pl.tail_splits;

@@ -25,7 +25,7 @@ constexpr int64_t kMaxSlotsPerCall = 1 << 24;    // a queue entry carries a 24-b
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr unsigned kIdleNanoseconds = 1000;      // an idle inserter sleeps this long between looks at its queue
-constexpr uint32_t kFloorRefresh = 16;           // idle looks between two exchanges of bounds with the peers (a power of two)
+constexpr uint32_t kFloorRefresh = 64;           // idle looks between two exchanges of bounds with the peers (a power of two)
 constexpr uint32_t kIdleLimit = 1u << 22;        // idle looks before an inserter gives up (about four seconds)
 
 constexpr int kMaxFloorPeers = 7;
@@ -56,6 +56,7 @@ struct Params {
   float* floor_out[kMaxFloorPeers];
   int floor_peers;
   int64_t row_shift;
+  uint32_t floor_refresh_mask;   // bounds are exchanged inside a unit every (mask + 1) looks at the queue
   // Tail (wide-tile kernel only): the row blocks left over after the last full wave of CTAs
   // have their slot range cut in tail_splits parts, so the last wave is short instead of
   // mostly idle. Their partial lists go to tail_score/tail_slot [part][tail row][width].

@@ -280,7 +280,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     floor_s[lane] = seed;
     __syncwarp();
     // While a unit runs, the shards that scan the same rows at the same time (their first waves
-    // overlap) keep each other informed: every so many idle looks this warp stores the K-th best
+    // overlap) keep each other informed: every so many looks at its queue this warp stores the K-th best
     // score its 32 rows have reached so far where it rose, and raises its floors to what the
     // peers have stored. A bound above the row's own K-th entry simply closes the row earlier.
     const bool sharing = p.floor_peers > 0 || p.floor_sources > 0;
@@ -318,7 +318,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // two scanner warps feed a queue: the two column halves of this lane quarter
           if (finished == 2u * (units_done + 1u) && tail == head) break;
           if (++idle >= kIdleLimit || ((idle & 1023u) == 0 && *abort_flag)) { *abort_flag = 1; ok = false; break; }
-          if (sharing && (idle & (kFloorRefresh - 1)) == 0) refresh_bounds(pair);
+          if (sharing && (idle & p.floor_refresh_mask) == 0) refresh_bounds(pair);
           // Nothing queued: most of a unit is like this. Polling flat out would spend issue
           // slots and, on a power-capped part, clock rate that the tensor pipe can use
           // (measured: 1166 -> 1197 TFLOP/s sustained on 65,536 rows x 16.7M slots).
@@ -392,7 +392,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         head += count;
         if (lane == 0) *reinterpret_cast<volatile uint32_t*>(&q->head) = head;
         // the start of a unit is all insertions and no idle look: exchange there too
-        if (sharing && (++batches & (kFloorRefresh - 1)) == 0) refresh_bounds(pair);
+        if (sharing && (++batches & p.floor_refresh_mask) == 0) refresh_bounds(pair);
       }
       if (!ok) break;
       __syncwarp();
