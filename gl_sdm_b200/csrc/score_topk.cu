@@ -666,17 +666,21 @@ extern "C" int glsdm_score_topk_shared(const void* queries, int64_t query_pitch,
   const int units = pl.unit_pairs * pl.splits + pl.tail_blocks * pl.tail_splits;
   const int grid = units < sms ? units : sms;
   if (wide) {
+    const bool bounds = row_floor != nullptr || floor_sources > 0 || floor_peers > 0;
+#define GLSDM_WIDE(KB, BOUNDS)                                                                              \
+  do {                                                                                                      \
+    const int smem = WideLayout<KB>::total();                                                               \
+    GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<KB, BOUNDS>,                                  \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem),                  \
+                  "score_topk shared memory");                                                              \
+    score_topk_wide_kernel<KB, BOUNDS><<<grid, kWideThreads, smem, stream>>>(map_q, map_k, p);              \
+  } while (0)
     if (dk == 128) {
-      const int smem = WideLayout<2>::total();
-      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "score_topk shared memory");
-      score_topk_wide_kernel<2><<<grid, kWideThreads, smem, stream>>>(map_q, map_k, p);
+      if (bounds) GLSDM_WIDE(2, true); else GLSDM_WIDE(2, false);
     } else {
-      const int smem = WideLayout<1>::total();
-      GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "score_topk shared memory");
-      score_topk_wide_kernel<1><<<grid, kWideThreads, smem, stream>>>(map_q, map_k, p);
+      if (bounds) GLSDM_WIDE(1, true); else GLSDM_WIDE(1, false);
     }
+#undef GLSDM_WIDE
   } else if (dk == 128) {
     const int smem = Layout<2>::total(width);
     GLSDM_CUDA_OK(cudaFuncSetAttribute(score_topk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),

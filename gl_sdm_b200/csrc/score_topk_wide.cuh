@@ -57,7 +57,10 @@ struct WideLayout {
   }
 };
 
-template <int KB>
+// kBounds: the instantiation that takes and gives row bounds (row_floor, floor_in, floor_out).
+// The plain one is compiled without any of it, so a single GPU runs exactly the kernel it ran
+// before bounds existed.
+template <int KB, bool kBounds>
 __global__ void __launch_bounds__(kWideThreads, 1)
 score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, Params p) {
   extern __shared__ __align__(1024) uint8_t raw_smem[];
@@ -266,6 +269,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // A caller may know a score that the K-th best of a row is sure to reach (row_floor): the
     // row's floor starts there instead of at -inf, and candidates below it are never queued.
     auto seed_for = [&](int unit_index) -> float {
+      if constexpr (!kBounds) return -INFINITY;
       if ((p.row_floor == nullptr && p.floor_sources == 0) || unit_index >= units) return -INFINITY;
       const UnitSpan s = unit_span(p, unit_index);
       const int64_t r = static_cast<int64_t>(s.block) * kBlockRows + iw * 32 + lane;
@@ -283,7 +287,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // overlap) keep each other informed: every so many looks at its queue this warp stores the K-th best
     // score its 32 rows have reached so far where it rose, and raises its floors to what the
     // peers have stored. A bound above the row's own K-th entry simply closes the row earlier.
-    const bool sharing = p.floor_peers > 0 || p.floor_sources > 0;
+    const bool sharing = kBounds && (p.floor_peers > 0 || p.floor_sources > 0);
     float told = -INFINITY;    // lane r: the last bound stored for row r of this unit
     uint32_t batches = 0;
     auto refresh_bounds = [&](int block) {
@@ -334,14 +338,17 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           uint64_t* row_list = lists + row * 32;
           const uint64_t cur = row_list[lane];
           const int pos = __popc(__ballot_sync(kFullMask, cur > key));
-          const float row_seed = __shfl_sync(kFullMask, seed, row);
+          float row_seed = -INFINITY;
+          if constexpr (kBounds) row_seed = __shfl_sync(kFullMask, seed, row);
           if (pos < K) {
             const uint64_t up = __shfl_up_sync(kFullMask, cur, 1);
             const uint64_t ne = lane < pos ? cur : (lane == pos ? key : up);
             row_list[lane] = ne;
             if (lane == K - 1)
               *reinterpret_cast<volatile float*>(&floor_s[row]) =
-                  ne ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed) : row_seed;
+                  ne ? (kBounds ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed)
+                                : from_orderable_bits(static_cast<uint32_t>(ne >> 32)))
+                     : row_seed;
           }
         };
         // Entries of four different rows are independent: their list loads, ballots and
@@ -375,13 +382,16 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint64_t up = __shfl_up_sync(kFullMask, cur[i], 1);
-            const float row_seed = __shfl_sync(kFullMask, seed, row[i]);
+            float row_seed = -INFINITY;
+            if constexpr (kBounds) row_seed = __shfl_sync(kFullMask, seed, row[i]);
             if (pos[i] < K) {
               const uint64_t ne = lane < pos[i] ? cur[i] : (lane == pos[i] ? key[i] : up);
               lists[row[i] * 32 + lane] = ne;
               if (lane == K - 1)
                 *reinterpret_cast<volatile float*>(&floor_s[row[i]]) =
-                    ne ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed) : row_seed;
+                    ne ? (kBounds ? fmaxf(from_orderable_bits(static_cast<uint32_t>(ne >> 32)), row_seed)
+                                  : from_orderable_bits(static_cast<uint32_t>(ne >> 32)))
+                       : row_seed;
             }
           }
         }
@@ -400,7 +410,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int r = 0; r < 32; ++r) {
         const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + r;
         const uint64_t e = lists[r * 32 + lane];
-        if (p.floor_peers > 0) {
+        if (kBounds && p.floor_peers > 0) {
           const uint64_t last = shfl_u64(e, K - 1);
           if (lane == r && last != 0) reached = from_orderable_bits(static_cast<uint32_t>(last >> 32));
         }
@@ -421,7 +431,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         lists[r * 32 + lane] = 0;
       }
-      if (p.floor_peers > 0 && reached > told) {
+      if (kBounds && p.floor_peers > 0 && reached > told) {
         // The K-th best over a part of the bank never exceeds the K-th best over all of it: a
         // valid bound for every other shard, whichever part of the slot range this unit covered.
         const int64_t row = static_cast<int64_t>(pair) * kBlockRows + iw * 32 + lane;
