@@ -57,6 +57,29 @@ struct WideLayout {
   }
 };
 
+// One exchange of bounds for the 32 rows of an inserter warp (lane r: row r): store the K-th best
+// score the row has reached where it rose since the last time, raise the floor to what the peers
+// have stored. Out of line: it runs a few hundred times per unit, the kernel around it is tuned.
+__device__ __noinline__ void exchange_row_bounds(const Params& p, const uint64_t* lists, float* floor_s, int block,
+                                                 int iw, int lane, int K, float& seed, float& told) {
+  const int64_t row = static_cast<int64_t>(block) * kBlockRows + iw * 32 + lane;
+  if (row >= p.rows) return;
+  const int64_t name = (row + p.row_shift) % p.rows;
+  const uint64_t last = lists[lane * 32 + K - 1];
+  const float mine = last ? from_orderable_bits(static_cast<uint32_t>(last >> 32)) : -INFINITY;
+  if (mine > told) {
+    told = mine;
+    for (int peer = 0; peer < p.floor_peers; ++peer) p.floor_out[peer][name] = mine;
+  }
+  float bound = seed;
+  for (int src = 0; src < p.floor_sources; ++src)
+    bound = fmaxf(bound, __ldcg(p.floor_in + static_cast<int64_t>(src) * p.rows + name));
+  if (bound > seed) {
+    seed = bound;
+    if (bound > mine) *reinterpret_cast<volatile float*>(&floor_s[lane]) = bound;
+  }
+}
+
 // kBounds: the instantiation that takes and gives row bounds (row_floor, floor_in, floor_out).
 // The plain one is compiled without any of it, so a single GPU runs exactly the kernel it ran
 // before bounds existed.
@@ -290,24 +313,7 @@ score_topk_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const bool sharing = kBounds && (p.floor_peers > 0 || p.floor_sources > 0);
     float told = -INFINITY;    // lane r: the last bound stored for row r of this unit
     uint32_t batches = 0;
-    auto refresh_bounds = [&](int block) {
-      const int64_t row = static_cast<int64_t>(block) * kBlockRows + iw * 32 + lane;
-      if (row >= p.rows) return;
-      const int64_t name = (row + p.row_shift) % p.rows;
-      const uint64_t last = lists[lane * 32 + K - 1];
-      const float mine = last ? from_orderable_bits(static_cast<uint32_t>(last >> 32)) : -INFINITY;
-      if (mine > told) {
-        told = mine;
-        for (int peer = 0; peer < p.floor_peers; ++peer) p.floor_out[peer][name] = mine;
-      }
-      float bound = seed;
-      for (int src = 0; src < p.floor_sources; ++src)
-        bound = fmaxf(bound, __ldcg(p.floor_in + static_cast<int64_t>(src) * p.rows + name));
-      if (bound > seed) {
-        seed = bound;
-        if (bound > mine) *reinterpret_cast<volatile float*>(&floor_s[lane]) = bound;
-      }
-    };
+    auto refresh_bounds = [&](int block) { exchange_row_bounds(p, lists, floor_s, block, iw, lane, K, seed, told); };
     for (int unit = first_unit; unit < units && ok; unit += unit_stride) {
       const UnitSpan span = unit_span(p, unit);
       const int pair = span.block;
