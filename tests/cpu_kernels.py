@@ -20,6 +20,53 @@ def pk_select_into(scores, width, routes, index_at, weights_at):
     routes[weights_at:weights_at + n] = torch.from_numpy(w.reshape(-1)).view(torch.int32)
 
 
+def score_topk(queries, keys, width, col_base=0, out=None, row_floor=None, floor_in=None, floor_out=(), row_shift=0):
+    """Dense-key routing of one shard with row bounds, as glsdm_score_topk_shared defines it: best
+    `width` (score, slot) per row, larger slot first on equal scores; candidates below the row's
+    bound are dropped (padding: -inf, slot -1); the width-th best score of every full list is
+    stored at the given addresses under the row's name (row + row_shift) % rows."""
+    import ctypes
+    scores = queries.float() @ keys.float().T
+    rows, slots = scores.shape
+    names = (torch.arange(rows) + row_shift) % rows
+    bound = torch.full((rows,), float("-inf")) if row_floor is None else row_floor.clone()
+    if floor_in is not None:
+        bound = torch.maximum(bound, floor_in[:, names].amax(0))
+    order = torch.argsort(scores.flip(1), dim=1, descending=True, stable=True)[:, :width]
+    slot = slots - 1 - order
+    best = scores.gather(1, slot)
+    keep = best >= bound.unsqueeze(1)
+    best = torch.where(keep, best, torch.full_like(best, float("-inf")))
+    slot = torch.where(keep, slot + col_base, torch.full_like(slot, -1))
+    told = keep[:, width - 1]
+    for address in floor_out:
+        box = np.ctypeslib.as_array((ctypes.c_float * rows).from_address(int(address)))
+        box[names[told].numpy()] = best[told, width - 1].numpy()
+    if out is None:
+        return best, slot.int()
+    out[0].copy_(best)
+    out[1].copy_(slot.int())
+    return out
+
+
+def topk_merge_packed(packed, parts, rows, width, out):
+    """parts x (scores [rows, width] as float32 bits | slots [rows, width]) -> (slots ascending, softmax
+    weights): reference tie rule gl_sdm/memory/routing.py:21-26 over the union of the lists."""
+    region = rows * width
+    blocks = packed.view(parts, 2, region)
+    score = blocks[:, 0].view(torch.float32).view(parts, rows, width).permute(1, 0, 2).reshape(rows, parts * width)
+    slot = blocks[:, 1].view(parts, rows, width).permute(1, 0, 2).reshape(rows, parts * width).long()
+    score = torch.where(slot >= 0, score, torch.full_like(score, float("-inf")))
+    by_slot = torch.argsort(slot, dim=1, descending=True, stable=True)          # larger slot first among equals
+    score, slot = score.gather(1, by_slot), slot.gather(1, by_slot)
+    chosen = torch.argsort(score, dim=1, descending=True, stable=True)[:, :width]
+    score, slot = score.gather(1, chosen), slot.gather(1, chosen)
+    canonical = torch.argsort(slot, dim=1)
+    out[0].copy_(slot.gather(1, canonical).to(out[0].dtype))
+    out[1].copy_(score.gather(1, canonical).softmax(-1))
+    return out
+
+
 def _blocked(buf, at, rows, block_rows, stride, width):
     out = []
     for b in range(rows // block_rows):
